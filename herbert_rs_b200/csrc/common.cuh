@@ -1,0 +1,66 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Conventions used by every kernel file:
+//  * activations and cache entries are of type T = float (32-bit path) or __nv_bfloat16;
+//    sums, norms, softmax, rotation and the residual stream are always float;
+//  * every launcher is `extern "C"`, takes raw device pointers plus a cudaStream_t (as void*),
+//    returns 0 on success and a non-zero code after storing a message for hb_last_error();
+//  * a launcher validates sizes on the host and refuses what its kernel cannot do; it never
+//    launches a kernel that could give a wrong result.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+typedef __nv_bfloat16 bf16;
+
+// ---- host-side error reporting ------------------------------------------------------------
+void hb_set_error(const char* fmt, ...);
+#define HB_FAIL(code, ...)            \
+  do {                                \
+    hb_set_error(__VA_ARGS__);        \
+    return (code);                    \
+  } while (0)
+#define HB_REQUIRE(cond, ...)         \
+  do {                                \
+    if (!(cond)) HB_FAIL(2, __VA_ARGS__); \
+  } while (0)
+#define HB_CHECK_LAUNCH(name)                                                   \
+  do {                                                                          \
+    cudaError_t e__ = cudaGetLastError();                                       \
+    if (e__ != cudaSuccess) HB_FAIL(3, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+  } while (0)
+
+// ---- conversions ---------------------------------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- reductions -----------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Sum over a whole block (any multiple of 32 threads up to 1024); every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarp) ? smem32[lane] : 0.0f;
+  t = warp_sum(t);
+  return t;
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }

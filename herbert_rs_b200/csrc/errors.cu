@@ -1,0 +1,18 @@
+// Last-error storage shared by every launcher (thread-local, host side).
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "api.h"
+#include "common.cuh"
+
+static thread_local char g_last_error[512] = "";
+
+void hb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* hb_last_error(void) { return g_last_error; }
+extern "C" int hb_abi_version(void) { return 1; }

@@ -1,0 +1,169 @@
+"""The engine: a model, its cache, and the one step function.
+
+`step(entries, want)` runs exactly the tokens it is given, as one packed batch, from the cache
+that earlier steps left, and returns float logits at the wanted places.  Sequences that start
+together bring their whole prompts in one step (unequal lengths, no padding) and then one token
+each; a sequence may also bring a few tokens at a time (a prompt cut into pieces).  The
+reference's counterparts serve one sequence: `prefill`, `decode_next`, `continue_prefill`
+(crates/core/src/backend.rs:137-158) and logits at every new position (`verify_draft_tokens`,
+crates/backends/backend_common/src/generic_model.rs:737-834).
+
+Everything is validated on the host before anything is launched, as the reference does
+(generic_model.rs:140-152, 165-172, 531-537): empty input, token id >= vocab, context overflow,
+and here also slot validity, room in the cache, and a slot named twice.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from ..cache import SequenceCache
+from ..errors import BackendError, RequestError
+from ..sampling import SamplingParams, device_choose
+from .batch import StepBatch
+from .runtime import Runtime
+
+Want = Union[str, Sequence[Sequence[int]], None]
+
+
+class Engine:
+    def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None,
+                 max_seq_len: Optional[int] = None):
+        if not torch.cuda.is_available() or model.rt.device.type != "cuda":
+            raise BackendError("the engine runs on a CUDA device only: there is no CPU path")
+        self.model = model
+        self.rt: Runtime = model.rt
+        ps = self.rt.page_size
+        num_pages = max(1, -(-int(max_tokens) // ps))
+        num_slots = max_slots if max_slots is not None else min(num_pages, 1024)
+        limit = model.spec.max_position if max_seq_len is None else min(max_seq_len, model.spec.max_position)
+        self.cache = SequenceCache(model.cache_needs(), model.reads_cache_of(), num_pages, num_slots,
+                                   page_size=ps, max_seq_len=limit, dtype=self.rt.dtype, device=self.rt.device)
+        self._host = torch.empty(1 << 14, dtype=torch.int32).pin_memory()
+        self._dev = torch.empty(1 << 14, dtype=torch.int32, device=self.rt.device)
+        self._tok_out = torch.empty(max(num_slots, 1), dtype=torch.int32, device=self.rt.device)
+        self._tok_host = torch.empty(max(num_slots, 1), dtype=torch.int32).pin_memory()
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+
+    # -- construction ------------------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", max_tokens: int = 4096,
+                    max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device="cuda",
+                    page_size: int = 64) -> "Engine":
+        from ..weights import load_model
+        model = load_model(model_dir, device=device, dtype=_dtype(dtype), page_size=page_size)
+        return cls(model, max_tokens, max_slots, max_seq_len)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.model.spec.vocab_size
+
+    @property
+    def default_stop_token_ids(self) -> tuple:
+        return tuple(self.model.spec.stop_token_ids)
+
+    @property
+    def max_slots(self) -> int:
+        return self.cache.num_slots
+
+    # -- slots -------------------------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    def truncate(self, slot: int, n: int) -> None:
+        self.cache.truncate(slot, n)
+
+    # -- the step ----------------------------------------------------------------------------
+    def _prepare(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Want,
+                 uniforms: Optional[np.ndarray] = None, pages_width: Optional[int] = None) -> StepBatch:
+        if len(entries) == 0:
+            raise RequestError("a step needs at least one sequence")
+        slots = [int(s) for s, _ in entries]
+        tokens = [list(t) for _, t in entries]
+        V = self.vocab_size
+        for s, t in zip(slots, tokens):
+            if len(t) == 0:
+                raise RequestError(f"slot {s}: a sequence must bring at least one token")
+            bad = [x for x in t if not (isinstance(x, (int, np.integer)) and 0 <= x < V)]
+            if bad:
+                raise RequestError(f"slot {s}: token id {bad[0]!r} is outside the vocabulary of {V}")
+        if want is None or want == "none":
+            want_l: List[List[int]] = [[] for _ in tokens]
+        elif want == "last":
+            want_l = [[len(t) - 1] for t in tokens]
+        elif want == "all":
+            want_l = [list(range(len(t))) for t in tokens]
+        else:
+            want_l = [list(w) for w in want]
+            if len(want_l) != len(tokens):
+                raise RequestError("want must list places for every sequence of the step")
+            for w, t in zip(want_l, tokens):
+                if any(not (0 <= i < len(t)) for i in w):
+                    raise RequestError(f"a wanted place is outside the {len(t)} tokens its sequence brings")
+        self.cache.reserve([(s, len(t)) for s, t in zip(slots, tokens)])
+        pos0 = [self.cache.lengths[s] for s in slots]
+        batch = StepBatch(slots, tokens, pos0, want_l, self.cache.num_kv_groups, pages_width, self.rt.page_size)
+        n = batch.layout.total
+        if n > self._host.numel():
+            size = 1 << (n - 1).bit_length()
+            self._host = torch.empty(size, dtype=torch.int32).pin_memory()
+            self._dev = torch.empty(size, dtype=torch.int32, device=self.rt.device)
+        rows = [self.cache.page_rows(g, slots, batch.pages_width) for g in range(self.cache.num_kv_groups)]
+        self._copied.synchronize()  # the previous step's transfer has read the pinned buffer
+        batch.fill_host(self._host.numpy(), rows, uniforms)
+        self._dev[:n].copy_(self._host[:n], non_blocking=True)
+        self._copied.record()
+        self.h2d_bytes_last = n * 4
+        batch.bind(self._dev)
+        return batch
+
+    def _finish(self, batch: StepBatch) -> None:
+        for s, n in zip(batch.slots, batch.q_lens):
+            self.cache.advance(s, n)
+
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Want = "last") -> Optional[torch.Tensor]:
+        """Run the given tokens; return logits [wanted, vocab] (float32, on the device), in the order
+        of the entries and of their wanted places.  The tensor is the engine's own buffer: it is
+        overwritten by the next step, so copy what must last."""
+        batch = self._prepare(entries, want)
+        logits = self.model.forward(batch, self.cache)
+        self._finish(batch)
+        return logits
+
+    def step_and_choose(self, entries: Sequence[Tuple[int, Sequence[int]]], params: SamplingParams,
+                        uniforms: Optional[Sequence[float]] = None) -> List[int]:
+        """One step with the logits at each sequence's last token, then one token id per sequence
+        chosen on the device; only the ids travel back to the host."""
+        B = len(entries)
+        u = None if uniforms is None else np.asarray(uniforms, dtype=np.float32)
+        batch = self._prepare(entries, "last", u)
+        logits = self.model.forward(batch, self.cache)
+        self._finish(batch)
+        out = self._tok_out[:B]
+        device_choose(logits, params, batch.uniforms, out)
+        self._tok_host[:B].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes_last = B * 4
+        return self._tok_host[:B].tolist()
+
+
+def _dtype(d) -> torch.dtype:
+    if isinstance(d, torch.dtype):
+        return d
+    table = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+             "f32": torch.float32}
+    if d not in table:
+        raise BackendError(f"unknown dtype {d!r}: bfloat16 or float32")
+    return table[d]

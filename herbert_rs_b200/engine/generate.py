@@ -1,0 +1,171 @@
+"""The generation loop: batches of unequal prompts, stop tokens, sequences that end earlier,
+and as many batches one after another as there are requests.
+
+The reference's loop serves one sequence (crates/cli/src/main.rs:1000-1009 first token from the
+prompt's logits; :1241-1376 `for _ in 0..max_tokens { decode_next; sample; push; stop checks }`).
+Kept from it: the stop token is part of the output (main.rs:1272, 1357); `ignore_eos`
+(main.rs:94-96); the repetition detector (crates/core/src/decode_utils.rs:14-33: the same
+pattern of 6..100 tokens three times in a row); the statistics' definitions (main.rs:1443-1459:
+prefill tok/s = prompt tokens / prefill seconds; decode tok/s = (generated - 1) / decode seconds).
+
+The loop only decides; it talks to the engine through three calls (`alloc_slot`, `free_slot`,
+`step_and_choose`), so its decisions are tested on the CPU with a stand-in engine.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+from ..errors import CacheError, RequestError
+from ..sampling import SamplingParams, uniform_for
+
+MIN_PATTERN, MAX_PATTERN, REPEATS = 6, 100, 3  # crates/core/src/decode_utils.rs:15-17
+
+
+def detect_repetition_loop(tokens: Sequence[int]) -> Optional[int]:
+    """Length of a pattern that the last tokens repeat three times, or None."""
+    n = len(tokens)
+    for pat in range(MIN_PATTERN, MAX_PATTERN + 1):
+        need = pat * REPEATS
+        if n < need:
+            continue
+        base = n - need
+        first = tokens[base:base + pat]
+        if all(tokens[base + r * pat: base + (r + 1) * pat] == first for r in range(1, REPEATS)):
+            return pat
+    return None
+
+
+@dataclass
+class GenerationOptions:
+    max_tokens: int = 2048            # crates/cli/src/main.rs:90-92
+    stop_token_ids: Optional[Sequence[int]] = None  # None: the model's own (config eos_token_id)
+    ignore_eos: bool = False
+    repeat_check: bool = False
+    max_batch: Optional[int] = None   # most sequences of one batch; None: as many as there are slots
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+    decode_steps: int = 0
+    batches: int = 0
+
+    @property
+    def prefill_tokens_per_second(self) -> float:
+        return self.prompt_tokens / self.prefill_seconds if self.prefill_seconds > 0 else 0.0
+
+    @property
+    def decode_tokens_per_second(self) -> float:
+        n = self.generated_tokens - self.first_tokens
+        return n / self.decode_seconds if self.decode_seconds > 0 else 0.0
+
+    first_tokens: int = 0
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[List[int]]
+    finish_reasons: List[str]
+    stats: GenerationStats = field(default_factory=GenerationStats)
+
+
+def plan_batches(n_requests: int, max_batch: int) -> List[List[int]]:
+    """Requests in their order, cut into batches of at most max_batch."""
+    if max_batch <= 0:
+        raise RequestError("max_batch must be > 0")
+    return [list(range(i, min(i + max_batch, n_requests))) for i in range(0, n_requests, max_batch)]
+
+
+def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
+             sampling: Optional[SamplingParams] = None, stop_token_ids: Optional[Sequence[int]] = None
+             ) -> GenerationResult:
+    """Generate for every prompt; results keep the order of the requests.
+
+    `engine` needs: alloc_slot(), free_slot(slot), step_and_choose(entries, params, uniforms) -> ids,
+    and optionally `default_stop_token_ids` and `max_slots`.
+    finish_reason is one of: "stop_token", "max_tokens", "repetition", "capacity".
+    """
+    options = options or GenerationOptions()
+    sampling = sampling or SamplingParams()
+    sampling.validate()
+    if options.max_tokens < 0:
+        raise RequestError("max_tokens must be >= 0")
+    prompts = [list(p) for p in prompts]
+    for i, p in enumerate(prompts):
+        if not p:
+            raise RequestError(f"request {i}: the prompt is empty")
+    stops = stop_token_ids if stop_token_ids is not None else options.stop_token_ids
+    if stops is None:
+        stops = getattr(engine, "default_stop_token_ids", ())
+    stops = set() if options.ignore_eos else set(int(s) for s in stops)
+    seed = sampling.resolved_seed()
+    max_batch = options.max_batch or getattr(engine, "max_slots", None) or len(prompts) or 1
+
+    out: List[List[int]] = [[] for _ in prompts]
+    reasons: List[str] = ["max_tokens"] * len(prompts)
+    stats = GenerationStats()
+    if options.max_tokens == 0:
+        return GenerationResult(out, reasons, stats)
+
+    def finished(i: int, tok: int) -> Optional[str]:
+        if tok in stops:
+            return "stop_token"
+        if len(out[i]) >= options.max_tokens:
+            return "max_tokens"
+        if options.repeat_check and detect_repetition_loop(out[i]) is not None:
+            return "repetition"
+        return None
+
+    for batch_ids in plan_batches(len(prompts), max_batch):
+        stats.batches += 1
+        slots = {}
+        try:
+            for i in batch_ids:
+                slots[i] = engine.alloc_slot()
+            # all prompts in one step
+            t0 = time.perf_counter()
+            uni = [uniform_for(seed, i, 0) for i in batch_ids]
+            toks = engine.step_and_choose([(slots[i], prompts[i]) for i in batch_ids], sampling, uni)
+            stats.prefill_seconds += time.perf_counter() - t0
+            stats.prompt_tokens += sum(len(prompts[i]) for i in batch_ids)
+            active = []
+            for i, tok in zip(batch_ids, toks):
+                out[i].append(int(tok))
+                r = finished(i, int(tok))
+                if r is None:
+                    active.append(i)
+                else:
+                    reasons[i] = r
+            stats.first_tokens += len(batch_ids)
+            # then one token each, for the sequences that still run
+            t0 = time.perf_counter()
+            while active:
+                uni = [uniform_for(seed, i, len(out[i])) for i in active]
+                try:
+                    toks = engine.step_and_choose([(slots[i], [out[i][-1]]) for i in active], sampling, uni)
+                except CacheError:
+                    for i in active:
+                        reasons[i] = "capacity"
+                    break
+                stats.decode_steps += 1
+                still = []
+                for i, tok in zip(active, toks):
+                    out[i].append(int(tok))
+                    r = finished(i, int(tok))
+                    if r is None:
+                        still.append(i)
+                    else:
+                        reasons[i] = r
+                active = still
+            stats.decode_seconds += time.perf_counter() - t0
+        finally:
+            for s in slots.values():
+                engine.free_slot(s)
+    stats.generated_tokens = sum(len(o) for o in out)
+    return GenerationResult(out, reasons, stats)

@@ -1,0 +1,170 @@
+"""Python faces of the kernels: one function per launcher of the kernel library.
+
+Each function takes CUDA tensors, checks what only the host can check cheaply (device,
+dtype, contiguity of the innermost axis) and launches on the current CUDA stream.  A launcher
+that refuses its input raises `BackendError` with the launcher's own message.  Nothing here
+computes on the CPU and nothing falls back to a library model or attention routine.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from ..errors import BackendError
+from . import lib as _libmod
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL = 0, 1, 2
+
+_SIGS = {
+    "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "hb_rmsnorm": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "hb_swiglu": [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_add_residual": [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "hb_qk_norm_rope_cache": [c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                              c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_gemm_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
+}
+_fns: dict = {}
+
+
+def _fn(name: str):
+    f = _fns.get(name)
+    if f is None:
+        lib = _libmod.load()
+        try:
+            f = getattr(lib, name)
+        except AttributeError:
+            raise BackendError(f"kernel library has no entry point {name}") from None
+        f.argtypes = _SIGS[name]
+        f.restype = c_int
+        _fns[name] = f
+    return f
+
+
+def _run(name: str, *args) -> None:
+    rc = _fn(name)(*args)
+    if rc != 0:
+        raise BackendError(f"{name}: {_libmod.last_error()}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise BackendError(f"unsupported activation dtype {dtype}: float32 or bfloat16")
+
+
+def _ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _check(t: torch.Tensor, dtype, name: str) -> None:
+    if not t.is_cuda:
+        raise BackendError(f"{name} must be a CUDA tensor: there is no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise BackendError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.dim() > 0 and t.stride(-1) != 1:
+        raise BackendError(f"{name} must be contiguous along its last axis")
+
+
+def is_available() -> bool:
+    """True when a CUDA device is present (the kernels still have to build and load)."""
+    return torch.cuda.is_available()
+
+
+# ---------------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = float(table[ids[t], :]); out is the float residual stream [T, H]."""
+    _check(table, None, "table"); _check(ids, torch.int32, "ids"); _check(out, torch.float32, "out")
+    _run("hb_embed", dtype_code(table.dtype), table.data_ptr(), ids.data_ptr(), out.data_ptr(),
+         ids.numel(), table.shape[1], table.shape[0], _stream())
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * w; x and w float, out in the activation dtype."""
+    _check(x, torch.float32, "x"); _check(w, torch.float32, "w"); _check(out, None, "out")
+    n = out.shape[0]
+    _run("hb_rmsnorm", dtype_code(out.dtype), x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(rows),
+         n, x.shape[-1], float(eps), _stream())
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor, interleave: int) -> None:
+    """out[t, i] = silu(gate) * up from gu [T, 2I] (see the kernel for the column layout)."""
+    _check(gu, None, "gu"); _check(out, gu.dtype, "out")
+    _run("hb_swiglu", dtype_code(gu.dtype), gu.data_ptr(), gu.stride(0), out.data_ptr(), out.stride(0),
+         gu.shape[0], out.shape[1], int(interleave), _stream())
+
+
+def add_residual(residual: torch.Tensor, y: torch.Tensor) -> None:
+    """residual += y (float sum)."""
+    _check(residual, torch.float32, "residual"); _check(y, None, "y")
+    _run("hb_add_residual", dtype_code(y.dtype), residual.data_ptr(), y.data_ptr(), y.stride(0),
+         y.shape[0], y.shape[1], _stream())
+
+
+def qk_norm_rope_cache(qkv, q_weight, k_weight, eps, cos, sin, rotary_dim, tok_seq, tok_pos, seq_pages,
+                       k_cache, v_cache, num_heads, num_kv_heads, head_dim, page_size, write_cache=True) -> None:
+    """Head norm + rotation of q (in place) and k (into the cache), v copied into the cache."""
+    _check(qkv, None, "qkv")
+    _run("hb_qk_norm_rope_cache", dtype_code(qkv.dtype), qkv.data_ptr(), qkv.stride(0), _ptr(q_weight),
+         _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), int(rotary_dim),
+         0 if cos is None else cos.shape[0], tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(),
+         seq_pages.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), qkv.shape[0], num_heads,
+         num_kv_heads, head_dim, page_size, 1 if write_cache else 0, _stream())
+
+
+def gemm_simt(a, w, c, epilogue=EPI_STORE) -> None:
+    """c (op)= a @ w.T on the CUDA cores, any sizes."""
+    _check(a, None, "a"); _check(w, a.dtype, "w"); _check(c, None, "c")
+    _run("hb_gemm_simt", dtype_code(a.dtype), a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0),
+         c.data_ptr(), c.stride(0), a.shape[0], w.shape[0], a.shape[1], epilogue, _stream())
+
+
+def attention_simt(q, ldq, out, k_cache, v_cache, tok_seq, tok_pos, seq_pages, num_heads, num_kv_heads,
+                   head_dim, page_size, scale, window) -> None:
+    _run("hb_attention_simt", dtype_code(out.dtype), q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0),
+         k_cache.data_ptr(), v_cache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(),
+         seq_pages.stride(0), out.shape[0], num_heads, num_kv_heads, head_dim, page_size, float(scale),
+         int(window or 0), _stream())
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _check(logits, torch.float32, "logits"); _check(out, torch.int32, "out")
+    _run("hb_argmax", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(), _stream())
+
+
+def sample(logits, temperature, top_k, top_p, uniforms, out) -> None:
+    _check(logits, torch.float32, "logits"); _check(uniforms, torch.float32, "uniforms"); _check(out, torch.int32, "out")
+    _run("hb_sample", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], float(temperature),
+         int(top_k), float(top_p), uniforms.data_ptr(), out.data_ptr(), _stream())
+
+
+# ---------------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE) -> None:
+    """c (op)= a @ w.T with the kernel that fits dtype and sizes.
+
+    a [M, K] and w [N, K] share a dtype (float32: the true 32-bit product on the CUDA cores;
+    bfloat16: tensor-core kernels where their size rules hold, else the any-shape kernel).
+    """
+    gemm_simt(a, w, c, epilogue)
+
+
+def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, head_dim, page_size,
+              scale, window, seq_pages) -> None:
+    """Attention of every token of the step over its sequence's cached keys and values."""
+    attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
+                   num_kv_heads, head_dim, page_size, scale, window)

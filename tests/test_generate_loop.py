@@ -1,0 +1,130 @@
+"""The generation loop's decisions, with a stand-in engine (no GPU)."""
+import pytest
+
+import herbert_rs_b200 as hb
+from herbert_rs_b200.engine.generate import detect_repetition_loop, generate, plan_batches
+from herbert_rs_b200.errors import CacheError, RequestError
+
+
+class FakeEngine:
+    """Next token = (last token + 1) % 100; records every step; has `max_slots` slots."""
+
+    def __init__(self, max_slots=4, capacity=None):
+        self.max_slots = max_slots
+        self.free = list(range(max_slots))
+        self.steps = []
+        self.default_stop_token_ids = (50,)
+        self.lengths = {}
+        self.capacity = capacity
+        self.uniforms = []
+
+    def alloc_slot(self):
+        s = self.free.pop(0)
+        self.lengths[s] = 0
+        return s
+
+    def free_slot(self, s):
+        assert s not in self.free
+        self.free.append(s)
+        self.free.sort()
+
+    def step_and_choose(self, entries, params, uniforms):
+        for s, t in entries:
+            if self.capacity is not None and self.lengths[s] + len(t) > self.capacity:
+                raise CacheError("cache full")
+        for s, t in entries:
+            self.lengths[s] += len(t)
+        self.steps.append([(s, list(t)) for s, t in entries])
+        self.uniforms.append(list(uniforms))
+        return [(t[-1] + 1) % 100 for _, t in entries]
+
+
+def test_unequal_prompts_then_one_token_each():
+    e = FakeEngine()
+    r = generate(e, [[1, 2, 3], [10], [20, 21]], hb.GenerationOptions(max_tokens=3), hb.SamplingParams(temperature=0.0))
+    assert r.tokens == [[4, 5, 6], [11, 12, 13], [22, 23, 24]]
+    assert r.finish_reasons == ["max_tokens"] * 3
+    assert e.steps[0] == [(0, [1, 2, 3]), (1, [10]), (2, [20, 21])]      # all prompts in one step
+    assert e.steps[1] == [(0, [4]), (1, [11]), (2, [22])]                # then one token each
+    assert len(e.steps) == 3 and e.free == [0, 1, 2, 3]
+    assert r.stats.prompt_tokens == 6 and r.stats.generated_tokens == 9 and r.stats.decode_steps == 2
+
+
+def test_stop_token_ends_a_sequence_early_and_is_kept():
+    e = FakeEngine()
+    r = generate(e, [[48], [10], [49]], hb.GenerationOptions(max_tokens=5), hb.SamplingParams(temperature=0.0))
+    assert r.tokens[0] == [49, 50] and r.finish_reasons[0] == "stop_token"     # the stop token is part of the output
+    assert r.tokens[2] == [50] and r.finish_reasons[2] == "stop_token"         # stops on its very first token
+    assert r.tokens[1] == [11, 12, 13, 14, 15]
+    assert e.steps[1] == [(0, [49]), (1, [11])]        # the one that ended is not stepped again
+    assert e.steps[2] == [(1, [12])]                   # the batch shrinks; order is kept
+
+
+def test_ignore_eos_and_user_stop_ids():
+    r = generate(FakeEngine(), [[48]], hb.GenerationOptions(max_tokens=4, ignore_eos=True), hb.SamplingParams(temperature=0.0))
+    assert r.tokens == [[49, 50, 51, 52]]
+    r = generate(FakeEngine(), [[48]], hb.GenerationOptions(max_tokens=9, stop_token_ids=[52, 60]), hb.SamplingParams(temperature=0.0))
+    assert r.tokens == [[49, 50, 51, 52]] and r.finish_reasons == ["stop_token"]
+
+
+def test_more_requests_than_slots_run_as_batches_one_after_another():
+    e = FakeEngine(max_slots=2)
+    prompts = [[i] for i in range(5)]
+    r = generate(e, prompts, hb.GenerationOptions(max_tokens=2), hb.SamplingParams(temperature=0.0))
+    assert r.tokens == [[i + 1, i + 2] for i in range(5)]
+    assert r.stats.batches == 3
+    assert [len(s) for s in e.steps] == [2, 2, 2, 2, 1, 1]
+    assert e.steps[2][0][0] == 0 and e.steps[4][0][0] == 0     # slots are used again
+    assert plan_batches(5, 2) == [[0, 1], [2, 3], [4]]
+
+
+def test_slots_are_freed_when_a_step_fails():
+    class Broken(FakeEngine):
+        def step_and_choose(self, entries, params, uniforms):
+            raise RuntimeError("boom")
+    e = Broken()
+    with pytest.raises(RuntimeError):
+        generate(e, [[1], [2]], hb.GenerationOptions(max_tokens=2), hb.SamplingParams(temperature=0.0))
+    assert e.free == [0, 1, 2, 3]
+
+
+def test_running_out_of_cache_ends_with_capacity():
+    e = FakeEngine(capacity=4)
+    r = generate(e, [[1, 2]], hb.GenerationOptions(max_tokens=10), hb.SamplingParams(temperature=0.0))
+    assert r.finish_reasons == ["capacity"] and r.tokens == [[3, 4, 5]]
+
+
+def test_uniforms_depend_on_request_and_step_not_on_batch():
+    a, b = FakeEngine(max_slots=4), FakeEngine(max_slots=1)
+    p = hb.SamplingParams(temperature=0.8, seed=123)
+    generate(a, [[1], [2], [3]], hb.GenerationOptions(max_tokens=3), p)
+    generate(b, [[1], [2], [3]], hb.GenerationOptions(max_tokens=3), p)
+    together = {(i, s): a.uniforms[s][i] for s in range(3) for i in range(3)}
+    alone = {(i, s): b.uniforms[i * 3 + s][0] for i in range(3) for s in range(3)}
+    assert together == alone
+    assert len(set(together.values())) == 9 and all(0.0 <= u < 1.0 for u in together.values())
+
+
+def test_bad_requests():
+    with pytest.raises(RequestError, match="empty"):
+        generate(FakeEngine(), [[1], []])
+    with pytest.raises(RequestError, match="temperature"):
+        generate(FakeEngine(), [[1]], sampling=hb.SamplingParams(temperature=-1.0))
+    with pytest.raises(RequestError, match="top_p"):
+        generate(FakeEngine(), [[1]], sampling=hb.SamplingParams(top_p=0.0))
+    assert generate(FakeEngine(), [[1]], hb.GenerationOptions(max_tokens=0)).tokens == [[]]
+
+
+def test_repetition_detector():
+    # the reference's constants: patterns of 6..100 tokens, three times (decode_utils.rs:14-33)
+    pat = [1, 2, 3, 4, 5, 6]
+    assert detect_repetition_loop([9] + pat * 3) == 6
+    assert detect_repetition_loop(pat * 2 + pat[:5]) is None
+    assert detect_repetition_loop([1, 2, 3, 4, 5] * 6) == 10     # a 5-pattern shows up as a 10-pattern
+    assert detect_repetition_loop([7] * 17) is None and detect_repetition_loop([7] * 18) == 6
+
+    class Looping(FakeEngine):
+        def step_and_choose(self, entries, params, uniforms):
+            return [7 for _ in entries]
+    r = generate(Looping(), [[1]], hb.GenerationOptions(max_tokens=100, repeat_check=True), hb.SamplingParams(temperature=0.0))
+    assert r.finish_reasons == ["repetition"] and len(r.tokens[0]) == 18
