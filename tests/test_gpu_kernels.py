@@ -1,0 +1,269 @@
+"""Each kernel alone against a plain PyTorch restatement of the same op, at sizes other than
+the tiny models' (odd widths, every head size in steps of 16, page edges, windows)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from herbert_rs_b200 import ops
+from herbert_rs_b200.errors import BackendError
+from herbert_rs_b200.sampling import SamplingParams, host_sample, host_survivors
+from plain_qwen3 import apply_rope, attention_scores, rms_norm, rope_tables, sample_distribution
+
+pytestmark = pytest.mark.gpu
+DT = [torch.float32, torch.bfloat16]
+
+
+def dev(t):
+    return t.cuda()
+
+
+def close(got, ref, dtype, scale=1.0):
+    got, ref = got.detach().double().cpu(), ref.double().cpu()
+    tol = (2e-5 if dtype == torch.float32 else 1.2e-2) * scale * max(1.0, ref.abs().max().item())
+    err = (got - ref).abs().max().item()
+    assert err <= tol, f"max error {err:.3e} > {tol:.3e}"
+
+
+def test_library_is_loaded_in_tree():
+    from herbert_rs_b200.ops import lib
+    lib.load()
+    maps = open("/proc/self/maps").read()
+    assert "libherbert_b200.so" in maps
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_embed(dtype):
+    torch.manual_seed(0)
+    table = torch.randn(301, 72).to(dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = torch.empty(5, 72, device="cuda")
+    ops.embed(dev(table), dev(ids), out)
+    assert torch.equal(out.cpu(), table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("dim,eps", [(72, 1e-6), (1000, 1e-5), (4096, 1e-6), (33, 1e-3)])
+def test_rmsnorm_and_gather(dtype, dim, eps):
+    torch.manual_seed(1)
+    x = torch.randn(9, dim) * 3
+    w = 1 + 0.1 * torch.randn(dim)
+    out = torch.empty(9, dim, device="cuda", dtype=dtype)
+    ops.rmsnorm(dev(x), dev(w), out, eps)
+    close(out, rms_norm(x.double(), w.double(), eps), dtype)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32)
+    out2 = torch.empty(3, dim, device="cuda", dtype=dtype)
+    ops.rmsnorm(dev(x), dev(w), out2, eps, dev(rows))
+    assert torch.equal(out2.cpu(), out.cpu()[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("inter,interleave", [(24, 8), (172, 0), (1000, 8), (7, 0)])
+def test_swiglu_layouts(dtype, inter, interleave):
+    torch.manual_seed(2)
+    g, u = (torch.randn(5, inter) * 2).to(dtype), torch.randn(5, inter).to(dtype)
+    if interleave:
+        gu = torch.cat([g.view(5, -1, 8), u.view(5, -1, 8)], dim=2).reshape(5, 2 * inter)
+    else:
+        gu = torch.cat([g, u], dim=1)
+    out = torch.empty(5, inter, device="cuda", dtype=dtype)
+    ops.swiglu(dev(gu.contiguous()), out, interleave)
+    gd, ud = g.double(), u.double()
+    close(out, gd / (1 + torch.exp(-gd)) * ud, dtype)
+    with pytest.raises(BackendError, match="no multiple of the interleave"):
+        ops.swiglu(dev(torch.zeros(1, 20, dtype=dtype)), torch.empty(1, 10, device="cuda", dtype=dtype), 8)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("M,N,K", [(1, 72, 96), (5, 100, 33), (70, 64, 64), (129, 301, 172), (64, 256, 1024)])
+def test_gemm_simt_every_epilogue(dtype, M, N, K):
+    torch.manual_seed(3)
+    a, w = torch.randn(M, K).to(dtype), (torch.randn(N, K) * 0.1).to(dtype)
+    ref = a.double() @ w.double().T
+    c = torch.empty(M, N, device="cuda", dtype=dtype)
+    ops.gemm_simt(dev(a), dev(w), c, ops.EPI_STORE)
+    close(c, ref, dtype)
+    c32 = torch.empty(M, N, device="cuda")
+    ops.gemm_simt(dev(a), dev(w), c32, ops.EPI_STORE_F32)
+    close(c32, ref, torch.float32, scale=1.0 if dtype == torch.float32 else 1.0)
+    res = torch.randn(M, N)
+    r = dev(res.clone())
+    ops.gemm_simt(dev(a), dev(w), r, ops.EPI_RESIDUAL)
+    close(r, res.double() + ref, torch.float32)
+    # a padded leading dimension: only the first K columns of each row are read
+    wide = torch.cat([a, torch.full((M, 5), 1e4).to(dtype)], dim=1)
+    c2 = torch.empty(M, N, device="cuda", dtype=dtype)
+    ops.gemm_simt(dev(wide)[:, :K], dev(w), c2, ops.EPI_STORE)
+    assert torch.equal(c2, c)
+
+
+def _paged(k, page, n_pages_total, perm_seed):
+    """Scatter per-sequence [len, nkv, hd] tensors into a page pool in a shuffled page order.
+    Returns (pool [pages, nkv, page, hd], table [B, P])."""
+    B = len(k)
+    nkv, hd = k[0].shape[1], k[0].shape[2]
+    need = [-(-x.shape[0] // page) for x in k]
+    P = max(need)
+    order = torch.randperm(n_pages_total, generator=torch.Generator().manual_seed(perm_seed)).tolist()
+    pool = torch.full((n_pages_total, nkv, page, hd), 777.0)        # poison: a stray read shows
+    table = torch.zeros(B, P, dtype=torch.int32)
+    for b, x in enumerate(k):
+        for lp in range(need[b]):
+            pg = order.pop()
+            table[b, lp] = pg
+            chunk = x[lp * page:(lp + 1) * page]
+            pool[pg, :, :chunk.shape[0]] = chunk.transpose(0, 1)
+    return pool, table
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (6, 3, 48, 24, True), (8, 1, 128, 128, False),
+                                                (3, 3, 80, 80, True), (2, 1, 256, 64, True)])
+def test_qk_norm_rope_cache_write(dtype, nh, nkv, hd, rot, norm):
+    torch.manual_seed(4)
+    page, eps = 16, 1e-5
+    pos0, qlen = [0, 30, 15], [20, 3, 1]              # crosses page edges at 16 and 32
+    B, T = 3, sum(qlen)
+    tok_seq = torch.tensor(sum(([b] * n for b, n in enumerate(qlen)), []), dtype=torch.int32)
+    tok_pos = torch.tensor(sum((list(range(p, p + n)) for p, n in zip(pos0, qlen)), []), dtype=torch.int32)
+    qkv = (torch.randn(T, (nh + 2 * nkv) * hd + 8) * 2).to(dtype)
+    qw, kw = 1 + 0.1 * torch.randn(hd), 1 + 0.1 * torch.randn(hd)
+    cos, sin = rope_tables(rot, 10000.0, 64, torch.float32)
+    table = torch.tensor([[5, 2, 0], [1, 7, 3], [4, 0, 0]], dtype=torch.int32)
+    kc = torch.full((8, nkv, page, hd), 9.0).to(dtype).cuda()
+    vc = torch.full((8, nkv, page, hd), 9.0).to(dtype).cuda()
+    d_qkv = dev(qkv.clone())
+    ops.qk_norm_rope_cache(d_qkv, dev(qw) if norm else None, dev(kw) if norm else None, eps, dev(cos), dev(sin), rot,
+                           dev(tok_seq), dev(tok_pos), dev(table), kc, vc, nh, nkv, hd, page)
+    x = qkv.double()[:, :(nh + 2 * nkv) * hd]
+    q = x[:, :nh * hd].view(T, nh, hd)
+    k = x[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    v = x[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    if norm:
+        q, k = rms_norm(q, qw.double(), eps), rms_norm(k, kw.double(), eps)
+    c, s = cos.double()[tok_pos.long()], sin.double()[tok_pos.long()]
+    q, k = apply_rope(q, c, s, rot), apply_rope(k, c, s, rot)
+    close(d_qkv[:, :nh * hd], q.reshape(T, -1), dtype)
+    assert torch.equal(d_qkv[:, nh * hd:].cpu(), qkv[:, nh * hd:])         # k, v columns and the padding stay
+    written = torch.zeros(8, page, dtype=torch.bool)
+    for t in range(T):
+        b, p = tok_seq[t].item(), tok_pos[t].item()
+        pg = table[b, p // page].item()
+        close(kc[pg, :, p % page], k[t], dtype)
+        assert torch.equal(vc[pg, :, p % page].cpu(), v[t].to(dtype))
+        written[pg, p % page] = True
+    assert (kc.cpu().float()[~written] == 9.0).all() and (vc.cpu().float()[~written] == 9.0).all()
+    # a step that only reads another step's cache entry leaves it alone
+    kc2, vc2 = kc.clone(), vc.clone()
+    ops.qk_norm_rope_cache(dev(qkv.clone()), dev(qw) if norm else None, dev(kw) if norm else None, eps, dev(cos), dev(sin),
+                           rot, dev(tok_seq), dev(tok_pos), dev(table), kc2.fill_(1.0), vc2.fill_(1.0), nh, nkv, hd, page,
+                           write_cache=False)
+    assert (kc2 == 1.0).all() and (vc2 == 1.0).all()
+
+
+def _attention_case(dtype, nh, nkv, hd, lens, qlens, window, page=16, seed=5, sharp=None):
+    """Random q/k/v for B sequences; the last qlen positions of each are this step's queries."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    ks = [torch.randn(n, nkv, hd, generator=g).to(dtype).float() for n in lens]
+    vs = [torch.randn(n, nkv, hd, generator=g).to(dtype).float() for n in lens]
+    qs = [torch.randn(n, nh, hd, generator=g).to(dtype).float() for n in lens]
+    if sharp:
+        for (b, qpos, h, kpos) in sharp:       # make key kpos stand out for query (b, qpos, h)
+            kh = h // (nh // nkv)
+            qs[b][qpos, h] = 0; qs[b][qpos, h, 3] = 12.0
+            ks[b][:, kh, 3] = ks[b][:, kh, 3].clamp(-1, 1)
+            ks[b][kpos, kh, 3] = 12.0
+    scale = 1.0 / math.sqrt(hd)
+    ref = [attention_scores(q.double(), k.double(), v.double(), scale, window)[n - ql:]
+           for q, k, v, n, ql in zip(qs, ks, vs, lens, qlens)]
+    kpool, table = _paged(ks, page, sum(-(-n // page) for n in lens) + 3, seed)
+    vpool, _ = _paged(vs, page, sum(-(-n // page) for n in lens) + 3, seed)
+    qrows = torch.cat([q[n - ql:] for q, n, ql in zip(qs, lens, qlens)]).reshape(-1, nh * hd)
+    tok_seq = torch.tensor(sum(([b] * ql for b, ql in enumerate(qlens)), []), dtype=torch.int32)
+    tok_pos = torch.tensor(sum((list(range(n - ql, n)) for n, ql in zip(lens, qlens)), []), dtype=torch.int32)
+    return dict(q=qrows.to(dtype), k=kpool.to(dtype), v=vpool.to(dtype), table=table, tok_seq=tok_seq, tok_pos=tok_pos,
+                ref=torch.cat(ref).reshape(-1, nh * hd), scale=scale, vs=vs)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 3, 48), (8, 1, 128), (5, 5, 80), (12, 4, 64), (2, 1, 256), (3, 1, 112)])
+@pytest.mark.parametrize("window", [None, 21])
+def test_attention_simt_prefill_and_decode_shapes(dtype, nh, nkv, hd, window):
+    for lens, qlens in [([1, 70, 33], [1, 70, 33]), ([200, 17, 64, 65], [1, 1, 1, 1]), ([90, 50], [7, 50])]:
+        c = _attention_case(dtype, nh, nkv, hd, lens, qlens, window)
+        out = torch.empty(c["q"].shape, device="cuda", dtype=dtype)
+        ops.attention_simt(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(c["tok_seq"]), dev(c["tok_pos"]),
+                           dev(c["table"]), nh, nkv, hd, 16, c["scale"], window)
+        close(out, c["ref"], dtype)
+
+
+@pytest.mark.parametrize("dtype", DT)
+def test_attention_finds_a_far_key_and_respects_the_windows_edge(dtype):
+    nh, nkv, hd = 4, 2, 64
+    lens, qlens = [700, 300], [1, 1]
+    # sequence 0: query head 3 looks at key 5 (far away, first page); sequence 1: head 0 at key 299-40+1
+    W = 40
+    for window, sharp, hit in [(None, [(0, 699, 3, 5)], True), (W, [(1, 299, 0, 299 - W + 1)], True),
+                               (W, [(1, 299, 0, 299 - W)], False)]:
+        c = _attention_case(dtype, nh, nkv, hd, lens, qlens, window, sharp=sharp)
+        out = torch.empty(c["q"].shape, device="cuda", dtype=dtype)
+        ops.attention_simt(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(c["tok_seq"]), dev(c["tok_pos"]),
+                           dev(c["table"]), nh, nkv, hd, 16, c["scale"], window)
+        close(out, c["ref"], dtype)
+        b, _, h, kpos = sharp[0]
+        target = c["vs"][b][kpos, h // 2]
+        got = out[b].view(nh, hd)[h].float().cpu()
+        assert ((got - target).abs().max() < 0.05) == hit
+
+
+def test_argmax_first_maximum_and_ties():
+    torch.manual_seed(6)
+    x = torch.randn(7, 5000)
+    x[0, 4000] = x[0, 17] = 50.0
+    x[1, :] = -float("inf")
+    x[2, 4999] = 99.0
+    x[3, 0] = 99.0
+    out = torch.empty(7, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(x), out)
+    want = [int(torch.argmax(r)) for r in x]
+    want[0], want[1] = 17, 0
+    assert out.cpu().tolist() == want
+    padded = dev(torch.cat([x, torch.full((7, 9), 1e9)], dim=1))[:, :5000]       # a leading dimension beyond vocab
+    ops.argmax(padded, out)
+    assert out.cpu().tolist() == want
+
+
+@pytest.mark.parametrize("t,k,p", [(0.8, 20, 0.9), (0.4, 40, 0.9), (1.0, 0, 1.0), (1.3, 0, 0.5), (0.7, 5, 1.0),
+                                   (1.0, 1, 0.9), (1.0, 3000, 0.95), (2.0, 7, 0.01)])
+def test_sample_kernel_against_its_host_twin_and_the_reference_distribution(t, k, p):
+    rng = np.random.default_rng(7)
+    V, R = 2500, 4096
+    logits = (rng.standard_normal(V) * 2.0).astype(np.float32)
+    us = ((np.arange(R) + 0.5) / R).astype(np.float32)
+    rows = dev(torch.from_numpy(logits)).expand(R, V).contiguous()
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(rows, t, k, p, dev(torch.from_numpy(us)), out)
+    got = out.cpu().numpy()
+    params = SamplingParams(t, k, p)
+    keep, e = host_survivors(logits, params)
+    assert keep[got].all()                                   # only survivors are ever drawn
+    c = np.cumsum(e.astype(np.float64)); c /= c[-1]
+    lo = np.concatenate([[0.0], c[:-1]])
+    # the drawn token's cumulative interval contains r, up to float rounding of the running sums
+    assert (us >= lo[got] - 1e-5).all() and (us <= c[got] + 1e-5).all()
+    twin = np.array([host_sample(logits, params, float(u)) for u in us[::16]])
+    assert (twin == got[::16]).mean() > 0.99
+    want = sample_distribution(logits, t, k, p)
+    assert np.abs(np.bincount(got, minlength=V) / R - want).max() < 3.0 / R + 1e-5
+
+
+def test_sample_refuses_bad_options():
+    x = dev(torch.zeros(1, 8)); u = dev(torch.zeros(1)); o = torch.empty(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(BackendError, match="temperature must be > 0"):
+        ops.sample(x, 0.0, 0, 1.0, u, o)
+    with pytest.raises(BackendError, match="head size 272 exceeds"):
+        ops.attention_simt(x, 8, x, x, x, o, o, o, 1, 1, 272, 16, 1.0, None)
+    with pytest.raises(BackendError, match="CUDA tensor"):
+        ops.argmax(torch.zeros(1, 8), o)

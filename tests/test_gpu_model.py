@@ -1,0 +1,235 @@
+"""The engine against the plain implementation, in every way of cutting the work."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import herbert_rs_b200 as hb
+from gpu_util import (DTYPES, assert_close, engine_for, random_ids, replay_batches, replay_tail_one_by_one,
+                      replay_whole, to_np)
+from plain_qwen3 import PlainModel
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def plain(model_dirs):
+    return {k: PlainModel(v) for k, v in model_dirs.items()}
+
+
+@pytest.fixture(scope="module")
+def sharp_dir(tmp_path_factory, model_dirs):
+    """Tiny B with the q/k head-norm weights scaled up: scores spread out, so that attention looks
+    at few keys and a single wrong, missing or stale key changes the logits visibly."""
+    from herbert_rs_b200.weights import ModelFiles, save_file
+    d = str(tmp_path_factory.mktemp("tiny_Bsharp"))
+    files = ModelFiles(model_dirs["B"])
+    t = {n: files.tensor(n) for n in files.names()}
+    for n in t:
+        if n.endswith("q_norm.weight") or n.endswith("k_norm.weight"):
+            t[n] = (t[n].float() * 4.0).to(torch.bfloat16)
+    save_file(t, os.path.join(d, "model.safetensors"))
+    with open(os.path.join(d, "config.json"), "w") as f:
+        f.write(open(os.path.join(model_dirs["B"], "config.json")).read())
+    return d
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_each_request_alone_and_whole(model_dirs, plain, name, dtype):
+    eng = engine_for(model_dirs[name], dtype)
+    rng = np.random.default_rng(5)
+    V, P = plain[name].cfg["V"], plain[name].cfg["P"]
+    for n in [1, 2, 13, 64, 65, min(P, 200)]:
+        ids = random_ids(rng, V, n)
+        assert_close(replay_whole(eng, ids), plain[name].logits(ids).numpy(), dtype, f"{name} whole n={n}")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(model_dirs, plain, name, dtype):
+    eng = engine_for(model_dirs[name], dtype)
+    rng = np.random.default_rng(6)
+    for n in [33, 70, 100]:
+        ids = random_ids(rng, plain[name].cfg["V"], n)
+        ref = plain[name].logits(ids).numpy()
+        got = replay_tail_one_by_one(eng, ids, 32)
+        assert_close(got, ref, dtype, f"{name} tail n={n}")
+        assert_close(got, replay_whole(eng, ids), dtype, f"{name} tail vs whole n={n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C", "Bsharp"])
+def test_unequal_batches_one_after_another(model_dirs, sharp_dir, plain, name, dtype):
+    d = sharp_dir if name == "Bsharp" else model_dirs[name]
+    pm = PlainModel(d) if name == "Bsharp" else plain[name]
+    rng = np.random.default_rng(7)
+    lens = [40, 9, 75, 1, 66, 20, 5, 90, 33]
+    prompts = [31, 5, 64, 1, 60, 13, 1, 70, 2]
+    reqs = [random_ids(rng, pm.cfg["V"], n) for n in lens]
+    # few pages (64 tokens each): the second and third batch must reuse what the first gave back
+    eng = engine_for(d, dtype, max_tokens=64 * 5, max_slots=4)
+    got = replay_batches(eng, reqs, prompts, [[0, 1, 2, 3], [4, 5, 6], [7, 8]])
+    for i, ids in enumerate(reqs):
+        assert_close(got[i], pm.logits(ids).numpy(), dtype, f"{name} batched request {i} (len {lens[i]})")
+    assert eng.cache.slots.free_count == 4 and all(p.free_count == 5 for p in eng.cache.pools)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batch_composition_does_not_change_logits(model_dirs, dtype):
+    eng = engine_for(model_dirs["B"], dtype)
+    rng = np.random.default_rng(8)
+    reqs = [random_ids(rng, 384, n) for n in (50, 3, 17)]
+    alone = [replay_whole(eng, r) for r in reqs]
+    together = replay_batches(eng, reqs, [len(r) for r in reqs], [[0, 1, 2]])
+    # same kernels, same per-sequence arithmetic: only rounding may differ, and here not even that
+    for a, b in zip(alone, together):
+        assert np.abs(a - b).max() <= 1e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding(model_dirs, plain, name, dtype):
+    n = {"A": 128, "C": 300}[name]           # A: up to its position limit; C: several pages, past its window
+    eng = engine_for(model_dirs[name], dtype)
+    ids = random_ids(np.random.default_rng(9), plain[name].cfg["V"], n)
+    got = replay_tail_one_by_one(eng, ids, n - 3)
+    assert_close(got, plain[name].logits(ids).numpy(), dtype, f"{name} long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(model_dirs, plain, name, dtype):
+    eng = engine_for(model_dirs[name], dtype)
+    ids = random_ids(np.random.default_rng(10), plain[name].cfg["V"], 4)
+    ref = plain[name].logits(ids).numpy()
+    assert_close(replay_tail_one_by_one(eng, ids, 3), ref, dtype, f"{name} first tokens")
+    s = eng.alloc_slot()
+    first = to_np(eng.step([(s, ids[:1])], "last"))
+    assert_close(first, ref[:1], dtype, "the very first token")
+    assert eng.step([(s, ids[1:2])], None) is None            # nothing wanted: nothing returned
+    assert_close(to_np(eng.step([(s, ids[2:4])], [[1]])), ref[3:4], dtype, "after a silent step")
+    eng.free_slot(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_cut_into_pieces(model_dirs, plain, dtype):
+    eng = engine_for(model_dirs["C"], dtype)
+    ids = random_ids(np.random.default_rng(11), 300, 150)
+    s = eng.alloc_slot()
+    rows = []
+    for a, b in [(0, 7), (7, 64), (64, 65), (65, 140), (140, 150)]:
+        rows.append(to_np(eng.step([(s, ids[a:b])], "all")))
+    eng.free_slot(s)
+    assert_close(np.concatenate(rows, 0), plain["C"].logits(ids).numpy(), dtype, "prompt in pieces")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_truncate_and_refeed(model_dirs, plain, dtype):
+    eng = engine_for(model_dirs["A"], dtype)
+    ids = random_ids(np.random.default_rng(12), 256, 90)
+    s = eng.alloc_slot()
+    eng.step([(s, ids)], None)
+    eng.truncate(s, 70)
+    other = ids[:70] + random_ids(np.random.default_rng(13), 256, 20)
+    got = to_np(eng.step([(s, other[70:])], "all"))
+    eng.free_slot(s)
+    assert_close(got, plain["A"].logits(other).numpy()[70:], dtype, "after truncate")
+
+
+def test_requests_are_validated_before_anything_runs(model_dirs):
+    eng = engine_for(model_dirs["A"], "float32", max_tokens=128)
+    s = eng.alloc_slot()
+    with pytest.raises(hb.RequestError, match="outside the vocabulary"):
+        eng.step([(s, [1, 256])])
+    with pytest.raises(hb.RequestError, match="at least one token"):
+        eng.step([(s, [])])
+    with pytest.raises(hb.RequestError, match="at least one sequence"):
+        eng.step([])
+    with pytest.raises(hb.RequestError, match="wanted place"):
+        eng.step([(s, [1, 2])], [[2]])
+    with pytest.raises(hb.CacheError, match="twice in one step"):
+        eng.step([(s, [1]), (s, [2])])
+    with pytest.raises(hb.CacheError, match="exceed the limit of 128"):
+        eng.step([(s, [1] * 129)])
+    with pytest.raises(hb.CacheError, match="not held"):
+        eng.step([(3, [1])])
+    assert eng.length(s) == 0
+    eng.free_slot(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(model_dirs, plain, tmp_path, dtype):
+    """bin/trace_run as a user runs it: steps on standard input, logits in files."""
+    rng = np.random.default_rng(14)
+    a, b, c = (random_ids(rng, 256, n) for n in (40, 6, 70))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}, {"id": "b", "tokens": b[:5], "want": [4]}], "end": []}]
+    for k in range(10):
+        e = [{"id": "a", "tokens": [a[30 + k]], "want": [0]}]
+        if k == 0:
+            e.append({"id": "b", "tokens": [b[5]], "want": [0]})
+        steps.append({"step": k + 1, "entries": e, "end": ["b"] if k == 0 else (["a"] if k == 9 else [])})
+    steps.append({"step": 11, "entries": [{"id": "c", "tokens": c, "want": []}], "end": []})
+    steps.append({"step": 12, "entries": [{"id": "c", "tokens": [9], "want": [0]}], "end": ["c"]})
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["A"], "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    ra, rb = plain["A"].logits(a).numpy(), plain["A"].logits(b).numpy()
+    rc = plain["A"].logits(c + [9]).numpy()
+    g0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(3, 256)
+    assert_close(g0.astype(np.float64), np.stack([ra[0], ra[29], rb[4]]), dtype, "trace step 0")
+    g1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(2, 256)
+    assert_close(g1.astype(np.float64), np.stack([ra[30], rb[5]]), dtype, "trace step 1")
+    g10 = np.fromfile(out / "10.f32", dtype="<f4").reshape(1, 256)
+    assert_close(g10.astype(np.float64), ra[39:40], dtype, "trace step 10")
+    assert not (out / "11.f32").exists()
+    g12 = np.fromfile(out / "12.f32", dtype="<f4").reshape(1, 256)
+    assert_close(g12.astype(np.float64), rc[70:71], dtype, "trace step 12")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(model_dirs, plain, dtype):
+    eng = engine_for(model_dirs["B"], dtype)
+    rng = np.random.default_rng(15)
+    prompts = [random_ids(rng, 384, n) for n in (9, 1, 30, 4, 17)]
+    res = hb.generate(eng, prompts, hb.GenerationOptions(max_tokens=12, ignore_eos=True, max_batch=3),
+                      hb.SamplingParams(temperature=0.0))
+    assert res.stats.batches == 2 and all(len(t) == 12 for t in res.tokens)
+    margin = {"float32": 1e-4, "bfloat16": 4e-2}[dtype]
+    same = 0
+    for p, got in zip(prompts, res.tokens):
+        ids = list(p)
+        for tok in got:
+            ref = plain["B"].logits(ids)[-1].numpy()
+            assert ref.max() - ref[tok] <= margin       # the plain model's best token, or one tied with it within rounding
+            same += int(tok == int(ref.argmax()))
+            ids.append(tok)
+    if dtype == "float32":
+        assert same == 60
+    eng.cache.check()
+    assert eng.cache.slots.free_count == eng.cache.num_slots
+
+
+def test_sampled_generation_is_reproducible_and_batch_independent(model_dirs):
+    eng = engine_for(model_dirs["B"], "float32")
+    rng = np.random.default_rng(16)
+    prompts = [random_ids(rng, 384, n) for n in (1, 7, 16, 31)]
+    sp = hb.SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=1234)
+    opt = hb.GenerationOptions(max_tokens=12, ignore_eos=True)
+    a = hb.generate(eng, prompts, opt, sp).tokens
+    b = hb.generate(eng, prompts, opt, sp).tokens
+    assert a == b
+    one = hb.generate(eng, prompts, hb.GenerationOptions(max_tokens=12, ignore_eos=True, max_batch=1), sp).tokens
+    assert one == a
+    c = hb.generate(eng, prompts, opt, hb.SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=99)).tokens
+    assert c != a

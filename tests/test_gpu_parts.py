@@ -1,0 +1,286 @@
+"""Each part alone, and the generality of the layer list: a toy mixer with state of its own
+that is registered, built and stepped from here, a layer that runs twice, and a layer that
+reads another layer's cache, none of which changes a file of the library."""
+import json
+import os
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import herbert_rs_b200 as hb
+import plain_qwen3 as P
+from gpu_util import DTYPES, assert_close, engine_for, random_ids, replay_batches, replay_tail_one_by_one, replay_whole, to_np
+from herbert_rs_b200.cache import CacheNeed, SequenceCache, StateNeed
+from herbert_rs_b200.config import (AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec, ScheduleStep,
+                                    SwiGLUSpec)
+from herbert_rs_b200.engine.batch import StepBatch
+from herbert_rs_b200.parts import Mixer, ParamSpec
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+TD = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _bf(t):
+    return t.to(torch.bfloat16)
+
+
+def _batch(cache, rt, slots, lens):
+    """A step batch over `cache` for sequences that bring `lens` new tokens each."""
+    cache.reserve(list(zip(slots, lens)))
+    b = StepBatch(slots, [[0] * n for n in lens], [cache.lengths[s] for s in slots], [[] for _ in slots],
+                  cache.num_kv_groups, None, cache.page_size)
+    host = np.zeros(b.layout.total, dtype=np.int32)
+    b.fill_host(host, [cache.page_rows(g, slots, b.pages_width) for g in range(cache.num_kv_groups)])
+    b.bind(torch.from_numpy(host).cuda())
+    return b
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part_alone(dtype):
+    rt = hb.Runtime("cuda", TD[dtype])
+    part = hb.build_part("norm", NormSpec(200, 2e-5), rt=rt)
+    assert list(part.param_specs()) == ["weight"]
+    w = 1 + 0.1 * torch.randn(200)
+    part.load({"weight": w.cuda()})
+    x = torch.randn(6, 200) * 2
+    out = torch.empty(6, 200, device="cuda", dtype=TD[dtype])
+    part.forward(x.cuda(), out)
+    assert_close(to_np(out), P.rms_norm(x.double(), w.double(), 2e-5).numpy(), dtype, "norm part")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_position_part_alone(dtype):
+    rt = hb.Runtime("cuda", TD[dtype])
+    part = hb.build_part("position", PositionSpec(48, 24, 500000.0, 300), rt=rt)
+    cos, sin = P.rope_tables(24, 500000.0, 300, torch.float64)
+    assert part.cos.dtype == torch.float32 and part.cos.shape == (300, 12)      # angles stay 32-bit on both paths
+    assert (part.cos.cpu().double() - cos).abs().max() < 1e-5 and (part.sin.cpu().double() - sin).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 10])
+def test_attention_mixer_alone(dtype, window):
+    torch.manual_seed(0)
+    rt = hb.Runtime("cuda", TD[dtype], page_size=16)
+    H, nh, nkv, hd = 72, 6, 2, 32
+    spec = AttentionSpec(H, nh, nkv, hd, scale=0.2, qk_norm=NormSpec(hd, 1e-5),
+                         position=PositionSpec(hd, 16, 1e4, 128), window=window)
+    mixer = hb.build_part("mixer", spec, rt=rt)
+    w = {n: _bf(torch.randn(ps.shape) * (0.1 if ps.role == "matrix" else 0.0) + (1.0 if ps.role == "vector" else 0.0))
+         for n, ps in mixer.param_specs().items()}
+    w["q_norm.weight"] = _bf(1 + 0.2 * torch.randn(hd)); w["k_norm.weight"] = _bf(1 + 0.2 * torch.randn(hd))
+    mixer.load({n: (t.float() if mixer.param_specs()[n].role == "vector" else t.to(TD[dtype])).cuda() for n, t in w.items()})
+    need = mixer.cache_need()
+    assert need.kv.num_kv_heads == nkv and need.kv.head_dim == hd and need.kv.window == window and need.state is None
+    cache = SequenceCache([need], [None], 16, 4, page_size=16, dtype=TD[dtype], device="cuda")
+    lens = [37, 5]
+    hs = [_bf(torch.randn(n, H)) for n in lens]
+    cfg = dict(nh=nh, nkv=nkv, hd=hd, eps=1e-5, rot=16, scale=0.2)
+    cos, sin = P.rope_tables(16, 1e4, 64, torch.float64)
+    wd = {"x." + k: v.float() for k, v in w.items()}
+    ref = [P.attention_block(h.double(), wd, "x.", cfg, cos, sin, window) for h in hs]
+    slots = [cache.alloc_slot(), cache.alloc_slot()]
+    # prompts minus the last 4 tokens in one step, then 4 single-token steps
+    outs = [[], []]
+    fed = [n - 4 for n in lens]
+    for step in range(5):
+        ns = fed if step == 0 else [1, 1]
+        off = [0, 0] if step == 0 else [fed[0] + step - 1, fed[1] + step - 1]
+        rt.workspace.rewind()
+        b = _batch(cache, rt, slots, ns)
+        h = torch.cat([hs[i][off[i]:off[i] + ns[i]] for i in range(2)]).to(TD[dtype]).cuda()
+        res = torch.zeros(sum(ns), H, device="cuda")
+        mixer.forward(h, res, b, cache.view(0))
+        for s, n in zip(slots, ns):
+            cache.advance(s, n)
+        outs[0].append(to_np(res[:ns[0]])); outs[1].append(to_np(res[ns[0]:]))
+    for i in range(2):
+        assert_close(np.concatenate(outs[i]), ref[i].numpy(), dtype, f"attention mixer seq {i}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [64, 52])
+def test_feed_forward_part_alone(dtype, inter):
+    torch.manual_seed(1)
+    rt = hb.Runtime("cuda", TD[dtype])
+    ffn = hb.build_part("ffn", SwiGLUSpec(40, inter), rt=rt)
+    w = {n: _bf(torch.randn(ps.shape) * 0.2) for n, ps in ffn.param_specs().items()}
+    ffn.load({n: t.to(TD[dtype]).cuda() for n, t in w.items()})
+    h = _bf(torch.randn(9, 40))
+    res0 = torch.randn(9, 40)
+    res = res0.clone().cuda()
+    rt.workspace.rewind()
+    ffn.forward(h.to(TD[dtype]).cuda(), res, None)
+    ref = res0.double() + P.swiglu_mlp(h.double(), {"m." + k: v.float() for k, v in w.items()}, "m.")
+    assert_close(to_np(res), ref.numpy(), dtype, "feed-forward part")
+
+
+# ---- a toy mixer with state of its own, defined here ---------------------------------------------
+@dataclass(frozen=True)
+class EmaSpec:
+    hidden_size: int
+    decay: float
+    kind: str = "toy_ema"
+
+
+class EmaMixer(Mixer):
+    """s_t = decay * s_{t-1} + (1 - decay) * h_t per sequence; output s_t * w.  The state s is one
+    vector per sequence, kept in the cache's fixed-size region between steps."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+
+    def param_specs(self):
+        return {"mix.weight": ParamSpec((self.spec.hidden_size,), role="vector", init="ones_noise")}
+
+    def load(self, tensors):
+        self.w = tensors["mix.weight"]
+
+    def cache_need(self):
+        return CacheNeed(state=StateNeed((self.spec.hidden_size,)))
+
+    def forward(self, h, residual, batch, cache):
+        a = self.spec.decay
+        for b, slot in enumerate(batch.slots):
+            lo, hi = int(batch.seq_start_host[b]), int(batch.seq_start_host[b + 1])
+            s = cache.state[slot]
+            for t in range(lo, hi):
+                s.mul_(a).add_(h[t].float(), alpha=1 - a)
+                residual[t] += s * self.w
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    """Layers alternate: EMA mixer, attention, EMA mixer ...; read from its own config.json keys."""
+    vocab_size: int
+    hidden_size: int
+    num_hidden_layers: int
+    ema_decay: float
+    intermediate_size: int
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["vocab_size"], d["hidden_size"], d["num_hidden_layers"], d["ema_decay"], d["intermediate_size"])
+
+    def to_dict(self):
+        return dict(architectures=["ToyEmaForCausalLM"], **self.__dict__)
+
+    def model_spec(self):
+        H = self.hidden_size
+        norm = NormSpec(H, 1e-5)
+        att = AttentionSpec(H, 4, 2, 16, scale=0.25, qk_norm=NormSpec(16, 1e-5), position=PositionSpec(16, 16, 1e4, 256))
+        blocks = tuple(BlockSpec(mixer=EmaSpec(H, self.ema_decay) if i % 2 == 0 else att,
+                                 ffn=SwiGLUSpec(H, self.intermediate_size), norm1=norm, norm2=norm,
+                                 names=(("norm1", "input_layernorm"), ("mixer", "ema" if i % 2 == 0 else "self_attn"),
+                                        ("norm2", "post_attention_layernorm"), ("ffn", "mlp")))
+                       for i in range(self.num_hidden_layers))
+        return ModelSpec("ToyEmaForCausalLM", self.vocab_size, H, blocks,
+                         tuple(ScheduleStep(i) for i in range(self.num_hidden_layers)), norm, True, 256)
+
+
+def _toy_plain(w, cfg, ids):
+    x = P.embedding(w["model.embed_tokens.weight"], ids, torch.float64)
+    T = len(ids)
+    cos, sin = P.rope_tables(16, 1e4, T, torch.float64)
+    acfg = dict(nh=4, nkv=2, hd=16, eps=1e-5, rot=16, scale=0.25)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        n1 = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-5)
+        if i % 2 == 0:
+            s = torch.zeros(cfg["hidden_size"], dtype=torch.float64)
+            out = []
+            for t in range(T):
+                s = cfg["ema_decay"] * s + (1 - cfg["ema_decay"]) * n1[t]
+                out.append(s * w[p + "ema.mix.weight"].double())
+            x = x + torch.stack(out)
+        else:
+            x = x + P.attention_block(n1, w, p + "self_attn.", acfg, cos, sin, None)
+        n2 = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+        x = x + P.swiglu_mlp(n2, w, p + "mlp.")
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], 1e-5), w["model.embed_tokens.weight"]).numpy()
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    hb.register_part("mixer", "toy_ema", EmaMixer)
+    hb.register_architecture("ToyEmaForCausalLM", ToyConfig)
+    cfg = dict(architectures=["ToyEmaForCausalLM"], vocab_size=120, hidden_size=64, num_hidden_layers=3,
+               ema_decay=0.8, intermediate_size=96)
+    d = hb.write_random_model(cfg, str(tmp_path / "toy"), seed=4)
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    assert "model.layers.0.ema.mix.weight" in w and "model.layers.1.self_attn.q_proj.weight" in w
+    eng = engine_for(d, "float32", max_tokens=64 * 6, max_slots=3)
+    assert len(eng.cache.state_needs) == 1 and eng.cache.state[0].shape == (2, 3, 64)   # 2 EMA layers, 3 slots
+    assert eng.cache.num_kv_groups == 1 and eng.cache.kv[0].shape[0] == 1              # 1 attention layer
+    rng = np.random.default_rng(1)
+    reqs = [random_ids(rng, 120, n) for n in (30, 7, 45, 12, 20)]
+    for r in reqs[:2]:
+        ref = _toy_plain(w, cfg, r)
+        assert_close(replay_whole(eng, r), ref, "float32", "toy whole")
+        assert_close(replay_tail_one_by_one(eng, r, 5), ref, "float32", "toy one by one")     # state carried between steps
+    got = replay_batches(eng, reqs, [20, 7, 1, 3, 9], [[0, 1, 2], [3, 4]])                    # slots reused: state starts at zero
+    for g, r in zip(got, reqs):
+        assert_close(g, _toy_plain(w, cfg, r), "float32", "toy batched")
+    s = eng.alloc_slot()
+    eng.step([(s, [1, 2, 3])], None)
+    with pytest.raises(hb.CacheError, match="cannot be rolled back"):
+        eng.truncate(s, 1)
+    eng.free_slot(s)
+
+
+# ---- the order of layers is data -----------------------------------------------------------------
+@dataclass(frozen=True)
+class LoopedConfig(hb.Qwen3Config):
+    """Tiny B's layers run in the order 0, 1, 0, 2r: layer 0 twice (each run with its own cache
+    entry), and a last step that runs layer 2 but reads what step 1 (layer 1) stored."""
+
+    def model_spec(self):
+        s = super().model_spec()
+        sched = (ScheduleStep(0), ScheduleStep(1), ScheduleStep(0), ScheduleStep(2, reads_cache_of=1))
+        return ModelSpec("LoopedForCausalLM", s.vocab_size, s.hidden_size, s.blocks, sched, s.final_norm,
+                         s.tie_word_embeddings, s.max_position, s.stop_token_ids)
+
+
+def _looped_plain(w, cfg, ids):
+    T = len(ids)
+    cos, sin = P.rope_tables(cfg["rot"], cfg["theta"], T, torch.float64)
+    x = P.embedding(w["model.embed_tokens.weight"], ids, torch.float64)
+    x = P.decoder_layer(x, w, 0, cfg, cos, sin)
+    x_in1 = x
+    x = P.decoder_layer(x, w, 1, cfg, cos, sin)
+    x = P.decoder_layer(x, w, 0, cfg, cos, sin)
+    # step 3: layer 2's weights for q, o and the feed-forward; keys and values are those layer 1 stored
+    p1, p2 = "model.layers.1.", "model.layers.2."
+    nh, nkv, hd = cfg["nh"], cfg["nkv"], cfg["hd"]
+    n_in1 = P.rms_norm(x_in1, w[p1 + "input_layernorm.weight"], cfg["eps"])
+    k = P.apply_rope(P.rms_norm(P.linear(n_in1, w[p1 + "self_attn.k_proj.weight"]).view(T, nkv, hd),
+                                w[p1 + "self_attn.k_norm.weight"], cfg["eps"]), cos, sin, cfg["rot"])
+    v = P.linear(n_in1, w[p1 + "self_attn.v_proj.weight"]).view(T, nkv, hd)
+    n1 = P.rms_norm(x, w[p2 + "input_layernorm.weight"], cfg["eps"])
+    q = P.apply_rope(P.rms_norm(P.linear(n1, w[p2 + "self_attn.q_proj.weight"]).view(T, nh, hd),
+                                w[p2 + "self_attn.q_norm.weight"], cfg["eps"]), cos, sin, cfg["rot"])
+    o = P.attention_scores(q, k, v, cfg["scale"], None).reshape(T, nh * hd)
+    h = x + P.linear(o, w[p2 + "self_attn.o_proj.weight"])
+    x = h + P.swiglu_mlp(P.rms_norm(h, w[p2 + "post_attention_layernorm.weight"], cfg["eps"]), w, p2 + "mlp.")
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], cfg["eps"]), w["lm_head.weight"]).numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_layer_named_twice_and_a_layer_reading_anothers_cache(tmp_path, dtype):
+    hb.register_architecture("LoopedForCausalLM", LoopedConfig)
+    cfg = dict(TINY["B"]); cfg["architectures"] = ["LoopedForCausalLM"]
+    d = hb.write_random_model(cfg, str(tmp_path / "looped"), seed=8)
+    with open(os.path.join(d, "config.json")) as f:
+        c = json.load(f)
+    c["architectures"] = ["LoopedForCausalLM"]
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(c, f)
+    eng = engine_for(d, dtype)
+    assert eng.cache.kv[0].shape[0] == 3        # four steps, three cache entries: the reader has none
+    pm = P.PlainModel(d)
+    ids = random_ids(np.random.default_rng(2), 384, 80)
+    ref = _looped_plain(pm.w, pm.cfg, ids)
+    assert_close(replay_whole(eng, ids), ref, dtype, "looped whole")
+    assert_close(replay_tail_one_by_one(eng, ids, 32), ref, dtype, "looped one by one")
