@@ -1,0 +1,150 @@
+// Skinny matrix product for decoding: few activation rows against a whole weight matrix.
+//   C[M,N] (op)= A[M,K] * W[N,K]^T,  M <= 64, bfloat16 operands, float accumulation.
+//
+// A decode step reads every weight once and is bound by that stream, so the kernel is laid out
+// around the weight bytes (the reference's matvec has the same premise: one pass over W per
+// token, backends/backend_bf16_avx512/src/avx512_bf16_matvec.S:1-60).  The weight rows are the
+// M operand of the tensor-core instruction ("swapped" roles): one CTA owns 16 weight rows, its 8
+// warps share K, and every lane fetches 16 contiguous bytes of a weight row straight from global
+// memory into the registers mma.sync.m16n8k16 wants.  The k index inside one instruction is
+// permuted the same way for both operands (a lane's 8 consecutive elements serve k-slots
+// {2t,2t+1,2t+8,2t+9} of two instructions), which leaves the dot products unchanged.
+// The activation rows (at most 64 x K) come through L1/L2.  Partial sums of the 8 warps meet in
+// shared memory; the epilogue stores, adds into the float residual stream, or applies SwiGLU to
+// rows stored as 8 gate rows followed by the 8 up rows of the same channels.
+#include "api.h"
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_THREADS (SK_WARPS * 32)
+#define HB_EPI_SWIGLU 3
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float* d, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, int UNROLL, int EPI>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, void* Cv, int ldc,
+                   int M, int N, int K) {
+  __shared__ float red[SK_WARPS][16][NT * 8 + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  const int r_lo = row0 + g, r_hi = row0 + g + 8;
+  const bf16* w_lo = W + (size_t)(r_lo < N ? r_lo : 0) * ldw;
+  const bf16* w_hi = W + (size_t)(r_hi < N ? r_hi : 0) * ldw;
+  const bool lo_ok = r_lo < N, hi_ok = r_hi < N;
+
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+  const int ksteps = (K + 31) >> 5;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int ks0 = warp; ks0 < ksteps; ks0 += SK_WARPS * UNROLL) {
+    uint4 wa[UNROLL], wb[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (ks0 + u * SK_WARPS) * 32 + 8 * t;
+      const bool ok = k < K;  // K is a multiple of 8: a lane's 8 elements are all inside or all outside
+      wa[u] = (ok && lo_ok) ? ld_stream16(w_lo + k) : zero;
+      wb[u] = (ok && hi_ok) ? ld_stream16(w_hi + k) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (ks0 + u * SK_WARPS) * 32 + 8 * t;
+      const bool ok = k < K;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int m = nt * 8 + g;
+        uint4 x = zero;
+        if (ok && m < M) x = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k));
+        mma_bf16_16816(acc[nt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, x.x, x.y);
+        mma_bf16_16816(acc[nt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, x.z, x.w);
+      }
+    }
+  }
+  // accumulator layout: acc[nt][0..1] = (weight row g,   tokens nt*8 + 2t, 2t+1); [2..3] = row g+8
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
+    red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+    red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
+    red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+  }
+  __syncthreads();
+  if (EPI == HB_EPI_SWIGLU) {
+    // 8 channels x (NT*8) tokens; output column = block * 8 + channel
+    for (int idx = threadIdx.x; idx < 8 * NT * 8; idx += SK_THREADS) {
+      const int ch = idx & 7, m = idx >> 3;
+      if (m >= M) continue;
+      float gate = 0.0f, up = 0.0f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) {
+        gate += red[w][ch][m];
+        up += red[w][ch + 8][m];
+      }
+      const int col = blockIdx.x * 8 + ch;
+      if (row0 + ch + 8 < N) ((bf16*)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += SK_THREADS) {
+      const int r = idx & 15, m = idx >> 4;
+      const int n = row0 + r;
+      if (m >= M || n >= N) continue;
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) s += red[w][r][m];
+      const size_t o = (size_t)m * ldc + n;
+      if (EPI == HB_EPI_STORE) ((bf16*)Cv)[o] = __float2bfloat16_rn(s);
+      else if (EPI == HB_EPI_STORE_F32) ((float*)Cv)[o] = s;
+      else ((float*)Cv)[o] += s;
+    }
+  }
+}
+
+template <int NT, int UNROLL>
+static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C, int ldc, int M, int N, int K,
+                         int epi, cudaStream_t s) {
+  const unsigned grid = (unsigned)ceil_div(N, 16);
+  switch (epi) {
+    case HB_EPI_STORE: gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE_F32: gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE_F32><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_RESIDUAL: gemm_skinny_kernel<NT, UNROLL, HB_EPI_RESIDUAL><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_SWIGLU: gemm_skinny_kernel<NT, UNROLL, HB_EPI_SWIGLU><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
+    default: HB_FAIL(2, "gemm_skinny: unknown epilogue %d", epi);
+  }
+  HB_CHECK_LAUNCH("gemm_skinny");
+  return 0;
+}
+
+// epi HB_EPI_SWIGLU: W holds 2I rows in groups of 16 (8 gate, 8 up); C is [M, I] bfloat16.
+extern "C" int hb_gemm_skinny_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
+                                   int K, int epi, void* stream) {
+  HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_skinny: sizes must be positive");
+  HB_REQUIRE(M <= 64, "gemm_skinny: at most 64 activation rows, got %d", M);
+  HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_skinny: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
+  HB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_skinny: operands must be 16-byte aligned");
+  HB_REQUIRE(epi != HB_EPI_SWIGLU || N % 16 == 0, "gemm_skinny: SwiGLU rows come in groups of 16, N=%d", N);
+  cudaStream_t s = (cudaStream_t)stream;
+  const bf16* a = (const bf16*)A;
+  const bf16* w = (const bf16*)W;
+  if (M <= 8) return skinny_launch<1, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+  if (M <= 16) return skinny_launch<2, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+  if (M <= 32) return skinny_launch<4, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+  return skinny_launch<8, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+}

@@ -17,7 +17,8 @@ from ..errors import BackendError
 from . import lib as _libmod
 
 F32, BF16 = 0, 1
-EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL = 0, 1, 2
+EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+SKINNY_MAX_ROWS = 64
 
 _SIGS = {
     "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -28,6 +29,7 @@ _SIGS = {
                               c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -153,6 +155,19 @@ def sample(logits, temperature, top_k, top_p, uniforms, out) -> None:
          int(top_k), float(top_p), uniforms.data_ptr(), out.data_ptr(), _stream())
 
 
+def gemm_skinny(a, w, c, epilogue=EPI_STORE) -> None:
+    """c (op)= a @ w.T for at most 64 rows of a (bfloat16), streaming w once; EPI_SWIGLU: w holds
+    gate/up rows in groups of 8 and c is [M, N/2]."""
+    _check(a, torch.bfloat16, "a"); _check(w, torch.bfloat16, "w"); _check(c, None, "c")
+    _run("hb_gemm_skinny_bf16", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
+         a.shape[0], w.shape[0], a.shape[1], epilogue, _stream())
+
+
+def _skinny_ok(a, w) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 # ---------------------------------------------------------------------------------------------
 def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE) -> None:
     """c (op)= a @ w.T with the kernel that fits dtype and sizes.
@@ -160,7 +175,21 @@ def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_
     a [M, K] and w [N, K] share a dtype (float32: the true 32-bit product on the CUDA cores;
     bfloat16: tensor-core kernels where their size rules hold, else the any-shape kernel).
     """
-    gemm_simt(a, w, c, epilogue)
+    if _skinny_ok(a, w):
+        gemm_skinny(a, w, c, epilogue)
+    else:
+        gemm_simt(a, w, c, epilogue)
+
+
+def gemm_swiglu(a: torch.Tensor, wgu: torch.Tensor, out: torch.Tensor, interleave: int, scratch) -> None:
+    """out = silu(gate) * up with [gate | up] = a @ wgu.T.  Fused into the product where a kernel can;
+    otherwise the product goes to `scratch(shape, dtype)` and the SwiGLU kernel follows."""
+    if interleave == 8 and _skinny_ok(a, wgu):
+        gemm_skinny(a, wgu, out, EPI_SWIGLU)
+        return
+    gu = scratch((a.shape[0], wgu.shape[0]), a.dtype)
+    gemm(a, wgu, gu)
+    swiglu(gu, out, interleave)
 
 
 def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, head_dim, page_size,

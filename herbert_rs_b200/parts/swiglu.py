@@ -51,10 +51,8 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, residual, batch):
         ws, T, inter = self.rt.workspace, h.shape[0], self.spec.intermediate_size
-        gu = ws.take((T, 2 * inter), h.dtype)
-        ops.gemm(h, self.wgu, gu)
         act = ws.take((T, inter), h.dtype)
-        ops.swiglu(gu, act, self.interleave)
+        ops.gemm_swiglu(h, self.wgu, act, self.interleave, ws.take)
         ops.gemm(act, self.wd, residual, ops.EPI_RESIDUAL)
 
 

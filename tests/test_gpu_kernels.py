@@ -267,3 +267,37 @@ def test_sample_refuses_bad_options():
         ops.attention_simt(x, 8, x, x, x, o, o, o, 1, 1, 272, 16, 1.0, None)
     with pytest.raises(BackendError, match="CUDA tensor"):
         ops.argmax(torch.zeros(1, 8), o)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("N,K", [(96, 64), (304, 96), (1000, 1024), (48, 4104), (16, 8)])
+def test_gemm_skinny_every_epilogue(M, N, K):
+    torch.manual_seed(8)
+    a, w = torch.randn(M, K).to(torch.bfloat16), (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny(dev(a), dev(w), c, ops.EPI_STORE)
+    close(c, ref, torch.bfloat16)
+    c32 = torch.empty(M, N, device="cuda")
+    ops.gemm_skinny(dev(a), dev(w), c32, ops.EPI_STORE_F32)
+    close(c32, ref, torch.float32)
+    res = torch.randn(M, N)
+    r = dev(res.clone())
+    ops.gemm_skinny(dev(a), dev(w), r, ops.EPI_RESIDUAL)
+    close(r, res.double() + ref, torch.float32)
+    if N % 16 == 0:
+        out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_skinny(dev(a), dev(w), out, ops.EPI_SWIGLU)
+        blocks = ref.view(M, N // 16, 2, 8)
+        gate, up = blocks[:, :, 0].reshape(M, -1), blocks[:, :, 1].reshape(M, -1)
+        close(out, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    a, w = dev(torch.zeros(65, 64, dtype=torch.bfloat16)), dev(torch.zeros(32, 64, dtype=torch.bfloat16))
+    c = torch.empty(65, 32, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(BackendError, match="at most 64"):
+        ops.gemm_skinny(a, w, c)
+    with pytest.raises(BackendError, match="multiples of 8"):
+        ops.gemm_skinny(a[:4, :60], w[:, :60], c[:4])
+    ops.gemm(a, w, c)        # the dispatcher takes another kernel instead
