@@ -141,50 +141,63 @@ def attention_scores(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     return out
 
 
+def _same(x):
+    return x
+
+
+def bf16_storage(x: torch.Tensor) -> torch.Tensor:
+    """Round to bfloat16 and back: what storing an activation in bfloat16 does to it."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
 def attention_block(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, cfg: dict, cos, sin,
-                    window: Optional[int]) -> torch.Tensor:
+                    window: Optional[int], store=_same) -> torch.Tensor:
     """Projections, per-head q/k norm before the rotation, rotation, attention, output projection
     (generic_attention/prefill/mod.rs:73-293; head norm generic_attention/mod.rs:62-76)."""
     T = h.shape[0]
     nh, nkv, hd = cfg["nh"], cfg["nkv"], cfg["hd"]
-    q = linear(h, w[prefix + "q_proj.weight"]).view(T, nh, hd)
-    k = linear(h, w[prefix + "k_proj.weight"]).view(T, nkv, hd)
-    v = linear(h, w[prefix + "v_proj.weight"]).view(T, nkv, hd)
+    q = store(linear(h, w[prefix + "q_proj.weight"])).view(T, nh, hd)
+    k = store(linear(h, w[prefix + "k_proj.weight"])).view(T, nkv, hd)
+    v = store(linear(h, w[prefix + "v_proj.weight"])).view(T, nkv, hd)
     q = rms_norm(q, w[prefix + "q_norm.weight"], cfg["eps"])
     k = rms_norm(k, w[prefix + "k_norm.weight"], cfg["eps"])
-    q = apply_rope(q, cos[:T], sin[:T], cfg["rot"])
-    k = apply_rope(k, cos[:T], sin[:T], cfg["rot"])
-    o = attention_scores(q, k, v, cfg["scale"], window).reshape(T, nh * hd)
+    q = store(apply_rope(q, cos[:T], sin[:T], cfg["rot"]))
+    k = store(apply_rope(k, cos[:T], sin[:T], cfg["rot"]))
+    o = store(attention_scores(q, k, v, cfg["scale"], window)).reshape(T, nh * hd)
     return linear(o, w[prefix + "o_proj.weight"])
 
 
-def swiglu_mlp(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str) -> torch.Tensor:
+def swiglu_mlp(h: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, store=_same) -> torch.Tensor:
     """f = (silu(h Wg^T) * (h Wu^T)) Wd^T with silu(x) = x/(1+exp(-x))
     (generic_mlp.rs:83-96; kernels.rs:677-687)."""
     g = linear(h, w[prefix + "gate_proj.weight"])
     u = linear(h, w[prefix + "up_proj.weight"])
-    return linear((g / (1.0 + torch.exp(-g))) * u, w[prefix + "down_proj.weight"])
+    return linear(store((g / (1.0 + torch.exp(-g))) * u), w[prefix + "down_proj.weight"])
 
 
-def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, cfg: dict, cos, sin) -> torch.Tensor:
+def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, cfg: dict, cos, sin, store=_same) -> torch.Tensor:
     """n1 = norm(x); h = x + attn(n1); n2 = norm(h); out = h + mlp(n2)
     (generic_layer.rs:1131-1328)."""
     p = f"model.layers.{i}."
-    n1 = rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
-    h = x + attention_block(n1, w, p + "self_attn.", cfg, cos, sin, cfg["windows"][i])
-    n2 = rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["eps"])
-    return h + swiglu_mlp(n2, w, p + "mlp.")
+    n1 = store(rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"]))
+    h = x + attention_block(n1, w, p + "self_attn.", cfg, cos, sin, cfg["windows"][i], store)
+    n2 = store(rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["eps"]))
+    return h + swiglu_mlp(n2, w, p + "mlp.", store)
 
 
-def logits_all_positions(w: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int], dtype=torch.float64) -> torch.Tensor:
+def logits_all_positions(w: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int], dtype=torch.float64,
+                         store=_same) -> torch.Tensor:
     """Logits at every position of one whole sequence: embed -> layers -> final norm -> head
-    (generic_model.rs:131-319; the head is the embedding table when tied, loader_common.rs:1851-1860)."""
+    (generic_model.rs:131-319; the head is the embedding table when tied, loader_common.rs:1851-1860).
+    `store` is applied wherever an engine would keep an activation between two kernels (norm
+    outputs, projections, rotated q/k, attention output, the gated product); with `bf16_storage`
+    the result shows how much of a bfloat16 engine's error is the storage format's own."""
     T = len(ids)
     cos, sin = rope_tables(cfg["rot"], cfg["theta"], T, dtype)
     x = embedding(w["model.embed_tokens.weight"], ids, dtype)
     for i in range(cfg["L"]):
-        x = decoder_layer(x, w, i, cfg, cos, sin)
-    n = rms_norm(x, w["model.norm.weight"], cfg["eps"])
+        x = decoder_layer(x, w, i, cfg, cos, sin, store)
+    n = store(rms_norm(x, w["model.norm.weight"], cfg["eps"]))
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return linear(n, head)
 
@@ -194,8 +207,8 @@ class PlainModel:
         self.cfg = read_config(f"{model_dir}/config.json")
         self.w = read_safetensors(f"{model_dir}/model.safetensors")
 
-    def logits(self, ids: Sequence[int], dtype=torch.float64) -> torch.Tensor:
-        return logits_all_positions(self.w, self.cfg, ids, dtype)
+    def logits(self, ids: Sequence[int], dtype=torch.float64, store=_same) -> torch.Tensor:
+        return logits_all_positions(self.w, self.cfg, ids, dtype, store)
 
     def greedy(self, prompt: Sequence[int], n: int, dtype=torch.float64) -> List[int]:
         """n greedy tokens, recomputing the whole sequence each time; first maximum wins

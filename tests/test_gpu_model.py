@@ -9,8 +9,8 @@ import pytest
 import torch
 
 import herbert_rs_b200 as hb
-from gpu_util import (DTYPES, assert_close, engine_for, random_ids, replay_batches, replay_tail_one_by_one,
-                      replay_whole, to_np)
+from gpu_util import (DTYPES, TOL, assert_close, engine_for, random_ids, replay_batches, replay_tail_one_by_one,
+                      replay_whole, sensitivity_bound, to_np)
 from plain_qwen3 import PlainModel
 
 pytestmark = pytest.mark.gpu
@@ -77,7 +77,8 @@ def test_unequal_batches_one_after_another(model_dirs, sharp_dir, plain, name, d
     eng = engine_for(d, dtype, max_tokens=64 * 5, max_slots=4)
     got = replay_batches(eng, reqs, prompts, [[0, 1, 2, 3], [4, 5, 6], [7, 8]])
     for i, ids in enumerate(reqs):
-        assert_close(got[i], pm.logits(ids).numpy(), dtype, f"{name} batched request {i} (len {lens[i]})")
+        bound = sensitivity_bound(pm, ids, dtype) if name == "Bsharp" else None
+        assert_close(got[i], pm.logits(ids).numpy(), dtype, f"{name} batched request {i} (len {lens[i]})", bound)
     assert eng.cache.slots.free_count == 4 and all(p.free_count == 5 for p in eng.cache.pools)
 
 
@@ -88,9 +89,10 @@ def test_batch_composition_does_not_change_logits(model_dirs, dtype):
     reqs = [random_ids(rng, 384, n) for n in (50, 3, 17)]
     alone = [replay_whole(eng, r) for r in reqs]
     together = replay_batches(eng, reqs, [len(r) for r in reqs], [[0, 1, 2]])
-    # same kernels, same per-sequence arithmetic: only rounding may differ, and here not even that
+    # float32: one kernel for every size, the same sums per row.  bfloat16: a step of few rows and
+    # a step of many rows take different product kernels, so rounding (and only rounding) differs.
     for a, b in zip(alone, together):
-        assert np.abs(a - b).max() <= 1e-6
+        assert np.abs(a - b).max() <= (1e-6 if dtype == "float32" else TOL[dtype])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
