@@ -1,0 +1,331 @@
+// Decode attention over the paged cache: one new query per sequence, bfloat16, tensor cores.
+//
+// Work is split over (key range, kv head, sequence): a CTA takes a run of 64-key pages of one kv
+// head of one sequence and serves all query heads of that kv head's group at once, so a key or
+// value is read from memory once for the whole group (the reference pairs the heads of a group
+// against each key row the same way: backends/backend_common/src/avx512_attn_dot8_bf16.S, and
+// its Metal flash-decoding kernel splits the keys into tiles with partial (m, l, o) results:
+// backends/backend_metal attention_decode_flash_v2.metal).  Pages travel global -> shared with
+// cp.async in a ring of stages; each of the 4 warps owns 16 keys of every page:
+//   S = Q K^T  (mma.sync m16n8k16, query heads padded to 16 rows), s = dot * scale,
+//   online softmax in float (running m, l per head),  O += P V  (V through ldmatrix.trans).
+// Warps, then splits, are merged with the usual rescaling; every split writes (m, l, O) to
+// scratch memory and a second kernel combines them:  out = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s.
+// Keys visible to the query at position p: lo..p, lo = max(0, p - window + 1) if window > 0.
+#include "api.h"
+#include "common.cuh"
+
+#define AD_WARPS 4
+#define AD_THREADS (AD_WARPS * 32)
+#define AD_TILE 64
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float* d, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+struct DecodeArgs {
+  const bf16* q;       // [B, ldq]: row b holds the query heads of sequence b's new token
+  int ldq;
+  const bf16* kcache;  // [pages][nkv][page_size][hd]
+  const bf16* vcache;
+  const int* seq_len;  // length after this step (the new token's key is already stored)
+  const int* seq_pages;
+  int pages_stride;
+  float* part_o;       // [B][nh][nsplit][hd]
+  float* part_ml;      // [B][nh][nsplit][2]
+  int nh, nkv, hd, page_size, nsplit;
+  float scale;
+  int window;
+  int stages;
+};
+
+// HDM: the largest head size this instantiation holds in registers (hd <= HDM, hd % 16 == 0).
+template <int HDM>
+__global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs a) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int hd = a.hd, G = a.nh / a.nkv;
+  const int row_bytes = hd * 2 + 16;                 // padded: conflict-free ldmatrix for any hd % 16 == 0
+  const int tile_bytes = AD_TILE * row_bytes;
+  const int chunks_per_row = hd >> 3;
+
+  const int len = a.seq_len[b];
+  const int p = len - 1;
+  const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+  const int tile_lo = lo / AD_TILE, tile_hi = (len + AD_TILE - 1) / AD_TILE;   // tiles [tile_lo, tile_hi)
+  const int ntiles = tile_hi - tile_lo;
+  const int per = (ntiles + a.nsplit - 1) / a.nsplit;
+  const int t0 = tile_lo + split * per;
+  const int t1 = min(tile_hi, t0 + per);
+  const int tiles_per_page = a.page_size / AD_TILE;
+  const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
+  const size_t head_elems = (size_t)a.page_size * hd;
+
+  auto issue = [&](int tile, int stage) {
+    const int page = pages[tile / tiles_per_page];
+    const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AD_TILE * hd;
+    const bf16* kg = a.kcache + off;
+    const bf16* vg = a.vcache + off;
+    unsigned char* ks = smem + (size_t)stage * 2 * tile_bytes;
+    unsigned char* vs = ks + tile_bytes;
+    const int total = AD_TILE * chunks_per_row;
+    for (int c = threadIdx.x; c < total; c += AD_THREADS) {
+      const int r = c / chunks_per_row, cc = c % chunks_per_row;
+      cp_async16(ks + r * row_bytes + cc * 16, kg + (size_t)r * hd + cc * 8);
+      cp_async16(vs + r * row_bytes + cc * 16, vg + (size_t)r * hd + cc * 8);
+    }
+  };
+
+  // query fragments: rows = heads of the group (g and g + 8), zero beyond G
+  unsigned qf[HDM / 16][4];
+  {
+    const bf16* qb = a.q + (size_t)b * a.ldq + (size_t)kvh * G * hd;
+#pragma unroll
+    for (int ks = 0; ks < HDM / 16; ++ks) {
+      qf[ks][0] = qf[ks][1] = qf[ks][2] = qf[ks][3] = 0u;
+      if (ks * 16 < hd) {
+        const int d = ks * 16 + 2 * t;
+        if (g < G) {
+          qf[ks][0] = *reinterpret_cast<const unsigned*>(qb + (size_t)g * hd + d);
+          qf[ks][2] = *reinterpret_cast<const unsigned*>(qb + (size_t)g * hd + d + 8);
+        }
+        if (g + 8 < G) {
+          qf[ks][1] = *reinterpret_cast<const unsigned*>(qb + (size_t)(g + 8) * hd + d);
+          qf[ks][3] = *reinterpret_cast<const unsigned*>(qb + (size_t)(g + 8) * hd + d + 8);
+        }
+      }
+    }
+  }
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};   // heads g and g + 8
+  float o[HDM / 8][4];
+#pragma unroll
+  for (int i = 0; i < HDM / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+  const int S = a.stages;
+  for (int i = 0; i < S - 1; ++i) {
+    if (t0 + i < t1) issue(t0 + i, i);
+    cp_async_commit();
+  }
+  for (int tile = t0; tile < t1; ++tile) {
+    const int it = tile - t0;
+    if (tile + S - 1 < t1) issue(tile + S - 1, (it + S - 1) % S);
+    cp_async_commit();
+    // groups committed so far: S - 1 + it + 1; the group of `tile` is done when at most S - 1 are pending
+    if (S == 2) cp_async_wait<1>(); else if (S == 3) cp_async_wait<2>(); else cp_async_wait<3>();
+    __syncthreads();
+    const unsigned char* ks = smem + (size_t)(it % S) * 2 * tile_bytes;
+    const unsigned char* vs = ks + tile_bytes;
+    const int key0 = tile * AD_TILE + warp * 16;
+    if (key0 <= p && key0 + 15 >= lo) {
+      // ---- S = Q K^T for this warp's 16 keys -------------------------------------------------
+      float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+#pragma unroll
+      for (int kk = 0; kk < HDM / 16; ++kk) {
+        if (kk * 16 < hd) {
+          const int mi = lane >> 3;
+          const int key = warp * 16 + (mi >> 1) * 8 + (lane & 7);
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4(b0, b1, b2, b3, ks + key * row_bytes + (kk * 16 + (mi & 1) * 8) * 2);
+          mma16816(s[0], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+          mma16816(s[1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+        }
+      }
+      // ---- mask, online softmax ---------------------------------------------------------------
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = key0 + nt * 8 + 2 * t + (j & 1);
+          const float v = (key <= p && key >= lo) ? s[nt][j] * a.scale : -INFINITY;
+          s[nt][j] = v;
+          mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        corr[r] = (m_new == -INFINITY) ? 1.0f : expf(m[r] - m_new);
+        m[r] = m_new;
+      }
+      float ps[2] = {0.0f, 0.0f};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float pv = (s[nt][j] == -INFINITY) ? 0.0f : expf(s[nt][j] - m[j >> 1]);
+          s[nt][j] = pv;
+          ps[j >> 1] += pv;
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 1);
+        ps[r] += __shfl_xor_sync(0xffffffffu, ps[r], 2);
+        l[r] = l[r] * corr[r] + ps[r];
+      }
+      const unsigned pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
+      const unsigned pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
+      // ---- O = O * corr + P V -------------------------------------------------------------------
+#pragma unroll
+      for (int nd = 0; nd < HDM / 16; ++nd) {
+        if (nd * 16 < hd) {
+          o[2 * nd][0] *= corr[0]; o[2 * nd][1] *= corr[0]; o[2 * nd][2] *= corr[1]; o[2 * nd][3] *= corr[1];
+          o[2 * nd + 1][0] *= corr[0]; o[2 * nd + 1][1] *= corr[0]; o[2 * nd + 1][2] *= corr[1]; o[2 * nd + 1][3] *= corr[1];
+          const int mi = lane >> 3;
+          const int key = warp * 16 + (mi & 1) * 8 + (lane & 7);
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, vs + key * row_bytes + (nd * 16 + (mi >> 1) * 8) * 2);
+          mma16816(o[2 * nd], pa0, pa1, pa2, pa3, b0, b1);
+          mma16816(o[2 * nd + 1], pa0, pa1, pa2, pa3, b2, b3);
+        }
+      }
+    }
+    __syncthreads();   // every warp is done with this stage before it is refilled
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the 4 warps through shared memory ---------------------------------------------------
+  float* sm_m = reinterpret_cast<float*>(smem);            // [4][16]
+  float* sm_l = sm_m + AD_WARPS * 16;                      // [4][16]
+  float* sm_o = sm_l + AD_WARPS * 16;                      // [4][16][hd]
+  if (t == 0) {
+    sm_m[warp * 16 + g] = m[0]; sm_m[warp * 16 + g + 8] = m[1];
+    sm_l[warp * 16 + g] = l[0]; sm_l[warp * 16 + g + 8] = l[1];
+  }
+#pragma unroll
+  for (int nd = 0; nd < HDM / 8; ++nd) {
+    if (nd * 8 < hd) {
+      const int d = nd * 8 + 2 * t;
+      float* r0 = sm_o + ((size_t)warp * 16 + g) * hd + d;
+      float* r1 = sm_o + ((size_t)warp * 16 + g + 8) * hd + d;
+      r0[0] = o[nd][0]; r0[1] = o[nd][1];
+      r1[0] = o[nd][2]; r1[1] = o[nd][3];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * hd; idx += AD_THREADS) {
+    const int r = idx / hd, d = idx % hd;
+    if (r >= 16) break;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) mm = fmaxf(mm, sm_m[w * 16 + r]);
+    float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) {
+      const float mw = sm_m[w * 16 + r];
+      const float f = (mw == -INFINITY) ? 0.0f : expf(mw - mm);
+      acc += f * sm_o[((size_t)w * 16 + r) * hd + d];
+      ll += f * sm_l[w * 16 + r];
+    }
+    const int h = kvh * G + r;
+    const size_t pi = ((size_t)b * a.nh + h) * a.nsplit + split;
+    a.part_o[pi * hd + d] = acc;
+    if (d == 0) {
+      a.part_ml[pi * 2] = mm;
+      a.part_ml[pi * 2 + 1] = ll;
+    }
+  }
+}
+
+// out[b][h][:] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s
+__global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const size_t base = ((size_t)b * nh + h) * nsplit;
+  float mm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+  float ll = 0.0f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = part_ml[(base + s) * 2];
+    if (ms != -INFINITY) ll += expf(ms - mm) * part_ml[(base + s) * 2 + 1];
+  }
+  const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = part_ml[(base + s) * 2];
+      if (ms != -INFINITY) acc += expf(ms - mm) * part_o[(base + s) * hd + d];
+    }
+    out[(size_t)b * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+static int decode_smem_bytes(int hd, int stages) {
+  const int pipeline = stages * 2 * AD_TILE * (hd * 2 + 16);
+  const int merge = (2 * AD_WARPS * 16 + AD_WARPS * 16 * hd) * 4;
+  return pipeline > merge ? pipeline : merge;
+}
+
+extern "C" long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int hd, int nsplit) {
+  return (long long)n_seqs * nh * nsplit * (hd + 2);
+}
+
+// scratch: hb_attention_decode_scratch_floats(...) floats; the kernel writes every element it later reads.
+extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int ldo, const void* kcache,
+                                        const void* vcache, const int* seq_len, const int* seq_pages,
+                                        int pages_stride, float* scratch, int n_seqs, int nh, int nkv, int hd,
+                                        int page_size, int nsplit, float scale, int window, void* stream) {
+  HB_REQUIRE(n_seqs > 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: sizes must be positive");
+  HB_REQUIRE(nh % nkv == 0, "attention_decode: %d query heads are not a multiple of %d key/value heads", nh, nkv);
+  HB_REQUIRE(nh / nkv <= 16, "attention_decode: at most 16 query heads per key/value head, got %d", nh / nkv);
+  HB_REQUIRE(hd % 16 == 0 && hd <= 256, "attention_decode: head size %d must be a multiple of 16, at most 256", hd);
+  HB_REQUIRE(page_size % AD_TILE == 0, "attention_decode: page size %d must be a multiple of %d", page_size, AD_TILE);
+  HB_REQUIRE(nsplit >= 1 && nsplit <= 65535 && n_seqs <= 65535 && nkv <= 65535, "attention_decode: grid too large");
+  HB_REQUIRE(ldq % 2 == 0 && ((uintptr_t)q & 3) == 0, "attention_decode: queries must be 4-byte aligned");
+  HB_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "attention_decode: cache must be 16-byte aligned");
+  HB_REQUIRE(window >= 0, "attention_decode: window must be >= 0");
+  cudaStream_t s = (cudaStream_t)stream;
+  int stages = 3;
+  if (decode_smem_bytes(hd, stages) > 110 * 1024) stages = 2;
+  const int smem = decode_smem_bytes(hd, stages);
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)n_seqs * nh * nsplit * hd;
+  DecodeArgs a{(const bf16*)q, ldq, (const bf16*)kcache, (const bf16*)vcache, seq_len, seq_pages, pages_stride,
+               part_o, part_ml, nh, nkv, hd, page_size, nsplit, scale, window, stages};
+  dim3 grid(nsplit, nkv, n_seqs);
+  cudaError_t e;
+  if (hd <= 64) {
+    e = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    attention_decode_kernel<64><<<grid, AD_THREADS, smem, s>>>(a);
+  } else if (hd <= 128) {
+    e = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    attention_decode_kernel<128><<<grid, AD_THREADS, smem, s>>>(a);
+  } else {
+    e = cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    attention_decode_kernel<256><<<grid, AD_THREADS, smem, s>>>(a);
+  }
+  HB_CHECK_LAUNCH("attention_decode");
+  dim3 cgrid(nh, n_seqs);
+  attention_decode_combine_kernel<<<cgrid, hd >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
+  HB_CHECK_LAUNCH("attention_decode_combine");
+  return 0;
+}

@@ -24,14 +24,14 @@ from ..cache import SequenceCache
 from ..errors import BackendError, RequestError
 from ..sampling import SamplingParams, device_choose
 from .batch import StepBatch
-from .runtime import Runtime
+from .runtime import Runtime, Workspace
 
 Want = Union[str, Sequence[Sequence[int]], None]
 
 
 class Engine:
     def __init__(self, model, max_tokens: int, max_slots: Optional[int] = None,
-                 max_seq_len: Optional[int] = None):
+                 max_seq_len: Optional[int] = None, use_graphs: bool = True):
         if not torch.cuda.is_available() or model.rt.device.type != "cuda":
             raise BackendError("the engine runs on a CUDA device only: there is no CPU path")
         self.model = model
@@ -48,6 +48,15 @@ class Engine:
         self._tok_host = torch.empty(max(num_slots, 1), dtype=torch.int32).pin_memory()
         self._copied = torch.cuda.Event()
         self._copied.record()
+        # Decode steps (one token per sequence) are launch-bound: each shape of such a step is
+        # captured once as a CUDA graph and replayed; lengths, pages and tokens are read from the
+        # step buffer on the device, so one graph serves every later step of that shape.
+        self.use_graphs = use_graphs and model.graph_safe
+        self._graphs: dict = {}
+        self._graph_ws = Workspace(self.rt.device)
+        self._eager_ws = self.rt.workspace
+        self.graph_replays = 0
+        self.launches_last = 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
 
@@ -55,10 +64,10 @@ class Engine:
     @classmethod
     def from_folder(cls, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", max_tokens: int = 4096,
                     max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device="cuda",
-                    page_size: int = 64) -> "Engine":
+                    page_size: int = 64, use_graphs: bool = True) -> "Engine":
         from ..weights import load_model
         model = load_model(model_dir, device=device, dtype=_dtype(dtype), page_size=page_size)
-        return cls(model, max_tokens, max_slots, max_seq_len)
+        return cls(model, max_tokens, max_slots, max_seq_len, use_graphs)
 
     @property
     def vocab_size(self) -> int:
@@ -114,12 +123,17 @@ class Engine:
                     raise RequestError(f"a wanted place is outside the {len(t)} tokens its sequence brings")
         self.cache.reserve([(s, len(t)) for s, t in zip(slots, tokens)])
         pos0 = [self.cache.lengths[s] for s in slots]
+        if pages_width is None and self.use_graphs and all(len(t) == 1 for t in tokens):
+            # a few widths only, so that a captured decode step is reused while sequences grow
+            need = -(-(max(pos0) + 1) // self.rt.page_size)
+            pages_width = min(max(4, 1 << (need - 1).bit_length()), max(self.cache.max_pages_per_seq, need))
         batch = StepBatch(slots, tokens, pos0, want_l, self.cache.num_kv_groups, pages_width, self.rt.page_size)
         n = batch.layout.total
         if n > self._host.numel():
             size = 1 << (n - 1).bit_length()
             self._host = torch.empty(size, dtype=torch.int32).pin_memory()
             self._dev = torch.empty(size, dtype=torch.int32, device=self.rt.device)
+            self._graphs.clear()       # captured steps point into the old buffer
         rows = [self.cache.page_rows(g, slots, batch.pages_width) for g in range(self.cache.num_kv_groups)]
         self._copied.synchronize()  # the previous step's transfer has read the pinned buffer
         batch.fill_host(self._host.numpy(), rows, uniforms)
@@ -128,6 +142,38 @@ class Engine:
         self.h2d_bytes_last = n * 4
         batch.bind(self._dev)
         return batch
+
+    def _forward(self, batch: StepBatch):
+        """Logits of the step: eagerly, or by replaying the captured graph of this step's shape."""
+        if not (self.use_graphs and batch.is_decode):
+            self.rt.workspace = self._eager_ws
+            return self.model.forward(batch, self.cache)
+        key = (batch.n_seqs, batch.n_want, batch.pages_width)
+        hit = self._graphs.get(key)
+        if hit is not None:
+            graph, logits = hit
+            graph.replay()
+            self.graph_replays += 1
+            return logits
+        self.rt.workspace = self._graph_ws
+        try:
+            self._graph_ws.frozen = False
+            logits = self.model.forward(batch, self.cache)      # the real step; also sizes the arena
+            self._graph_ws.rewind()                             # grows the arena if the step overflowed it
+            if self._graph_ws._overflow_seen:
+                self._graphs.clear()                            # older graphs point into the old arena
+                self._graph_ws._overflow_seen = False
+            self._graph_ws.frozen = True
+            if len(self._graphs) >= 64:
+                self._graphs.pop(next(iter(self._graphs)))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):                       # records only; nothing runs
+                captured = self.model.forward(batch, self.cache)
+            self._graphs[key] = (graph, captured)
+            return logits                                       # keeps its own storage alive
+        finally:
+            self._graph_ws.frozen = False
+            self.rt.workspace = self._eager_ws
 
     def _finish(self, batch: StepBatch) -> None:
         for s, n in zip(batch.slots, batch.q_lens):
@@ -138,7 +184,7 @@ class Engine:
         of the entries and of their wanted places.  The tensor is the engine's own buffer: it is
         overwritten by the next step, so copy what must last."""
         batch = self._prepare(entries, want)
-        logits = self.model.forward(batch, self.cache)
+        logits = self._forward(batch)
         self._finish(batch)
         return logits
 
@@ -149,7 +195,7 @@ class Engine:
         B = len(entries)
         u = None if uniforms is None else np.asarray(uniforms, dtype=np.float32)
         batch = self._prepare(entries, "last", u)
-        logits = self.model.forward(batch, self.cache)
+        logits = self._forward(batch)
         self._finish(batch)
         out = self._tok_out[:B]
         device_choose(logits, params, batch.uniforms, out)

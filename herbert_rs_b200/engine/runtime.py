@@ -21,11 +21,13 @@ class Workspace:
         self.offset = 0
         self.frozen = False
         self._overflow: list = []
+        self._overflow_seen = False     # the buffer was replaced since this flag was last cleared
         self._wanted = 0
 
     def rewind(self) -> None:
         if self._wanted > self.buf.numel() and not self.frozen:
             self.buf = torch.empty(int(self._wanted * 1.25) + 4096, dtype=torch.uint8, device=self.device)
+            self._overflow_seen = True
         self.offset = 0
         self._wanted = 0
         self._overflow.clear()

@@ -78,6 +78,10 @@ class DecoderModel:
         n += rows * self.spec.hidden_size * self.embed.element_size()
         return n
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+
     # -- cache -----------------------------------------------------------------------------
     def cache_needs(self) -> List:
         return [self.blocks[st.layer].cache_need() for st in self.spec.schedule]

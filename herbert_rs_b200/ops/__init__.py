@@ -32,6 +32,8 @@ _SIGS = {
     "hb_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
 }
@@ -192,8 +194,48 @@ def gemm_swiglu(a: torch.Tensor, wgu: torch.Tensor, out: torch.Tensor, interleav
     swiglu(gu, out, interleave)
 
 
+DECODE_TARGET_CTAS = 592   # about two waves of two resident CTAs on each of the 148 SMs
+
+
+def attention_decode_scratch_floats(n_seqs, num_heads, head_dim, nsplit) -> int:
+    return n_seqs * num_heads * nsplit * (head_dim + 2)
+
+
+def decode_splits(n_seqs: int, num_kv_heads: int, max_tiles: int) -> int:
+    """How many key ranges each (sequence, kv head) is cut into, so that the grid fills the GPU."""
+    want = -(-DECODE_TARGET_CTAS // max(1, n_seqs * num_kv_heads))
+    return max(1, min(want, max_tiles, 64))
+
+
+def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch, num_heads, num_kv_heads,
+                     head_dim, page_size, nsplit, scale, window) -> None:
+    """One query per sequence (row b of q) over the cache; scratch holds the splits' partial results."""
+    _check(out, torch.bfloat16, "out"); _check(scratch, torch.float32, "scratch")
+    n = out.shape[0]
+    if scratch.numel() < attention_decode_scratch_floats(n, num_heads, head_dim, nsplit):
+        raise BackendError("attention_decode: scratch is too small")
+    _run("hb_attention_decode_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
+         v_cache.data_ptr(), seq_len.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0), scratch.data_ptr(),
+         n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0), _stream())
+
+
+def _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size) -> bool:
+    return (out.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
+            and num_heads // num_kv_heads <= 16 and page_size % 64 == 0)
+
+
 def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, head_dim, page_size,
-              scale, window, seq_pages) -> None:
-    """Attention of every token of the step over its sequence's cached keys and values."""
+              scale, window, seq_pages, scratch=None) -> None:
+    """Attention of every token of the step over its sequence's cached keys and values.
+
+    bfloat16 steps of one token per sequence take the split-key tensor-core kernel; everything
+    else takes the any-shape kernel (which is also the float32 path)."""
+    if batch.is_decode and scratch is not None and _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size):
+        tiles = seq_pages.shape[1] * (page_size // 64)
+        nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)
+        buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
+        attention_decode(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
+                         head_dim, page_size, nsplit, scale, window)
+        return
     attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
                    num_kv_heads, head_dim, page_size, scale, window)

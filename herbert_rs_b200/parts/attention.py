@@ -69,7 +69,7 @@ class AttentionMixer(Mixer):
             cache.k, cache.v, self.nh, self.nkv, self.hd, cache.page_size, write_cache=cache.writes_kv)
         att = ws.take((T, self.q_dim), h.dtype)
         ops.attention(qkv, qkv.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd,
-                      cache.page_size, self.spec.scale, self.spec.window, pages)
+                      cache.page_size, self.spec.scale, self.spec.window, pages, scratch=ws.take)
         ops.gemm(att, self.wo, residual, ops.EPI_RESIDUAL)
 
 

@@ -40,6 +40,12 @@ class ParamSpec:
 
 
 class Part:
+    # True if forward() takes every per-step fact (tokens, positions, lengths, pages, slots) from
+    # the batch's device arrays, so that a recorded CUDA graph of a step can be replayed for later
+    # steps.  A part that branches on the batch's host-side values must say False; the engine
+    # then runs the model's decode steps eagerly.
+    graph_safe = True
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}
 

@@ -16,6 +16,10 @@ class PreNormBlock(Block):
         self.ffn = build_part("ffn", spec.ffn, rt=rt)
         self._names = dict(spec.names)
 
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for _, p in self.children())
+
     def children(self):
         return (("norm1", self.norm1), ("mixer", self.mixer), ("norm2", self.norm2), ("ffn", self.ffn))
 

@@ -302,3 +302,45 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
     with pytest.raises(BackendError, match="multiples of 8"):
         ops.gemm_skinny(a[:4, :60], w[:, :60], c[:4])
     ops.gemm(a, w, c)        # the dispatcher takes another kernel instead
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 3, 48), (32, 8, 128), (5, 5, 80), (16, 1, 64), (2, 1, 256), (12, 4, 112)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("nsplit", [1, 3, 8])
+def test_attention_decode_kernel(nh, nkv, hd, window, nsplit):
+    lens = [1, 64, 65, 300, 129, 17]
+    c = _attention_case(torch.bfloat16, nh, nkv, hd, lens, [1] * len(lens), window, page=64, seed=11)
+    out = torch.empty(c["q"].shape, device="cuda", dtype=torch.bfloat16)
+    scratch = torch.full((ops.attention_decode_scratch_floats(len(lens), nh, hd, nsplit),), float("nan"), device="cuda")
+    ops.attention_decode(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(torch.tensor(lens, dtype=torch.int32)),
+                         dev(c["table"]), scratch, nh, nkv, hd, 64, nsplit, c["scale"], window)
+    close(out, c["ref"], torch.bfloat16)
+
+
+def test_attention_decode_finds_a_far_key_and_the_windows_edge():
+    nh, nkv, hd = 8, 2, 128
+    lens = [1500, 700]
+    W = 200
+    for window, sharp, hit in [(None, [(0, 1499, 5, 3)], True), (None, [(1, 699, 2, 64)], True),
+                               (W, [(1, 699, 0, 699 - W + 1)], True), (W, [(1, 699, 0, 699 - W)], False)]:
+        c = _attention_case(torch.bfloat16, nh, nkv, hd, lens, [1, 1], window, page=64, sharp=sharp)
+        out = torch.empty(c["q"].shape, device="cuda", dtype=torch.bfloat16)
+        nsplit = 5
+        scratch = torch.empty(ops.attention_decode_scratch_floats(2, nh, hd, nsplit), device="cuda")
+        ops.attention_decode(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(torch.tensor(lens, dtype=torch.int32)),
+                             dev(c["table"]), scratch, nh, nkv, hd, 64, nsplit, c["scale"], window)
+        close(out, c["ref"], torch.bfloat16)
+        b, _, h, kpos = sharp[0]
+        target = c["vs"][b][kpos, h // (nh // nkv)]
+        assert (((out[b].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit
+
+
+def test_attention_decode_refuses_what_it_cannot_do():
+    z = dev(torch.zeros(1, 4096, dtype=torch.bfloat16)); i = dev(torch.zeros(4, dtype=torch.int32).view(1, 4))
+    sc = torch.empty(1 << 16, device="cuda")
+    with pytest.raises(BackendError, match="at most 16 query heads"):
+        ops.attention_decode(z, 4096, z, z, z, i, i, sc, 34, 2, 16, 64, 1, 1.0, None)
+    with pytest.raises(BackendError, match="multiple of 16"):
+        ops.attention_decode(z, 4096, z, z, z, i, i, sc, 4, 2, 24, 64, 1, 1.0, None)
+    with pytest.raises(BackendError, match="page size"):
+        ops.attention_decode(z, 4096, z, z, z, i, i, sc, 4, 2, 32, 16, 1, 1.0, None)

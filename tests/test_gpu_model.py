@@ -235,3 +235,19 @@ def test_sampled_generation_is_reproducible_and_batch_independent(model_dirs):
     assert one == a
     c = hb.generate(eng, prompts, opt, hb.SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=99)).tokens
     assert c != a
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_captured_decode_steps_equal_eager_ones(model_dirs, plain, dtype):
+    """Decode steps replay a captured graph; the logits must be those of the eager kernels."""
+    rng = np.random.default_rng(17)
+    reqs = [random_ids(rng, 300, n) for n in (150, 31, 290, 77)]
+    prompts = [20, 30, 3, 70]
+    eager = engine_for(model_dirs["C"], dtype, use_graphs=False)
+    graphed = engine_for(model_dirs["C"], dtype, use_graphs=True)
+    a = replay_batches(eager, reqs, prompts, [[0, 1, 2, 3]])
+    b = replay_batches(graphed, reqs, prompts, [[0, 1, 2, 3]])
+    assert eager.graph_replays == 0 and graphed.graph_replays > 200
+    for x, y, ids in zip(a, b, reqs):
+        assert np.abs(x - y).max() <= 1e-6          # same kernels, same arithmetic
+        assert_close(y, plain["C"].logits(ids).numpy(), dtype, "graphed decode")

@@ -130,6 +130,8 @@ class EmaMixer(Mixer):
     """s_t = decay * s_{t-1} + (1 - decay) * h_t per sequence; output s_t * w.  The state s is one
     vector per sequence, kept in the cache's fixed-size region between steps."""
 
+    graph_safe = False      # it loops over the batch's host-side lists, so its steps cannot be replayed
+
     def __init__(self, spec, rt):
         self.spec, self.rt = spec, rt
 
