@@ -30,6 +30,7 @@ _SIGS = {
                               c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_gemm_tcgen05_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -165,6 +166,39 @@ def gemm_skinny(a, w, c, epilogue=EPI_STORE) -> None:
          a.shape[0], w.shape[0], a.shape[1], epilogue, _stream())
 
 
+_error_flags: dict = {}
+
+
+def _error_flag(device) -> torch.Tensor:
+    """One int per device that kernels with bounded waits set when a wait runs out."""
+    key = str(device)
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def check_kernel_errors() -> None:
+    """Raise if a kernel gave up on a bounded wait since the last check (reads one int per device,
+    which waits for the device)."""
+    for key, flag in _error_flags.items():
+        code = int(flag.item())
+        if code != 0:
+            flag.zero_()
+            raise BackendError(f"a kernel on {key} gave up waiting on a barrier (code {code}); its output is not valid")
+
+
+def gemm_tcgen05(a, w, c, epilogue=EPI_STORE) -> None:
+    """c (op)= a @ w.T on tcgen05 tensor cores with TMA-fed tiles (bfloat16, K a multiple of 8)."""
+    _check(a, torch.bfloat16, "a"); _check(w, torch.bfloat16, "w"); _check(c, None, "c")
+    _run("hb_gemm_tcgen05_bf16", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
+         a.shape[0], w.shape[0], a.shape[1], epilogue, _error_flag(a.device).data_ptr(), _stream())
+
+
+def _tcgen05_ok(a, w) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def _skinny_ok(a, w) -> bool:
     return (a.dtype == torch.bfloat16 and a.shape[0] <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -179,6 +213,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_
     """
     if _skinny_ok(a, w):
         gemm_skinny(a, w, c, epilogue)
+    elif _tcgen05_ok(a, w):
+        gemm_tcgen05(a, w, c, epilogue)
     else:
         gemm_simt(a, w, c, epilogue)
 
@@ -188,6 +224,9 @@ def gemm_swiglu(a: torch.Tensor, wgu: torch.Tensor, out: torch.Tensor, interleav
     otherwise the product goes to `scratch(shape, dtype)` and the SwiGLU kernel follows."""
     if interleave == 8 and _skinny_ok(a, wgu):
         gemm_skinny(a, wgu, out, EPI_SWIGLU)
+        return
+    if interleave == 8 and _tcgen05_ok(a, wgu):
+        gemm_tcgen05(a, wgu, out, EPI_SWIGLU)
         return
     gu = scratch((a.shape[0], wgu.shape[0]), a.dtype)
     gemm(a, wgu, gu)

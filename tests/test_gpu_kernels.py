@@ -344,3 +344,39 @@ def test_attention_decode_refuses_what_it_cannot_do():
         ops.attention_decode(z, 4096, z, z, z, i, i, sc, 4, 2, 24, 64, 1, 1.0, None)
     with pytest.raises(BackendError, match="page size"):
         ops.attention_decode(z, 4096, z, z, z, i, i, sc, 4, 2, 32, 16, 1, 1.0, None)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (1, 8, 8), (65, 96, 96), (200, 304, 224), (300, 1000, 1024),
+                                   (257, 24, 4104), (2048, 512, 256), (130, 272, 72)])
+def test_gemm_tcgen05_every_epilogue(M, N, K):
+    torch.manual_seed(9)
+    a, w = torch.randn(M, K).to(torch.bfloat16), (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    c32 = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_tcgen05(dev(a), dev(w), c32, ops.EPI_STORE_F32)
+    ops.check_kernel_errors()
+    close(c32, ref, torch.float32)
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tcgen05(dev(a), dev(w), c, ops.EPI_STORE)
+    close(c, ref, torch.bfloat16)
+    res = torch.randn(M, N)
+    r = dev(res.clone())
+    ops.gemm_tcgen05(dev(a), dev(w), r, ops.EPI_RESIDUAL)
+    close(r, res.double() + ref, torch.float32)
+    if N % 16 == 0:
+        out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_tcgen05(dev(a), dev(w), out, ops.EPI_SWIGLU)
+        blocks = ref.view(M, N // 16, 2, 8)
+        gate, up = blocks[:, :, 0].reshape(M, -1), blocks[:, :, 1].reshape(M, -1)
+        close(out, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
+    # a tile of the output must not spill into its neighbours: guard columns stay as they were
+    wide = torch.full((M, N + 8), 7.0, device="cuda")
+    ops.gemm_tcgen05(dev(a), dev(w), wide[:, :N], ops.EPI_STORE_F32)
+    assert (wide[:, N:] == 7.0).all()
+    ops.check_kernel_errors()
+
+
+def test_gemm_tcgen05_refuses_rows_tma_cannot_address():
+    a, w = dev(torch.zeros(16, 60, dtype=torch.bfloat16)), dev(torch.zeros(32, 60, dtype=torch.bfloat16))
+    with pytest.raises(BackendError, match="multiples of 8"):
+        ops.gemm_tcgen05(a, w, torch.empty(16, 32, device="cuda", dtype=torch.bfloat16))
