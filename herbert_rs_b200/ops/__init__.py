@@ -35,6 +35,8 @@ _SIGS = {
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
 }
@@ -258,6 +260,20 @@ def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch,
          n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0), _stream())
 
 
+def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
+                      num_heads, num_kv_heads, head_dim, page_size, scale, window) -> None:
+    """Causal attention of packed query rows (seq_start marks the sequences) over the cache."""
+    _check(out, torch.bfloat16, "out")
+    _run("hb_attention_prefill_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
+         v_cache.data_ptr(), seq_start.data_ptr(), seq_pos0.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
+         int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window or 0),
+         _stream())
+
+
+def _prefill_kernel_ok(out, head_dim, page_size) -> bool:
+    return out.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and page_size % 64 == 0
+
+
 def _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size) -> bool:
     return (out.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
             and num_heads // num_kv_heads <= 16 and page_size % 64 == 0)
@@ -267,14 +283,19 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
               scale, window, seq_pages, scratch=None) -> None:
     """Attention of every token of the step over its sequence's cached keys and values.
 
-    bfloat16 steps of one token per sequence take the split-key tensor-core kernel; everything
-    else takes the any-shape kernel (which is also the float32 path)."""
+    bfloat16 steps of one token per sequence take the split-key tensor-core kernel, other bfloat16
+    steps the flash kernel; head sizes or pages those cannot serve, and the float32 path, take
+    the any-shape kernel."""
     if batch.is_decode and scratch is not None and _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size):
         tiles = seq_pages.shape[1] * (page_size // 64)
         nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)
         buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
         attention_decode(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
                          head_dim, page_size, nsplit, scale, window)
+        return
+    if _prefill_kernel_ok(out, head_dim, page_size):
+        attention_prefill(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
+                          batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window)
         return
     attention_simt(q, ldq, out, k_cache, v_cache, batch.tok_seq, batch.tok_pos, seq_pages, num_heads,
                    num_kv_heads, head_dim, page_size, scale, window)

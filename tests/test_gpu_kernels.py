@@ -380,3 +380,35 @@ def test_gemm_tcgen05_refuses_rows_tma_cannot_address():
     a, w = dev(torch.zeros(16, 60, dtype=torch.bfloat16)), dev(torch.zeros(32, 60, dtype=torch.bfloat16))
     with pytest.raises(BackendError, match="multiples of 8"):
         ops.gemm_tcgen05(a, w, torch.empty(16, 32, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 3, 48), (8, 2, 128), (5, 5, 80), (2, 1, 256), (3, 1, 112)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_prefill_kernel(nh, nkv, hd, window):
+    for lens, qlens in [([1, 70, 33, 200], [1, 70, 33, 200]), ([300, 130, 64], [100, 1, 64]), ([257], [129])]:
+        c = _attention_case(torch.bfloat16, nh, nkv, hd, lens, qlens, window, page=64, seed=12)
+        out = torch.full(c["q"].shape, float("nan"), device="cuda", dtype=torch.bfloat16)
+        starts = torch.tensor(np.concatenate([[0], np.cumsum(qlens)]), dtype=torch.int32)
+        pos0 = torch.tensor([n - q for n, q in zip(lens, qlens)], dtype=torch.int32)
+        ops.attention_prefill(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
+                              dev(c["table"]), len(lens), max(qlens), nh, nkv, hd, 64, c["scale"], window)
+        close(out, c["ref"], torch.bfloat16)
+
+
+def test_attention_prefill_finds_a_far_key_and_the_windows_edge():
+    nh, nkv, hd = 4, 2, 128
+    lens, qlens = [900, 500], [300, 500]
+    W = 150
+    for window, sharp, hit in [(None, [(0, 870, 3, 2)], True), (None, [(1, 499, 1, 448)], True),
+                               (W, [(1, 400, 0, 400 - W + 1)], True), (W, [(1, 400, 0, 400 - W)], False)]:
+        c = _attention_case(torch.bfloat16, nh, nkv, hd, lens, qlens, window, page=64, sharp=sharp)
+        out = torch.empty(c["q"].shape, device="cuda", dtype=torch.bfloat16)
+        starts = torch.tensor([0, 300, 800], dtype=torch.int32)
+        pos0 = torch.tensor([600, 0], dtype=torch.int32)
+        ops.attention_prefill(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
+                              dev(c["table"]), 2, 500, nh, nkv, hd, 64, c["scale"], window)
+        close(out, c["ref"], torch.bfloat16)
+        b, qpos, h, kpos = sharp[0]
+        row = (0 if b == 0 else 300) + qpos - int(pos0[b])
+        target = c["vs"][b][kpos, h // (nh // nkv)]
+        assert (((out[row].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit
