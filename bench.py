@@ -1,0 +1,273 @@
+#!/usr/bin/env python3
+"""Throughput of the engine at Qwen3-8B layer sizes with random weights, on one GPU.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--batch 8] [--layers L] [--prompt-len 2048] [--context 4096]
+
+A "step" is one decode step of a batch of sequences that were prefilled to --prompt-len tokens.
+`value` is decoded tokens per second of K steps timed on the device (CUDA events, after W warm-up
+steps); every step reads all weights (about 15 GB, far larger than the 126 MB L2), so no flush is
+needed between steps.  `e2e` is the same through the Python entry point with host tokens in and
+out of every step.  `prefill` times one 2,048-token prompt; `points` holds decode at batch 1 and
+64.  One JSON line goes to standard output.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096,
+                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=12288, rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960,
+                tie_word_embeddings=False, eos_token_id=151645)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append((time.time(), line.strip()))
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows) -> dict:
+        sm, mx, reasons = [], [], set()
+        for ts, line in self.rows:
+            if not any(a <= ts <= b for a, b in windows):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm() -> int:
+    # The reference is a Rust workspace (Cargo.toml, no setup.py / pyproject.toml): pip cannot
+    # install it, there is no Rust toolchain in this image, and its GPU backends need Vulkan or Metal.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "xigh/herbert-rs is a Rust workspace with Vulkan/Metal GPU backends: no Python package to install offline, no cargo/rustc in the image, no graphics stack on the box"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only (asked for {args.gpus}): this library has no multi-GPU path")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import numpy as np
+    import torch
+
+    import herbert_rs_b200 as hb
+    from herbert_rs_b200 import ops
+    from herbert_rs_b200.sampling import device_choose
+
+    pk = peaks()
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = args.layers
+    rt = hb.Runtime("cuda", torch.bfloat16)
+    model = hb.random_model(cfg, 0, rt)
+    max_b = args.batch if args.no_points else max(args.batch, 64)
+    engine = hb.Engine(model, max_tokens=max_b * args.context, max_slots=max_b, max_seq_len=args.context)
+    rng = np.random.default_rng(0)
+    V = cfg["vocab_size"]
+    greedy = hb.SamplingParams(temperature=0.0)
+    sampler = ClockSampler()
+    sampler.start()
+    windows = []
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def prefill_batch(B):
+        slots = [engine.alloc_slot() for _ in range(B)]
+        for s in slots:                      # one prompt per step keeps the workspace at prefill size
+            engine.step([(s, rng.integers(0, V, args.prompt_len).tolist())], None)
+        return slots
+
+    def decode_device(B, steps, warmup):
+        """K decode steps timed on the device: step buffer upload, graph replay, argmax."""
+        slots = prefill_batch(B)
+        toks = rng.integers(0, V, (steps + warmup, B)).tolist()
+        out = torch.empty(B, dtype=torch.int32, device="cuda")
+        def one(i):
+            batch = engine._prepare([(s, [toks[i][j]]) for j, s in enumerate(slots)], "last")
+            logits = engine._forward(batch)
+            engine._finish(batch)
+            device_choose(logits, greedy, batch.uniforms, out)
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        lens = [engine.length(s) for s in slots]
+        e0, e1 = events()
+        t0 = time.time()
+        e0.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        e1.record()
+        torch.cuda.synchronize()
+        windows.append((t0, time.time()))
+        ms = e0.elapsed_time(e1)
+        ops.check_kernel_errors()
+        for s in slots:
+            engine.free_slot(s)
+        mean_len = sum(lens) / B + (steps + 1) / 2.0
+        return ms / steps, mean_len
+
+    def decode_e2e(B, steps, warmup):
+        """The same through the public call: host token ids in, host token ids out, every step."""
+        slots = prefill_batch(B)
+        last = rng.integers(0, V, B).tolist()
+        for _ in range(warmup):
+            last = engine.step_and_choose([(s, [t]) for s, t in zip(slots, last)], greedy)
+        torch.cuda.synchronize()
+        t0 = time.time()
+        for _ in range(steps):
+            last = engine.step_and_choose([(s, [t]) for s, t in zip(slots, last)], greedy)
+        dt = time.time() - t0
+        windows.append((t0, t0 + dt))
+        h2d, d2h = engine.h2d_bytes_last, engine.d2h_bytes_last
+        for s in slots:
+            engine.free_slot(s)
+        return dt / steps, h2d, d2h
+
+    result = {}
+    # ---- prefill of one prompt -------------------------------------------------------------------
+    if not args.no_prefill:
+        T = args.prompt_len
+        times = []
+        for i in range(3 + 3):
+            s = engine.alloc_slot()
+            ids = rng.integers(0, V, T).tolist()
+            batch = engine._prepare([(s, ids)], "last")
+            e0, e1 = events()
+            t0 = time.time()
+            e0.record()
+            engine._forward(batch)
+            e1.record()
+            torch.cuda.synchronize()
+            engine._finish(batch)
+            engine.free_slot(s)
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+                windows.append((t0, time.time()))
+        ms = statistics.median(times)
+        c = model.config
+        per_layer = 2 * T * (c.hidden_size * (c.q_dim + 2 * c.kv_dim) + c.q_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+        attn = 4 * c.num_attention_heads * c.head_dim * T * (T + 1) // 2
+        flops = args.layers * (per_layer + attn) + 2 * c.hidden_size * c.vocab_size
+        result["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+                             "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- the headline: decode at --batch -----------------------------------------------------------
+    B = args.batch
+    launches0 = ops.launch_count()
+    ms_step, mean_len = decode_device(B, args.steps, args.warmup)
+    kernels_per_step = engine.kernels_per_graph.get(B, 0) + 1       # + the argmax launch
+    value = B / (ms_step / 1e3)
+    step_bytes = model.weight_bytes(rows=B) + int(B * mean_len * engine.cache.bytes_per_token())
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    result["roofline"] = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                          "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
+    if not args.no_e2e:
+        s_step, h2d, d2h = decode_e2e(B, max(8, args.steps // 2), args.warmup)
+        result["e2e"] = {"value": round(B / s_step, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    if not args.no_points:
+        pts = {}
+        for b in (1, 64):
+            ms_b, _ = decode_device(b, max(8, args.steps // 2), args.warmup)
+            pts[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+        result["points"] = pts
+    sampler.stop()
+    clocks = sampler.summary(windows)
+
+    line = {
+        "metric": "Qwen3-8B decode tok/s at batch 1, 8, 64; prefill tok/s at 2,048 tokens",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random-init weights N(0, 0.02)",
+        "impl": "ours", "gpu_launches": kernels_per_step * args.steps,
+        "config": {"model": "Qwen3-8B layer sizes", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": B, "seq_len": args.prompt_len, "context": args.context, "parallelism": "single-gpu",
+                   "page_size": rt.page_size, "l2": "inputs larger than L2 (all weights read every step)",
+                   "cache_fill": "prefill of random prompts", "kernels_per_step": kernels_per_step},
+        "clocks": clocks,
+    }
+    line.update(result)
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -56,6 +56,7 @@ class Engine:
         self._graph_ws = Workspace(self.rt.device)
         self._eager_ws = self.rt.workspace
         self.graph_replays = 0
+        self.kernels_per_graph: dict = {}   # batch size -> kernels in its captured decode step
         self.launches_last = 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
@@ -167,8 +168,11 @@ class Engine:
             if len(self._graphs) >= 64:
                 self._graphs.pop(next(iter(self._graphs)))
             graph = torch.cuda.CUDAGraph()
+            from .. import ops as _ops
+            before = _ops.launch_count()
             with torch.cuda.graph(graph):                       # records only; nothing runs
                 captured = self.model.forward(batch, self.cache)
+            self.kernels_per_graph[batch.n_seqs] = _ops.launch_count() - before
             self._graphs[key] = (graph, captured)
             return logits                                       # keeps its own storage alive
         finally:

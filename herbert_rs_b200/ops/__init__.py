@@ -57,7 +57,19 @@ def _fn(name: str):
     return f
 
 
+# kernels each launcher starts (for honest launch counts)
+_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2}
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (launches recorded into a graph count once)."""
+    return _launches
+
+
 def _run(name: str, *args) -> None:
+    global _launches
+    _launches += _KERNELS_PER_CALL.get(name, 1)
     rc = _fn(name)(*args)
     if rc != 0:
         raise BackendError(f"{name}: {_libmod.last_error()}")
