@@ -40,6 +40,8 @@ struct DecodeArgs {
 template <int HDM>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
+  pdl_launch();
+  pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int hd = a.hd, G = a.nh / a.nkv;
@@ -232,6 +234,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
 // out[b][h][:] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit) {
+  pdl_launch();
+  pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y;
   const size_t base = ((size_t)b * nh + h) * nsplit;
   float mm = -INFINITY;
@@ -289,19 +293,19 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   if (hd <= 64) {
     e = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    attention_decode_kernel<64><<<grid, AD_THREADS, smem, s>>>(a);
+    hb_launch(attention_decode_kernel<64>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   } else if (hd <= 128) {
     e = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    attention_decode_kernel<128><<<grid, AD_THREADS, smem, s>>>(a);
+    hb_launch(attention_decode_kernel<128>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   } else {
     e = cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    attention_decode_kernel<256><<<grid, AD_THREADS, smem, s>>>(a);
+    hb_launch(attention_decode_kernel<256>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   }
   HB_CHECK_LAUNCH("attention_decode");
   dim3 cgrid(nh, n_seqs);
-  attention_decode_combine_kernel<<<cgrid, hd >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
+  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
   HB_CHECK_LAUNCH("attention_decode_combine");
   return 0;
 }

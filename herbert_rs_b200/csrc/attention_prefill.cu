@@ -41,6 +41,8 @@ struct PrefillArgs {
 template <int HDM>
 __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
+  pdl_launch();
+  pdl_wait();
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int row0 = a.seq_start[b], qlen = a.seq_start[b + 1] - row0;
   if (qt * AP_QTILE >= qlen) return;
@@ -252,15 +254,15 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
   if (hd <= 64) {
     e = cudaFuncSetAttribute(attention_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_prefill: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    attention_prefill_kernel<64><<<grid, AP_THREADS, smem, s>>>(a);
+    hb_launch(attention_prefill_kernel<64>, dim3(grid), dim3(AP_THREADS), smem, s, a);
   } else if (hd <= 128) {
     e = cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_prefill: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    attention_prefill_kernel<128><<<grid, AP_THREADS, smem, s>>>(a);
+    hb_launch(attention_prefill_kernel<128>, dim3(grid), dim3(AP_THREADS), smem, s, a);
   } else {
     e = cudaFuncSetAttribute(attention_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_prefill: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    attention_prefill_kernel<256><<<grid, AP_THREADS, smem, s>>>(a);
+    hb_launch(attention_prefill_kernel<256>, dim3(grid), dim3(AP_THREADS), smem, s, a);
   }
   HB_CHECK_LAUNCH("attention_prefill");
   return 0;

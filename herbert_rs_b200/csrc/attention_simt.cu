@@ -34,6 +34,8 @@ struct AttnArgs {
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs a) {
   __shared__ float qs[ATT_WARPS][ATT_MAX_HD];
+  pdl_launch();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * ATT_WARPS + warp;
   if (unit >= (long long)a.n_tokens * a.nh) return;
@@ -104,9 +106,9 @@ extern "C" int hb_attention_simt(int dtype, const void* q, int ldq, void* out, i
   const long long blocks = ceil_div_ll((long long)n_tokens * nh, ATT_WARPS);
   HB_REQUIRE(blocks < 2147483647LL, "attention: too many (token, head) pairs");
   if (dtype == HB_F32)
-    attention_simt_kernel<float><<<(unsigned)blocks, ATT_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+    hb_launch(attention_simt_kernel<float>, dim3((unsigned)blocks), dim3(ATT_WARPS * 32), 0, (cudaStream_t)stream, a);
   else
-    attention_simt_kernel<bf16><<<(unsigned)blocks, ATT_WARPS * 32, 0, (cudaStream_t)stream>>>(a);
+    hb_launch(attention_simt_kernel<bf16>, dim3((unsigned)blocks), dim3(ATT_WARPS * 32), 0, (cudaStream_t)stream, a);
   HB_CHECK_LAUNCH("attention_simt");
   return 0;
 }

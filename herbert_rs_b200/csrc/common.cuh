@@ -32,6 +32,31 @@ void hb_set_error(const char* fmt, ...);
     if (e__ != cudaSuccess) HB_FAIL(3, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// ---- launching ------------------------------------------------------------------------------
+// Every kernel is launched through hb_launch.  With programmatic dependent launch switched on
+// (hb_set_pdl(1); off by default) a kernel may be scheduled while its predecessor in the stream is
+// still draining; it must then call pdl_wait() before it reads anything the predecessor wrote or
+// writes anything the predecessor may still read.  pdl_launch() tells the hardware that the next
+// kernel may start its own prologue.  Both are no-ops for a kernel launched without the attribute.
+int hb_pdl_enabled(void);
+template <typename... KArgs, typename... Args>
+static inline cudaError_t hb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = hb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- conversions ---------------------------------------------------------------------------
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }

@@ -15,6 +15,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int hidden, int vocab) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * hidden;
@@ -31,7 +33,7 @@ static int embed_launch(const void* table, const int* ids, float* out, int n_tok
                         int vocab, void* stream) {
   HB_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: sizes must be positive");
   int threads = hidden >= 1024 ? 256 : 128;
-  embed_kernel<T><<<n_tokens, threads, 0, (cudaStream_t)stream>>>((const T*)table, ids, out, hidden, vocab);
+  hb_launch(embed_kernel<T>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (const T*)table, ids, out, hidden, vocab);
   HB_CHECK_LAUNCH("embed");
   return 0;
 }
@@ -48,6 +50,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                T* __restrict__ out, const int* __restrict__ rows, int dim, float eps) {
   __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
   float s = 0.0f;
@@ -66,9 +70,9 @@ extern "C" int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, 
   HB_REQUIRE(n_rows > 0 && dim > 0, "rmsnorm: sizes must be positive");
   int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   if (dtype == HB_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, w, (float*)out, rows, dim, eps);
+    hb_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x, w, (float*)out, rows, dim, eps);
   else
-    rmsnorm_kernel<bf16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(x, w, (bf16*)out, rows, dim, eps);
+    hb_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x, w, (bf16*)out, rows, dim, eps);
   HB_CHECK_LAUNCH("rmsnorm");
   return 0;
 }
@@ -79,6 +83,8 @@ extern "C" int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ldo,
                               int inter, int interleave) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= inter) return;
@@ -104,9 +110,9 @@ extern "C" int hb_swiglu(int dtype, const void* gu, int ld, void* out, int ldo, 
   HB_REQUIRE(n_tokens <= 65535, "swiglu: at most 65535 tokens per call, got %d", n_tokens);
   dim3 grid(ceil_div(inter, 256), n_tokens);
   if (dtype == HB_F32)
-    swiglu_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)gu, ld, (float*)out, ldo, inter, interleave);
+    hb_launch(swiglu_kernel<float>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const float*)gu, ld, (float*)out, ldo, inter, interleave);
   else
-    swiglu_kernel<bf16><<<grid, 256, 0, (cudaStream_t)stream>>>((const bf16*)gu, ld, (bf16*)out, ldo, inter, interleave);
+    hb_launch(swiglu_kernel<bf16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const bf16*)gu, ld, (bf16*)out, ldo, inter, interleave);
   HB_CHECK_LAUNCH("swiglu");
   return 0;
 }
@@ -140,6 +146,8 @@ struct QkvCacheArgs {
 
 template <typename T>
 __global__ void qk_norm_rope_cache_kernel(QkvCacheArgs a) {
+  pdl_launch();
+  pdl_wait();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int heads_total = a.nh + 2 * a.nkv;
@@ -218,9 +226,9 @@ extern "C" int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* 
   const long long blocks = ceil_div_ll(units, wpb);
   HB_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_cache: too many (token, head) pairs");
   if (dtype == HB_F32)
-    qk_norm_rope_cache_kernel<float><<<(unsigned)blocks, wpb * 32, 0, (cudaStream_t)stream>>>(a);
+    hb_launch(qk_norm_rope_cache_kernel<float>, dim3((unsigned)blocks), dim3(wpb * 32), 0, (cudaStream_t)stream, a);
   else
-    qk_norm_rope_cache_kernel<bf16><<<(unsigned)blocks, wpb * 32, 0, (cudaStream_t)stream>>>(a);
+    hb_launch(qk_norm_rope_cache_kernel<bf16>, dim3((unsigned)blocks), dim3(wpb * 32), 0, (cudaStream_t)stream, a);
   HB_CHECK_LAUNCH("qk_norm_rope_cache");
   return 0;
 }
@@ -229,6 +237,8 @@ extern "C" int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* 
 // residual[t, :] += y[t, :] (for parts that cannot fuse the sum into their last product)
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ res, const T* __restrict__ y, int ld, int dim) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < dim) res[(size_t)t * dim + i] += to_f32(y[(size_t)t * ld + i]);
@@ -238,9 +248,9 @@ extern "C" int hb_add_residual(int dtype, float* res, const void* y, int ld, int
   HB_REQUIRE(n_tokens > 0 && dim > 0 && n_tokens <= 65535, "add_residual: bad sizes");
   dim3 grid(ceil_div(dim, 256), n_tokens);
   if (dtype == HB_F32)
-    add_residual_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(res, (const float*)y, ld, dim);
+    hb_launch(add_residual_kernel<float>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, res, (const float*)y, ld, dim);
   else
-    add_residual_kernel<bf16><<<grid, 256, 0, (cudaStream_t)stream>>>(res, (const bf16*)y, ld, dim);
+    hb_launch(add_residual_kernel<bf16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, res, (const bf16*)y, ld, dim);
   HB_CHECK_LAUNCH("add_residual");
   return 0;
 }

@@ -16,3 +16,9 @@ void hb_set_error(const char* fmt, ...) {
 
 extern "C" const char* hb_last_error(void) { return g_last_error; }
 extern "C" int hb_abi_version(void) { return 1; }
+
+// Programmatic dependent launch between consecutive kernels of a stream (see common.cuh).
+static int g_pdl = 0;   // measured slower than plain stream order inside captured decode graphs: off unless asked for
+int hb_pdl_enabled(void) { return g_pdl; }
+extern "C" void hb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+extern "C" int hb_get_pdl(void) { return g_pdl; }

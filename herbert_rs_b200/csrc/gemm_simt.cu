@@ -20,6 +20,8 @@ gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int 
                  int M, int N, int K) {
   __shared__ float As[TK][TM + 4];
   __shared__ float Ws[TK][TN + 4];
+  pdl_launch();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
   const int tx = tid & 15, ty = tid >> 4;  // outputs: rows ty*4.., cols tx*4..
@@ -80,13 +82,13 @@ static int gemm_simt_launch(const void* A, int lda, const void* W, int ldw, void
   cudaStream_t s = (cudaStream_t)stream;
   switch (epi) {
     case HB_EPI_STORE:
-      gemm_simt_kernel<T, HB_EPI_STORE><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K);
+      hb_launch(gemm_simt_kernel<T, HB_EPI_STORE>, dim3(grid), dim3(256), 0, s, (const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K);
       break;
     case HB_EPI_STORE_F32:
-      gemm_simt_kernel<T, HB_EPI_STORE_F32><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K);
+      hb_launch(gemm_simt_kernel<T, HB_EPI_STORE_F32>, dim3(grid), dim3(256), 0, s, (const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K);
       break;
     case HB_EPI_RESIDUAL:
-      gemm_simt_kernel<T, HB_EPI_RESIDUAL><<<grid, 256, 0, s>>>((const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K);
+      hb_launch(gemm_simt_kernel<T, HB_EPI_RESIDUAL>, dim3(grid), dim3(256), 0, s, (const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K);
       break;
     default:
       HB_FAIL(2, "gemm: unknown epilogue %d", epi);

@@ -55,15 +55,23 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
 
   const int ksteps = (K + 31) >> 5;
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int ks0 = warp; ks0 < ksteps; ks0 += SK_WARPS * UNROLL) {
-    uint4 wa[UNROLL], wb[UNROLL];
+  // Weights never depend on the previous kernel: the first batch of loads is issued before the
+  // wait on it, and every later batch is issued before the batch in hand is multiplied.
+  uint4 wa[UNROLL], wb[UNROLL], na[UNROLL], nb[UNROLL];
+  auto load_w = [&](int ks0, uint4* ra, uint4* rb) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (ks0 + u * SK_WARPS) * 32 + 8 * t;
       const bool ok = k < K;  // K is a multiple of 8: a lane's 8 elements are all inside or all outside
-      wa[u] = (ok && lo_ok) ? ld_stream16(w_lo + k) : zero;
-      wb[u] = (ok && hi_ok) ? ld_stream16(w_hi + k) : zero;
+      ra[u] = (ok && lo_ok) ? ld_stream16(w_lo + k) : zero;
+      rb[u] = (ok && hi_ok) ? ld_stream16(w_hi + k) : zero;
     }
+  };
+  pdl_launch();
+  load_w(warp, wa, wb);
+  pdl_wait();
+  for (int ks0 = warp; ks0 < ksteps; ks0 += SK_WARPS * UNROLL) {
+    load_w(ks0 + SK_WARPS * UNROLL, na, nb);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (ks0 + u * SK_WARPS) * 32 + 8 * t;
@@ -76,6 +84,11 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
         mma_bf16_16816(acc[nt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, x.x, x.y);
         mma_bf16_16816(acc[nt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, x.z, x.w);
       }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      wa[u] = na[u];
+      wb[u] = nb[u];
     }
   }
   // accumulator layout: acc[nt][0..1] = (weight row g,   tokens nt*8 + 2t, 2t+1); [2..3] = row g+8
@@ -122,10 +135,10 @@ static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C
                          int epi, cudaStream_t s) {
   const unsigned grid = (unsigned)ceil_div(N, 16);
   switch (epi) {
-    case HB_EPI_STORE: gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_STORE_F32: gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE_F32><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_RESIDUAL: gemm_skinny_kernel<NT, UNROLL, HB_EPI_RESIDUAL><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_SWIGLU: gemm_skinny_kernel<NT, UNROLL, HB_EPI_SWIGLU><<<grid, SK_THREADS, 0, s>>>(A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE_F32: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_RESIDUAL: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_SWIGLU: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
     default: HB_FAIL(2, "gemm_skinny: unknown epilogue %d", epi);
   }
   HB_CHECK_LAUNCH("gemm_skinny");

@@ -15,92 +15,13 @@
 // No thread-block clusters and no multicast are used.  Rows/columns beyond M, N, K are
 // zero-filled by TMA on load and skipped on store.  Every wait on an mbarrier is bounded; a wait
 // that runs out sets *error_flag and the CTA winds down (tensor memory is always released).
-#include <cuda.h>
-
 #include "api.h"
 #include "common.cuh"
+#include "tcgen05_utils.cuh"
 
 #define TG_BM 128
-#define TG_BK 64
 #define TG_THREADS 192
-#define TG_WAIT_NS 2000000000ull   // a wait on an mbarrier gives up after two seconds
 #define HB_EPI_SWIGLU 3
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false if the phase did not complete within TG_WAIT_NS.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-  unsigned long long start = 0;
-  for (unsigned i = 0;; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((i & 255u) == 255u) {
-      const unsigned long long now = global_ns();
-      if (start == 0) start = now;
-      else if (now - start > TG_WAIT_NS) return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
-                                            unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major bf16 tile stored by TMA with the 128-byte swizzle:
-// rows are 128 bytes, groups of 8 rows (1024 bytes) follow one another.
-__device__ __forceinline__ unsigned long long umma_desc_sw128(unsigned smem_addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);   // start address, 16-byte units
-  d |= (unsigned long long)1 << 16;                          // leading byte offset (unused with swizzled K-major)
-  d |= (unsigned long long)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
-  d |= (unsigned long long)1 << 46;                          // descriptor version of this architecture
-  d |= (unsigned long long)2 << 61;                          // 128-byte swizzle
-  return d;
-}
 
 template <int BN>
 struct TgSmem {
@@ -140,9 +61,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  pdl_launch();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();
   const unsigned tmem_acc = *tmem_slot;
 
   if (warp == 0) {
@@ -262,37 +185,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-// ---- host side ----------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// A [rows, K] bf16 matrix with leading dimension ld, read in boxes of box_rows x 64 elements.
-static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  HB_REQUIRE(fn != nullptr, "gemm_tcgen05: the driver does not provide cuTensorMapEncodeTiled");
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {TG_BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  HB_REQUIRE(r == CUDA_SUCCESS, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return 0;
-}
-
 template <int BN, int EPI>
 static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int* err,
                      cudaStream_t s) {
@@ -304,7 +196,7 @@ static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
     configured = true;
   }
   dim3 grid(ceil_div(M, TG_BM), ceil_div(N, BN));
-  gemm_tcgen05_kernel<BN, EPI><<<grid, TG_THREADS, smem, s>>>(ma, mw, C, ldc, M, N, K, err);
+  hb_launch(gemm_tcgen05_kernel<BN, EPI>, dim3(grid), dim3(TG_THREADS), smem, s, ma, mw, C, ldc, M, N, K, err);
   HB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }

@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_launch();
+  pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -69,9 +71,97 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
   }
 }
 
-extern "C" int hb_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, void* stream) {
+// Two stages for large vocabularies: every row is cut into ARGMAX_CHUNKS pieces that separate
+// blocks scan (so a batch of 8 rows keeps far more than 8 SMs busy), then one warp per row picks
+// the best piece; ties go to the lower index at both stages.
+#define ARGMAX_CHUNKS 64
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int ld, int vocab, float* __restrict__ pv, int* __restrict__ pi) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  pdl_launch();
+  pdl_wait();
+  const int chunk = blockIdx.x, row = blockIdx.y;
+  const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+  const int beg = chunk * per, end = min(vocab, beg + per);
+  const float* r = logits + (size_t)row * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = beg + threadIdx.x; i < end; i += blockDim.x) {
+    const float v = r[i];
+    if (v > best) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        best = sv[w];
+        bi = si[w];
+      }
+    pv[(size_t)row * ARGMAX_CHUNKS + chunk] = best;
+    pi[(size_t)row * ARGMAX_CHUNKS + chunk] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  const int row = blockIdx.x, lane = threadIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = lane; c < ARGMAX_CHUNKS; c += 32) {
+    const float v = pv[(size_t)row * ARGMAX_CHUNKS + c];
+    const int i = pi[(size_t)row * ARGMAX_CHUNKS + c];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
+// scratch (optional): 2 * ARGMAX_CHUNKS * n_rows 4-byte words; with it, large vocabularies take two stages.
+extern "C" int hb_argmax(const float* logits, int ld, int n_rows, int vocab, int* out, void* scratch,
+                         long long scratch_words, void* stream) {
   HB_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "argmax: bad sizes");
-  argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
+  if (scratch != nullptr && vocab >= 8192 && scratch_words >= 2LL * ARGMAX_CHUNKS * n_rows && n_rows <= 65535) {
+    float* pv = (float*)scratch;
+    int* pi = (int*)scratch + (size_t)ARGMAX_CHUNKS * n_rows;
+    hb_launch(argmax_partial_kernel, dim3(ARGMAX_CHUNKS, n_rows), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, pv, pi);
+    HB_CHECK_LAUNCH("argmax_partial");
+    hb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, (cudaStream_t)stream, (const float*)pv, (const int*)pi, out);
+    HB_CHECK_LAUNCH("argmax_final");
+    return 0;
+  }
+  hb_launch(argmax_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, ld, vocab, out);
   HB_CHECK_LAUNCH("argmax");
   return 0;
 }
@@ -104,6 +194,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature, int top_k,
               float top_p, const float* __restrict__ uniforms, int* __restrict__ out) {
   __shared__ SampleShared sh;
+  pdl_launch();
+  pdl_wait();
   const int tid = threadIdx.x;
   const float* row = logits + (size_t)blockIdx.x * ld;
 
@@ -260,7 +352,7 @@ extern "C" int hb_sample(const float* logits, int ld, int n_rows, int vocab, flo
   HB_REQUIRE(temperature > 0.0f, "sample: temperature must be > 0 (0 is greedy: use argmax)");
   HB_REQUIRE(top_k >= 0, "sample: top_k must be >= 0");
   HB_REQUIRE(top_p > 0.0f, "sample: top_p must be > 0");
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, temperature, top_k,
+  hb_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, ld, vocab, temperature, top_k,
                                                                     top_p, uniforms, out);
   HB_CHECK_LAUNCH("sample");
   return 0;

@@ -9,6 +9,7 @@ computes on the CPU and nothing falls back to a library model or attention routi
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -19,6 +20,9 @@ from . import lib as _libmod
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64
+# Which kernel serves products of at most 64 activation rows: "stream" (TMA + tcgen05, K slices) or
+# "skinny" (mma.sync with direct global loads).  Both are kept and tested; measurements decide.
+DECODE_GEMM = "skinny"
 
 _SIGS = {
     "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -31,13 +35,15 @@ _SIGS = {
     "hb_gemm_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_tcgen05_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                            ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "hb_attention_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
 }
 _fns: dict = {}
@@ -47,6 +53,8 @@ def _fn(name: str):
     f = _fns.get(name)
     if f is None:
         lib = _libmod.load()
+        if not _fns and "HB_PDL" in os.environ:
+            lib.hb_set_pdl(int(os.environ["HB_PDL"]))
         try:
             f = getattr(lib, name)
         except AttributeError:
@@ -58,7 +66,7 @@ def _fn(name: str):
 
 
 # kernels each launcher starts (for honest launch counts)
-_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2}
+_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2}
 _launches = 0
 
 
@@ -161,9 +169,19 @@ def attention_simt(q, ldq, out, k_cache, v_cache, tok_seq, tok_pos, seq_pages, n
          int(window or 0), _stream())
 
 
+_argmax_scratch: dict = {}
+ARGMAX_SCRATCH_ROWS = 4096
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the first maximum of row r."""
     _check(logits, torch.float32, "logits"); _check(out, torch.int32, "out")
-    _run("hb_argmax", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(), _stream())
+    key = str(logits.device)
+    if key not in _argmax_scratch:
+        _argmax_scratch[key] = torch.empty(2 * 64 * ARGMAX_SCRATCH_ROWS, dtype=torch.int32, device=logits.device)
+    sc = _argmax_scratch[key]
+    _run("hb_argmax", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(),
+         sc.data_ptr(), sc.numel(), _stream())
 
 
 def sample(logits, temperature, top_k, top_p, uniforms, out) -> None:
@@ -208,6 +226,33 @@ def gemm_tcgen05(a, w, c, epilogue=EPI_STORE) -> None:
          a.shape[0], w.shape[0], a.shape[1], epilogue, _error_flag(a.device).data_ptr(), _stream())
 
 
+_stream_bufs: dict = {}
+STREAM_SCRATCH_FLOATS = 296 * 64 * 128     # most (tile, slice) pairs a call cuts K into, at 64 padded rows
+STREAM_COUNTERS = 8192
+
+
+def _stream_buffers(device):
+    """Per device: scratch for the K slices' partial tiles and the tiles' arrival counters (zero
+    between launches).  Fixed addresses, so captured graphs can use them."""
+    key = str(device)
+    if key not in _stream_bufs:
+        _stream_bufs[key] = (torch.empty(STREAM_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+                             torch.zeros(STREAM_COUNTERS, dtype=torch.int32, device=device))
+    return _stream_bufs[key]
+
+
+def gemm_stream(a, w, c, epilogue=EPI_STORE) -> None:
+    """c (op)= a @ w.T for at most 64 rows of a (bfloat16): weights streamed once through TMA into
+    tcgen05 tensor cores, K cut into slices that the last-arriving CTA of a tile sums in order."""
+    _check(a, torch.bfloat16, "a"); _check(w, torch.bfloat16, "w"); _check(c, None, "c")
+    scratch, counters = _stream_buffers(a.device)
+    if w.shape[0] > STREAM_COUNTERS * 128:
+        raise BackendError(f"gemm_stream: {w.shape[0]} weight rows exceed the {STREAM_COUNTERS * 128} the counters cover")
+    _run("hb_gemm_stream_bf16", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
+         a.shape[0], w.shape[0], a.shape[1], epilogue, scratch.data_ptr(), scratch.numel(), counters.data_ptr(),
+         counters.numel(), _error_flag(a.device).data_ptr(), _stream())
+
+
 def _tcgen05_ok(a, w) -> bool:
     return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -226,7 +271,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_
     bfloat16: tensor-core kernels where their size rules hold, else the any-shape kernel).
     """
     if _skinny_ok(a, w):
-        gemm_skinny(a, w, c, epilogue)
+        (gemm_stream if DECODE_GEMM == "stream" else gemm_skinny)(a, w, c, epilogue)
     elif _tcgen05_ok(a, w):
         gemm_tcgen05(a, w, c, epilogue)
     else:
@@ -237,7 +282,7 @@ def gemm_swiglu(a: torch.Tensor, wgu: torch.Tensor, out: torch.Tensor, interleav
     """out = silu(gate) * up with [gate | up] = a @ wgu.T.  Fused into the product where a kernel can;
     otherwise the product goes to `scratch(shape, dtype)` and the SwiGLU kernel follows."""
     if interleave == 8 and _skinny_ok(a, wgu):
-        gemm_skinny(a, wgu, out, EPI_SWIGLU)
+        (gemm_stream if DECODE_GEMM == "stream" else gemm_skinny)(a, wgu, out, EPI_SWIGLU)
         return
     if interleave == 8 and _tcgen05_ok(a, wgu):
         gemm_tcgen05(a, wgu, out, EPI_SWIGLU)
@@ -247,7 +292,7 @@ def gemm_swiglu(a: torch.Tensor, wgu: torch.Tensor, out: torch.Tensor, interleav
     swiglu(gu, out, interleave)
 
 
-DECODE_TARGET_CTAS = 592   # about two waves of two resident CTAs on each of the 148 SMs
+DECODE_TARGET_CTAS = int(os.environ.get("HB_DECODE_CTAS", "296"))   # two resident CTAs on each of the 148 SMs: one wave
 
 
 def attention_decode_scratch_floats(n_seqs, num_heads, head_dim, nsplit) -> int:
@@ -256,7 +301,7 @@ def attention_decode_scratch_floats(n_seqs, num_heads, head_dim, nsplit) -> int:
 
 def decode_splits(n_seqs: int, num_kv_heads: int, max_tiles: int) -> int:
     """How many key ranges each (sequence, kv head) is cut into, so that the grid fills the GPU."""
-    want = -(-DECODE_TARGET_CTAS // max(1, n_seqs * num_kv_heads))
+    want = DECODE_TARGET_CTAS // max(1, n_seqs * num_kv_heads)      # rounded down: all CTAs resident at once
     return max(1, min(want, max_tiles, 64))
 
 

@@ -236,6 +236,20 @@ def test_argmax_first_maximum_and_ties():
     assert out.cpu().tolist() == want
 
 
+def test_argmax_two_stages_for_large_vocabularies():
+    torch.manual_seed(13)
+    x = torch.randn(9, 151936)
+    x[0, 151935] = x[0, 2374] = 77.0          # equal maxima in different pieces: the lower index wins
+    x[1, 0] = 50.0
+    x[2, :] = -float("inf")
+    x[3, 2373] = x[3, 2374] = 60.0            # on the edge between two pieces
+    out = torch.empty(9, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(x), out)
+    want = [int(torch.argmax(r)) for r in x]
+    want[0], want[2], want[3] = 2374, 0, 2373
+    assert out.cpu().tolist() == want
+
+
 @pytest.mark.parametrize("t,k,p", [(0.8, 20, 0.9), (0.4, 40, 0.9), (1.0, 0, 1.0), (1.3, 0, 0.5), (0.7, 5, 1.0),
                                    (1.0, 1, 0.9), (1.0, 3000, 0.95), (2.0, 7, 0.01)])
 def test_sample_kernel_against_its_host_twin_and_the_reference_distribution(t, k, p):
@@ -412,3 +426,42 @@ def test_attention_prefill_finds_a_far_key_and_the_windows_edge():
         row = (0 if b == 0 else 300) + qpos - int(pos0[b])
         target = c["vs"][b][kpos, h // (nh // nkv)]
         assert (((out[row].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit
+
+
+@pytest.mark.parametrize("M", [1, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(96, 64), (304, 96), (1000, 1024), (48, 4104), (16, 8), (4096, 4096), (640, 12288)])
+def test_gemm_stream_every_epilogue(M, N, K):
+    torch.manual_seed(10)
+    a, w = torch.randn(M, K).to(torch.bfloat16), (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    ref = a.double() @ w.double().T
+    da, dw = dev(a), dev(w)
+    c32 = torch.full((M, N), float("nan"), device="cuda")
+    for _ in range(2):                       # twice: the tiles' counters must be back at zero after a call
+        ops.gemm_stream(da, dw, c32, ops.EPI_STORE_F32)
+        ops.check_kernel_errors()
+        close(c32, ref, torch.float32)
+    again = torch.empty_like(c32)
+    ops.gemm_stream(da, dw, again, ops.EPI_STORE_F32)
+    assert torch.equal(again, c32)           # slices are summed in slice order, not in arrival order
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_stream(da, dw, c, ops.EPI_STORE)
+    close(c, ref, torch.bfloat16)
+    res = torch.randn(M, N)
+    r = dev(res.clone())
+    ops.gemm_stream(da, dw, r, ops.EPI_RESIDUAL)
+    close(r, res.double() + ref, torch.float32)
+    if N % 16 == 0:
+        out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_stream(da, dw, out, ops.EPI_SWIGLU)
+        blocks = ref.view(M, N // 16, 2, 8)
+        gate, up = blocks[:, :, 0].reshape(M, -1), blocks[:, :, 1].reshape(M, -1)
+        close(out, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
+    ops.check_kernel_errors()
+
+
+def test_gemm_stream_refuses_what_it_cannot_do():
+    a, w = dev(torch.zeros(65, 64, dtype=torch.bfloat16)), dev(torch.zeros(32, 64, dtype=torch.bfloat16))
+    with pytest.raises(BackendError, match="at most 64"):
+        ops.gemm_stream(a, w, torch.empty(65, 32, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(BackendError, match="multiples of 8"):
+        ops.gemm_stream(a[:4, :60], w[:, :60], torch.empty(4, 32, device="cuda", dtype=torch.bfloat16))
