@@ -19,6 +19,7 @@
 #define AD_WARPS 4
 #define AD_THREADS (AD_WARPS * 32)
 #define AD_TILE 64
+#define AD_MAX_TILES 1024   // tiles one CTA may be given (65,536 keys); the launcher sizes the splits to that
 
 struct DecodeArgs {
   const bf16* q;       // [B, ldq]: row b holds the query heads of sequence b's new token
@@ -60,19 +61,33 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
   const int tiles_per_page = a.page_size / AD_TILE;
   const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
   const size_t head_elems = (size_t)a.page_size * hd;
+  // the pages of this CTA's tiles, fetched once (a look-up per tile would put a memory round trip
+  // in front of every copy)
+  __shared__ int page_ids[AD_MAX_TILES];
+  const int first_tile = t0;
+  for (int i = threadIdx.x; i < t1 - t0; i += AD_THREADS) page_ids[i] = pages[(t0 + i) / tiles_per_page];
+  __syncthreads();
 
+  // This thread's first 16-byte chunk of a tile and the step to its next one (no division in the loop).
+  const int chunk_r0 = threadIdx.x / chunks_per_row, chunk_c0 = threadIdx.x % chunks_per_row;
+  const int step_r = AD_THREADS / chunks_per_row, step_c = AD_THREADS % chunks_per_row;
   auto issue = [&](int tile, int stage) {
-    const int page = pages[tile / tiles_per_page];
+    const int page = page_ids[tile - first_tile];
     const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AD_TILE * hd;
     const bf16* kg = a.kcache + off;
     const bf16* vg = a.vcache + off;
     unsigned char* ks = smem + (size_t)stage * 2 * tile_bytes;
     unsigned char* vs = ks + tile_bytes;
-    const int total = AD_TILE * chunks_per_row;
-    for (int c = threadIdx.x; c < total; c += AD_THREADS) {
-      const int r = c / chunks_per_row, cc = c % chunks_per_row;
+    int r = chunk_r0, cc = chunk_c0;
+    while (r < AD_TILE) {
       cp_async16(ks + r * row_bytes + cc * 16, kg + (size_t)r * hd + cc * 8);
       cp_async16(vs + r * row_bytes + cc * 16, vg + (size_t)r * hd + cc * 8);
+      r += step_r;
+      cc += step_c;
+      if (cc >= chunks_per_row) {
+        cc -= chunks_per_row;
+        ++r;
+      }
     }
   };
 
@@ -280,6 +295,8 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   HB_REQUIRE(ldq % 2 == 0 && ((uintptr_t)q & 3) == 0, "attention_decode: queries must be 4-byte aligned");
   HB_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "attention_decode: cache must be 16-byte aligned");
   HB_REQUIRE(window >= 0, "attention_decode: window must be >= 0");
+  HB_REQUIRE((long long)pages_stride * (page_size / AD_TILE) <= (long long)AD_MAX_TILES * nsplit,
+             "attention_decode: %d pages per sequence in %d splits exceed %d tiles per CTA", pages_stride, nsplit, AD_MAX_TILES);
   cudaStream_t s = (cudaStream_t)stream;
   int stages = 3;
   if (decode_smem_bytes(hd, stages) > 110 * 1024) stages = 2;

@@ -20,6 +20,7 @@
 #define AP_THREADS (AP_WARPS * 32)
 #define AP_TILE 64
 #define AP_QTILE 64
+#define AP_PAGE_IDS 1024     // tiles whose pages one CTA keeps in shared memory (65,536 keys)
 
 struct PrefillArgs {
   const bf16* q;   // [T, ldq]; row t holds the query heads of token t
@@ -61,19 +62,36 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
   const int tiles_per_page = a.page_size / AP_TILE;
   const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
   const size_t head_elems = (size_t)a.page_size * hd;
+  // pages of the tiles this CTA walks, fetched in blocks of AP_PAGE_IDS ahead of their copies
+  __shared__ int page_ids[AP_PAGE_IDS];
+  int first_tile = tile_lo;
+  auto fetch_pages = [&](int from) {
+    first_tile = from;
+    for (int i = threadIdx.x; i < AP_PAGE_IDS && from + i < tile_hi; i += AP_THREADS) page_ids[i] = pages[(from + i) / tiles_per_page];
+  };
+  fetch_pages(tile_lo);
+  __syncthreads();
 
+  // This thread's first 16-byte chunk of a tile and the step to its next one (no division in the loop).
+  const int chunk_r0 = threadIdx.x / chunks_per_row, chunk_c0 = threadIdx.x % chunks_per_row;
+  const int step_r = AP_THREADS / chunks_per_row, step_c = AP_THREADS % chunks_per_row;
   auto issue = [&](int tile, int stage) {
-    const int page = pages[tile / tiles_per_page];
+    const int page = page_ids[tile - first_tile];
     const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AP_TILE * hd;
     const bf16* kg = a.kcache + off;
     const bf16* vg = a.vcache + off;
     unsigned char* ks = smem + (size_t)stage * 2 * tile_bytes;
     unsigned char* vs = ks + tile_bytes;
-    const int total = AP_TILE * chunks_per_row;
-    for (int c = threadIdx.x; c < total; c += AP_THREADS) {
-      const int r = c / chunks_per_row, cc = c % chunks_per_row;
+    int r = chunk_r0, cc = chunk_c0;
+    while (r < AP_TILE) {
       cp_async16(ks + r * row_bytes + cc * 16, kg + (size_t)r * hd + cc * 8);
       cp_async16(vs + r * row_bytes + cc * 16, vg + (size_t)r * hd + cc * 8);
+      r += step_r;
+      cc += step_c;
+      if (cc >= chunks_per_row) {
+        cc -= chunks_per_row;
+        ++r;
+      }
     }
   };
 
@@ -240,6 +258,7 @@ extern "C" int hb_attention_prefill_bf16(const void* q, int ldq, void* out, int 
   HB_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "attention_prefill: cache must be 16-byte aligned");
   HB_REQUIRE(nh <= 65535 && n_seqs <= 65535, "attention_prefill: grid too large");
   HB_REQUIRE(window >= 0, "attention_prefill: window must be >= 0");
+  HB_REQUIRE((long long)pages_stride * (page_size / AP_TILE) <= AP_PAGE_IDS, "attention_prefill: sequences of more than %d keys are not supported", AP_PAGE_IDS * AP_TILE);
   int stages = 3;
   int smem = stages * 2 * AP_TILE * (hd * 2 + 16);
   if (smem > 110 * 1024) {
