@@ -16,6 +16,9 @@
 #include "common.cuh"
 #include "mma_utils.cuh"
 
+// exp: the hardware's fast exponential (ex2.approx, about 2 ulp in float).  The probabilities are
+// rounded to bfloat16 for the P V product right after, so nothing is lost; sums stay in float.
+
 #define AD_WARPS 4
 #define AD_THREADS (AD_WARPS * 32)
 #define AD_TILE 64
@@ -163,7 +166,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m[r], mx[r]);
-        corr[r] = (m_new == -INFINITY) ? 1.0f : expf(m[r] - m_new);
+        corr[r] = (m_new == -INFINITY) ? 1.0f : __expf(m[r] - m_new);
         m[r] = m_new;
       }
       float ps[2] = {0.0f, 0.0f};
@@ -171,7 +174,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float pv = (s[nt][j] == -INFINITY) ? 0.0f : expf(s[nt][j] - m[j >> 1]);
+          const float pv = (s[nt][j] == -INFINITY) ? 0.0f : __expf(s[nt][j] - m[j >> 1]);
           s[nt][j] = pv;
           ps[j >> 1] += pv;
         }
@@ -232,7 +235,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
 #pragma unroll
     for (int w = 0; w < AD_WARPS; ++w) {
       const float mw = sm_m[w * 16 + r];
-      const float f = (mw == -INFINITY) ? 0.0f : expf(mw - mm);
+      const float f = (mw == -INFINITY) ? 0.0f : __expf(mw - mm);
       acc += f * sm_o[((size_t)w * 16 + r) * hd + d];
       ll += f * sm_l[w * 16 + r];
     }
@@ -258,14 +261,14 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
   float ll = 0.0f;
   for (int s = 0; s < nsplit; ++s) {
     const float ms = part_ml[(base + s) * 2];
-    if (ms != -INFINITY) ll += expf(ms - mm) * part_ml[(base + s) * 2 + 1];
+    if (ms != -INFINITY) ll += __expf(ms - mm) * part_ml[(base + s) * 2 + 1];
   }
   const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.0f;
     for (int s = 0; s < nsplit; ++s) {
       const float ms = part_ml[(base + s) * 2];
-      if (ms != -INFINITY) acc += expf(ms - mm) * part_o[(base + s) * hd + d];
+      if (ms != -INFINITY) acc += __expf(ms - mm) * part_o[(base + s) * hd + d];
     }
     out[(size_t)b * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc * inv);
   }

@@ -16,6 +16,9 @@
 #include "common.cuh"
 #include "mma_utils.cuh"
 
+// exp: the hardware's fast exponential (ex2.approx, about 2 ulp in float).  The probabilities are
+// rounded to bfloat16 for the P V product right after, so nothing is lost; sums stay in float.
+
 #define AP_WARPS 4
 #define AP_THREADS (AP_WARPS * 32)
 #define AP_TILE 64
@@ -187,7 +190,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m[r], mx[r]);
-        corr[r] = (m_new == -INFINITY) ? 1.0f : expf(m[r] - m_new);
+        corr[r] = (m_new == -INFINITY) ? 1.0f : __expf(m[r] - m_new);
         m[r] = m_new;
       }
       float ps[2] = {0.0f, 0.0f};
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillAr
       for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float pv = (s[nt][j] == -INFINITY) ? 0.0f : expf(s[nt][j] - m[j >> 1]);
+          const float pv = (s[nt][j] == -INFINITY) ? 0.0f : __expf(s[nt][j] - m[j >> 1]);
           s[nt][j] = pv;
           ps[j >> 1] += pv;
         }

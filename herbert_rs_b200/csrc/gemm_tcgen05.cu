@@ -4,14 +4,16 @@
 // shader (backends/backend_vulkan bf16_matmul.comp) and its AVX-512 tile kernel
 // (backends/backend_bf16_avx512/src/avx512_bf16_matvec.S: avx512_bf16_matmul_tile).
 //
-// One CTA computes one 128 x BN tile of C (BN = 128 or 256):
+// A persistent grid (one CTA per SM) walks the 128 x BN tiles of C (BN = 128 or 256):
 //   warp 0   one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a 128 x 64 slab
 //            of A and a BN x 64 slab of W per pipeline stage, signalling an mbarrier per stage;
-//   warp 1   allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16) four times
-//            per stage and commits the stage's "empty" barrier, then the "accumulator ready" one;
-//   warps 2-5  read the accumulator with tcgen05.ld (each warp its 32 lanes = 32 rows of C) and
-//            apply the epilogue: store, store as float, add into the float residual stream, or
-//            SwiGLU over column groups of 8 gate + 8 up.
+//   warp 1   allocates tensor memory (two accumulators of BN columns); one lane issues tcgen05.mma
+//            (M=128, N=BN, K=16) four times per stage, commits the stage's "empty" barrier and, at
+//            the end of a tile, that accumulator's "full" barrier;
+//   warps 2-5  read a finished accumulator with tcgen05.ld (each warp its 32 lanes = 32 rows of
+//            C), hand it back ("empty" barrier) and apply the epilogue: store, store as float, add
+//            into the float residual stream, or SwiGLU over column groups of 8 gate + 8 up.
+// With two accumulators the epilogue of tile i runs while the tensor cores work on tile i+1.
 // No thread-block clusters and no multicast are used.  Rows/columns beyond M, N, K are
 // zero-filled by TMA on load and skipped on store.  Every wait on an mbarrier is bounded; a wait
 // that runs out sets *error_flag and the CTA winds down (tensor memory is always released).
@@ -30,6 +32,14 @@ struct TgSmem {
   static constexpr int kBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
@@ -39,14 +49,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles want 1024-byte alignment
   unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
-  const unsigned bars = base + STAGES * STAGE_BYTES;                  // full[STAGES], empty[STAGES], acc, tmem slot
-  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + STAGES * STAGE_BYTES + (2 * STAGES + 1) * 8);
+  // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the tensor-memory slot
+  const unsigned bars = base + STAGES * STAGE_BYTES;
+  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8);
   auto full_bar = [&](int s) { return bars + s * 8; };
   auto empty_bar = [&](int s) { return bars + (STAGES + s) * 8; };
-  const unsigned acc_bar = bars + 2 * STAGES * 8;
+  auto acc_full = [&](int b) { return bars + (2 * STAGES + b) * 8; };
+  auto acc_empty = [&](int b) { return bars + (2 * STAGES + 2 + b) * 8; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TG_BM, n0 = blockIdx.y * BN;
+  const int tiles_m = (M + TG_BM - 1) / TG_BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
 
   if (threadIdx.x == 0) {
@@ -54,11 +67,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);     // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   pdl_launch();
@@ -66,84 +82,130 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   pdl_wait();
-  const unsigned tmem_acc = *tmem_slot;
+  const unsigned tmem_base = *tmem_slot;
 
+  // Tiles in the order m fastest: CTAs that run side by side share the same slab of W in L2.
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(empty_bar(s), ((kb / STAGES) - 1) & 1)) {
-          atomicExch(error_flag, 1);
-          break;
+      int it = 0;        // k blocks issued so far, over all tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1)) {
+            atomicExch(error_flag, 1);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const unsigned a_dst = base + s * STAGE_BYTES;
+          tma_load_2d(a_dst, &map_a, kb * TG_BK, m0, full_bar(s));
+          tma_load_2d(a_dst + TG_BM * TG_BK * 2, &map_w, kb * TG_BK, n0, full_bar(s));
         }
-        mbar_expect_tx(full_bar(s), STAGE_BYTES);
-        const unsigned a_dst = base + s * STAGE_BYTES;
-        tma_load_2d(a_dst, &map_a, kb * TG_BK, m0, full_bar(s));
-        tma_load_2d(a_dst + TG_BM * TG_BK * 2, &map_w, kb * TG_BK, n0, full_bar(s));
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // instruction descriptor: D float, A and B bfloat16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
+      int it = 0, local = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        if (!mbar_wait(full_bar(s), (kb / STAGES) & 1)) {
-          atomicExch(error_flag, 2);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        // the epilogue must have drained this accumulator (its previous use was tile local - 2)
+        if (local >= 2 && !mbar_wait(acc_empty(buf), ((local >> 1) - 1) & 1)) {
+          atomicExch(error_flag, 4);
           ok = false;
           break;
         }
         tc_fence_after();
-        const unsigned a_addr = base + s * STAGE_BYTES;
-        const unsigned w_addr = a_addr + TG_BM * TG_BK * 2;
+        const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full_bar(s), (it / STAGES) & 1)) {
+            atomicExch(error_flag, 2);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const unsigned a_addr = base + s * STAGE_BYTES;
+          const unsigned w_addr = a_addr + TG_BM * TG_BK * 2;
 #pragma unroll
-        for (int k = 0; k < TG_BK / 16; ++k) {
-          tc_mma_bf16(tmem_acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(w_addr + k * 32), idesc,
-                      (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < TG_BK / 16; ++k) {
+            tc_mma_bf16(tmem_acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(w_addr + k * 32), idesc,
+                        (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));     // arrives when these MMAs have finished reading the stage
         }
-        tc_commit(empty_bar(s));     // arrives when these MMAs have finished reading the stage
+        tc_commit(acc_full(buf));      // arrives when every MMA of this tile is complete
       }
-      tc_commit(acc_bar);            // arrives when every MMA issued so far is complete
     }
   } else {
     // epilogue warps: TMEM lane quadrant = warp index modulo 4
     const int quad = warp & 3;
-    const bool ready = mbar_wait(acc_bar, 0);
-    if (!ready && lane == 0) atomicExch(error_flag, 3);
-    tc_fence_after();
-    const int m = m0 + quad * 32 + lane;
-    if (ready) {
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+      if (!mbar_wait(acc_full(buf), (local >> 1) & 1)) {
+        if (lane == 0) atomicExch(error_flag, 3);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
+      const int m = m0 + quad * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         unsigned r[32];
         tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+        if (c == BN / 32 - 1) {
+          // everything of this accumulator is in registers: the tensor cores may have it back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(buf));
+        }
         const int n = n0 + c * 32;
         if (m < M) {
           if (EPI == HB_EPI_SWIGLU) {
             // columns: [8 gate | 8 up] x 2 -> 16 outputs; output column = n/2 + ...
             bf16* out = (bf16*)Cv + (size_t)m * ldc + (n >> 1);
+            float y[16];
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                if (n + blk * 16 + 8 + j < N) {
-                  const float gate = __uint_as_float(r[blk * 16 + j]), up = __uint_as_float(r[blk * 16 + 8 + j]);
-                  out[blk * 8 + j] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
-                }
+                const float gate = __uint_as_float(r[blk * 16 + j]), up = __uint_as_float(r[blk * 16 + 8 + j]);
+                // silu(g) * u; fast exponential and division: the result is rounded to bfloat16 next
+                y[blk * 8 + j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
               }
+            if (n + 32 <= N && ((((size_t)m * ldc + (n >> 1)) & 7) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 8) {
+                uint4 v;
+                v.x = pack2(y[j], y[j + 1]); v.y = pack2(y[j + 2], y[j + 3]);
+                v.z = pack2(y[j + 4], y[j + 5]); v.w = pack2(y[j + 6], y[j + 7]);
+                *reinterpret_cast<uint4*>(out + j) = v;
+              }
+            } else {
+#pragma unroll
+              for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (n + blk * 16 + 8 + j < N) out[blk * 8 + j] = __float2bfloat16_rn(y[blk * 8 + j]);
+            }
           } else if (EPI == HB_EPI_STORE) {
             bf16* out = (bf16*)Cv + (size_t)m * ldc + n;
             if (n + 32 <= N && ((((size_t)m * ldc + n) & 7) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 v;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                v.x = *reinterpret_cast<unsigned*>(&p0); v.y = *reinterpret_cast<unsigned*>(&p1);
-                v.z = *reinterpret_cast<unsigned*>(&p2); v.w = *reinterpret_cast<unsigned*>(&p3);
+                v.x = pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                v.y = pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                v.z = pack2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                v.w = pack2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
                 *reinterpret_cast<uint4*>(out + j) = v;
               }
             } else {
@@ -181,7 +243,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
 }
 
@@ -195,7 +257,14 @@ static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
     if (e != cudaSuccess) HB_FAIL(3, "gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(ceil_div(M, TG_BM), ceil_div(N, BN));
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const int tiles = ceil_div(M, TG_BM) * ceil_div(N, BN);
+  dim3 grid(tiles < sms ? tiles : sms);
   hb_launch(gemm_tcgen05_kernel<BN, EPI>, dim3(grid), dim3(TG_THREADS), smem, s, ma, mw, C, ldc, M, N, K, err);
   HB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
