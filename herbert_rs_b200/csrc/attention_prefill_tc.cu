@@ -1,0 +1,391 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05), bfloat16, head sizes 64 and 128.
+//
+// The same arithmetic as attention_prefill.cu (causal grouped-query softmax attention in the flash
+// form, float softmax; reference: generic_attention/prefill/kernel_f32.rs:61-111), arranged for
+// tensor memory: a CTA owns 128 consecutive queries of one head of one sequence and walks the key
+// tiles (128 keys = two 64-key pages) of its causal range.
+//   warp 0     TMA: the Q tile once, then K and V tiles into two-stage rings (128-byte swizzle);
+//   warp 1     one lane issues tcgen05.mma:  S = Q K^T  (M=128, N=128) into one of two S buffers in
+//              tensor memory, and  O_j = P V  (M=128, N=head size; V is the MN-major operand as it
+//              lies in the cache) into one of two O buffers;
+//   warps 2-5  one thread per query row: read its row of S from tensor memory (no shuffles), mask,
+//              running maximum and sum in float, P = 2^(s*c - m) as bfloat16 into shared memory in
+//              the swizzled K-major layout the tensor cores read, and o = o * 2^(m_old - m_new) + O_j
+//              in registers; finally o / l goes to global memory.
+// The tensor cores compute S of tile j+1 while the row threads work on tile j.  Every wait on an
+// mbarrier is bounded; a wait that runs out sets *error_flag and the CTA winds down.
+#include "api.h"
+#include "common.cuh"
+#include "tcgen05_utils.cuh"
+
+#define PT_THREADS 192
+#define PT_Q 128        // queries per CTA
+#define PT_KEYS 128     // keys per tile
+#define PT_SUB (128 * 128)   // bytes of one [128 rows][64 columns] swizzled sub-tile
+
+__device__ __forceinline__ void mbar_arrive_cta(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// MN-major operand with the 128-byte swizzle: 64 contiguous elements of the MN axis per 128-byte row,
+// rows are consecutive K indices; lbo = bytes between 64-element MN blocks, 1024 between groups of 8 rows.
+__device__ __forceinline__ unsigned long long umma_desc_sw128_mn(unsigned smem_addr, unsigned lbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+// 2^x by the hardware's approximation (about 2 ulp in float); the result is rounded to bfloat16 next.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tc_ld32f(unsigned taddr, float* r) {
+  unsigned u[32];
+  tc_ld32(taddr, u);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
+}
+
+struct PrefillTcArgs {
+  bf16* out;
+  int ldo;
+  const int* seq_start;
+  const int* seq_pos0;
+  const int* seq_pages;
+  int pages_stride;
+  int nh, nkv, page_size;
+  float scale_log2;   // scale * log2(e)
+  int window;
+  int* error_flag;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(PT_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, PrefillTcArgs a) {
+  constexpr int NB = HD / 64;                 // 64-column blocks of the head
+  constexpr int TILE_BYTES = NB * PT_SUB;     // one Q, K, V tile
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
+  const unsigned q_s = base, k_s = q_s + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
+  unsigned char* p_gen = gen + (p_s - base);
+  const unsigned bars = p_s + 2 * PT_SUB;
+  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 s_empty
+  //           13 p_ready | 14,15 o_full | 16,17 o_empty
+  auto bar = [&](int i) { return bars + i * 8; };
+  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + (bars - base) + 18 * 8);
+
+  pdl_launch();
+  // the last query tiles have the longest key ranges: they go first, the short ones fill the tail
+  const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int row0 = a.seq_start[b], qlen = a.seq_start[b + 1] - row0;
+  if (qt * PT_Q >= qlen) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = h / (a.nh / a.nkv);
+  const int pos0 = a.seq_pos0[b];
+  const int q_first = qt * PT_Q, q_last = min(qlen, q_first + PT_Q) - 1;
+  const int p_first = pos0 + q_first, p_last = pos0 + q_last;
+  const int lo_first = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
+  const int tile_lo = lo_first / PT_KEYS, tile_hi = p_last / PT_KEYS + 1;
+  const int n_tiles = tile_hi - tile_lo;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 18; ++i) {
+      const bool from_rows = (i == 11 || i == 12 || i == 13 || i == 16 || i == 17);   // arrived at by the 4 row warps
+      mbar_init(bar(i), from_rows ? 4 : 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_wait();
+  const unsigned tmem = *tmem_slot;
+  const unsigned tm_s[2] = {tmem, tmem + 128u};
+  const unsigned tm_o[2] = {tmem + 256u, tmem + 256u + (unsigned)HD};
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(0), TILE_BYTES);
+#pragma unroll
+      for (int jb = 0; jb < NB; ++jb) tma_load_2d(q_s + jb * PT_SUB, &map_q, h * HD + jb * 64, row0 + q_first, bar(0));
+      const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        int rows[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int key0 = (tile_lo + j) * PT_KEYS + half * 64;
+          const int lp = key0 / a.page_size;
+          const int page = lp < a.pages_stride ? pages[lp] : 0;     // beyond the sequence: any page, its keys are masked
+          rows[half] = (page * a.nkv + kvh) * a.page_size + key0 % a.page_size;
+        }
+        if (j >= 2 && !mbar_wait(bar(3 + st), ((j >> 1) - 1) & 1)) { atomicExch(a.error_flag, 21); break; }
+        mbar_expect_tx(bar(1 + st), TILE_BYTES);
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb)
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+            tma_load_2d(k_s + st * TILE_BYTES + jb * PT_SUB + half * 8192, &map_k, jb * 64, rows[half], bar(1 + st));
+        if (j >= 2 && !mbar_wait(bar(7 + st), ((j >> 1) - 1) & 1)) { atomicExch(a.error_flag, 22); break; }
+        mbar_expect_tx(bar(5 + st), TILE_BYTES);
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb)
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+            tma_load_2d(v_s + st * TILE_BYTES + jb * PT_SUB + half * 8192, &map_v, jb * 64, rows[half], bar(5 + st));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // D float, A and B bfloat16; B of the second product is MN-major (bit 16)
+      const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(PT_KEYS >> 3) << 17) | ((unsigned)(PT_Q >> 4) << 24);
+      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(PT_Q >> 4) << 24);
+      bool ok = mbar_wait(bar(0), 0);
+      if (!ok) atomicExch(a.error_flag, 23);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        if (j >= 2 && !mbar_wait(bar(11 + st), ((j >> 1) - 1) & 1)) { atomicExch(a.error_flag, 24); return false; }   // S buffer drained
+        if (!mbar_wait(bar(1 + st), (j >> 1) & 1)) { atomicExch(a.error_flag, 25); return false; }                  // K tile landed
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const unsigned off = (ks >> 2) * PT_SUB + (ks & 3) * 32;
+          tc_mma_bf16(tm_s[st], umma_desc_sw128(q_s + off), umma_desc_sw128(k_s + st * TILE_BYTES + off), idesc_qk, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(bar(3 + st));    // K stage free
+        tc_commit(bar(9 + st));    // S ready
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (!ok) break;
+        if (!mbar_wait(bar(13), j & 1)) { atomicExch(a.error_flag, 26); break; }                                    // P written
+        if (!mbar_wait(bar(5 + st), (j >> 1) & 1)) { atomicExch(a.error_flag, 27); break; }                         // V tile landed
+        if (j >= 2 && !mbar_wait(bar(16 + st), ((j >> 1) - 1) & 1)) { atomicExch(a.error_flag, 28); break; }        // O buffer drained
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < PT_KEYS / 16; ++ks) {
+          const unsigned p_off = (ks >> 2) * PT_SUB + (ks & 3) * 32;
+          tc_mma_bf16(tm_o[st], umma_desc_sw128(p_s + p_off), umma_desc_sw128_mn(v_s + st * TILE_BYTES + ks * 2048, PT_SUB),
+                      idesc_pv, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(bar(7 + st));    // V stage free
+        tc_commit(bar(14 + st));   // O_j ready (and P free)
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;              // row of the tile
+    const int qi = q_first + r;
+    const bool valid = qi < qlen;
+    const int p = pos0 + qi;
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    const int lo_last = (a.window > 0 && p_last - a.window + 1 > 0) ? p_last - a.window + 1 : 0;
+    const unsigned lane_off = (unsigned)(quad * 32) << 16;
+    float m = -INFINITY, l = 0.0f, m_acc = -INFINITY;   // m_acc: the maximum the rows of o are scaled to
+    float o[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o[i] = 0.0f;
+    bool ok = true;
+    auto accumulate = [&](int j) -> bool {        // o = o * 2^(m_acc - m_j) + O_j
+      const int st = j & 1;
+      if (!mbar_wait(bar(14 + st), (j >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 29); return false; }
+      tc_fence_after();
+      return true;
+    };
+    float m_tile[2] = {-INFINITY, -INFINITY};      // maximum in force when P of tile j was formed
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j & 1;
+      const int key0 = (tile_lo + j) * PT_KEYS;
+      if (!mbar_wait(bar(9 + st), (j >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 30); ok = false; break; }
+      tc_fence_after();
+      const bool need_mask = (key0 + PT_KEYS - 1 > p_first) || (key0 < lo_last);
+      // pass 1: the row's maximum over this tile (of the raw scores: the scale is positive)
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < PT_KEYS / 32; ++c) {
+        float s[32];
+        tc_ld32f(tm_s[st] + lane_off + c * 32, s);
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            mx = fmaxf(mx, (key <= p && key >= lo) ? s[i] : -INFINITY);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+        }
+      }
+      mx *= a.scale_log2;
+      const float m_new = fmaxf(m, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      // the previous tile's P V must be complete before P is overwritten; take its result in as well
+      if (j > 0) {
+        ok = accumulate(j - 1);
+        if (!ok) break;
+        const int sp = (j - 1) & 1;
+        const float mt = m_tile[sp];
+        const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {      // unrolled: o stays in registers
+          float t[32];
+          tc_ld32f(tm_o[sp] + lane_off + c * 32, t);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * f + t[i];
+        }
+        m_acc = mt;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cta(bar(16 + sp));    // O buffer free
+      }
+      // pass 2: P = 2^(s*c - m) into shared memory (K-major, 128-byte swizzle), row sum in float
+      float sum = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < PT_KEYS / 32; ++c) {
+        float s[32];
+        tc_ld32f(tm_s[st] + lane_off + c * 32, s);
+        unsigned pk[16];
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            s[i] = (key <= p && key >= lo) ? fast_exp2(fmaf(s[i], a.scale_log2, -m_use)) : 0.0f;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = fast_exp2(fmaf(s[i], a.scale_log2, -m_use));
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          sum += s[i] + s[i + 1];
+          __nv_bfloat162 v = __floats2bfloat162_rn(s[i], s[i + 1]);
+          pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
+        }
+        // 32 keys = four 16-byte chunks of this row; chunk index within the 64-key sub-tile is xor-ed with row % 8
+        unsigned char* rowp = p_gen + (c >> 1) * PT_SUB + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
+          *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        }
+      }
+      const float corr = (m == -INFINITY) ? 0.0f : fast_exp2(m - m_use);
+      l = l * corr + sum;
+      m = m_new;
+      m_tile[st] = m_new;
+      // S buffer read, P written: hand both to the tensor cores
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_cta(bar(11 + st));
+        mbar_arrive_cta(bar(13));
+      }
+    }
+    if (ok) {
+      const int j = n_tiles - 1, sp = j & 1;
+      ok = accumulate(j);
+      if (ok) {
+        const float mt = m_tile[sp];
+        const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        bf16* dst = a.out + (size_t)(row0 + qi) * a.ldo + (size_t)h * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          float t[32];
+          tc_ld32f(tm_o[sp] + lane_off + c * 32, t);
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              unsigned w[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float x0 = (o[c * 32 + i + 2 * u] * f + t[i + 2 * u]) * inv;
+                const float x1 = (o[c * 32 + i + 2 * u + 1] * f + t[i + 2 * u + 1]) * inv;
+                __nv_bfloat162 v = __floats2bfloat162_rn(x0, x1);
+                w[u] = *reinterpret_cast<unsigned*>(&v);
+              }
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+// A [rows, cols] bf16 matrix with leading dimension ld, read in boxes of box_rows x 64 columns.
+static int make_map_cols(CUtensorMap* map, const void* ptr, long long rows, int cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  HB_REQUIRE(fn != nullptr, "tensor map: the driver does not provide cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  HB_REQUIRE(r == CUDA_SUCCESS, "tensor map: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+// q: [n_tokens, ldq] with the query heads in its first nh*hd columns; the cache holds n_pages pages.
+extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens, void* out, int ldo, const void* kcache,
+                                            const void* vcache, int n_pages, const int* seq_start, const int* seq_pos0,
+                                            const int* seq_pages, int pages_stride, int n_seqs, int max_q_len, int nh,
+                                            int nkv, int hd, int page_size, float scale, int window, int* error_flag,
+                                            void* stream) {
+  HB_REQUIRE(n_seqs > 0 && max_q_len > 0 && nh > 0 && nkv > 0 && n_tokens > 0 && n_pages > 0, "attention_prefill_tc: sizes must be positive");
+  HB_REQUIRE(hd == 64 || hd == 128, "attention_prefill_tc: head size %d is not 64 or 128", hd);
+  HB_REQUIRE(nh % nkv == 0, "attention_prefill_tc: %d query heads are not a multiple of %d key/value heads", nh, nkv);
+  HB_REQUIRE(page_size % 64 == 0, "attention_prefill_tc: page size %d must be a multiple of 64", page_size);
+  HB_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0,
+             "attention_prefill_tc: queries and output need 16-byte aligned rows");
+  HB_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "attention_prefill_tc: cache must be 16-byte aligned");
+  HB_REQUIRE(nh <= 65535 && n_seqs <= 65535 && window >= 0 && error_flag != nullptr, "attention_prefill_tc: bad arguments");
+  HB_REQUIRE(scale > 0.0f, "attention_prefill_tc: the score scale must be positive");
+  CUtensorMap mq, mk, mv;
+  int rc = make_map_cols(&mq, q, n_tokens, nh * hd, ldq, PT_Q);
+  if (rc) return rc;
+  const long long cache_rows = (long long)n_pages * nkv * page_size;
+  rc = make_map_cols(&mk, kcache, cache_rows, hd, hd, 64);
+  if (rc) return rc;
+  rc = make_map_cols(&mv, vcache, cache_rows, hd, hd, 64);
+  if (rc) return rc;
+  PrefillTcArgs a{(bf16*)out, ldo, seq_start, seq_pos0, seq_pages, pages_stride, nh, nkv, page_size,
+                  scale * 1.4426950408889634f, window, error_flag};
+  dim3 grid(ceil_div(max_q_len, PT_Q), nh, n_seqs);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int smem = 6 * (hd / 64) * PT_SUB + 2 * PT_SUB - (hd / 64) * PT_SUB + 1024 + 256;
+  cudaError_t e;
+  if (hd == 128) {
+    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    hb_launch(attention_prefill_tc_kernel<128>, grid, dim3(PT_THREADS), smem, s, mq, mk, mv, a);
+  } else {
+    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    hb_launch(attention_prefill_tc_kernel<64>, grid, dim3(PT_THREADS), smem, s, mq, mk, mv, a);
+  }
+  HB_CHECK_LAUNCH("attention_prefill_tc");
+  return 0;
+}

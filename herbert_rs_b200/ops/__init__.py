@@ -43,6 +43,8 @@ _SIGS = {
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
 }
@@ -327,6 +329,24 @@ def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pa
          _stream())
 
 
+def attention_prefill_tc(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,
+                         num_heads, num_kv_heads, head_dim, page_size, scale, window) -> None:
+    """The same on tcgen05 tensor cores (head sizes 64 and 128): S and O in tensor memory."""
+    _check(out, torch.bfloat16, "out")
+    _run("hb_attention_prefill_tc_bf16", q.data_ptr(), int(ldq), q.shape[0], out.data_ptr(), out.stride(0),
+         k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], seq_start.data_ptr(), seq_pos0.data_ptr(),
+         seq_pages.data_ptr(), seq_pages.stride(0), int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim,
+         page_size, float(scale), int(window or 0), _error_flag(out.device).data_ptr(), _stream())
+
+
+PREFILL_ATTENTION = os.environ.get("HB_PREFILL_ATTENTION", "tcgen05")   # or "mma": the mma.sync kernel for every size
+
+
+def _prefill_tc_ok(q, ldq, out, head_dim, page_size) -> bool:
+    return (PREFILL_ATTENTION == "tcgen05" and out.dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 64 == 0
+            and ldq % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
 def _prefill_kernel_ok(out, head_dim, page_size) -> bool:
     return out.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and page_size % 64 == 0
 
@@ -349,6 +369,10 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
         buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
         attention_decode(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
                          head_dim, page_size, nsplit, scale, window)
+        return
+    if _prefill_tc_ok(q, ldq, out, head_dim, page_size):
+        attention_prefill_tc(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,
+                             batch.max_q_len, num_heads, num_kv_heads, head_dim, page_size, scale, window)
         return
     if _prefill_kernel_ok(out, head_dim, page_size):
         attention_prefill(q, ldq, out, k_cache, v_cache, batch.seq_start, batch.seq_pos0, seq_pages, batch.n_seqs,

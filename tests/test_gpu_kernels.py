@@ -465,3 +465,37 @@ def test_gemm_stream_refuses_what_it_cannot_do():
         ops.gemm_stream(a, w, torch.empty(65, 32, device="cuda", dtype=torch.bfloat16))
     with pytest.raises(BackendError, match="multiples of 8"):
         ops.gemm_stream(a[:4, :60], w[:, :60], torch.empty(4, 32, device="cuda", dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (4, 4, 64), (6, 3, 128), (2, 1, 64)])
+@pytest.mark.parametrize("window", [None, 70, 200])
+def test_attention_prefill_tcgen05_kernel(nh, nkv, hd, window):
+    for lens, qlens in [([1, 70, 33, 200], [1, 70, 33, 200]), ([300, 130, 64], [100, 1, 64]), ([257], [129]), ([700], [700])]:
+        c = _attention_case(torch.bfloat16, nh, nkv, hd, lens, qlens, window, page=64, seed=14)
+        out = torch.full(c["q"].shape, float("nan"), device="cuda", dtype=torch.bfloat16)
+        starts = torch.tensor(np.concatenate([[0], np.cumsum(qlens)]), dtype=torch.int32)
+        pos0 = torch.tensor([n - q for n, q in zip(lens, qlens)], dtype=torch.int32)
+        ops.attention_prefill_tc(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
+                                 dev(c["table"]), len(lens), max(qlens), nh, nkv, hd, 64, c["scale"], window)
+        ops.check_kernel_errors()
+        close(out, c["ref"], torch.bfloat16)
+
+
+def test_attention_prefill_tcgen05_finds_a_far_key_and_the_windows_edge():
+    nh, nkv, hd = 4, 2, 128
+    lens, qlens = [900, 500], [300, 500]
+    W = 150
+    for window, sharp, hit in [(None, [(0, 870, 3, 2)], True), (None, [(1, 499, 1, 448)], True),
+                               (W, [(1, 400, 0, 400 - W + 1)], True), (W, [(1, 400, 0, 400 - W)], False)]:
+        c = _attention_case(torch.bfloat16, nh, nkv, hd, lens, qlens, window, page=64, sharp=sharp)
+        out = torch.empty(c["q"].shape, device="cuda", dtype=torch.bfloat16)
+        starts = torch.tensor([0, 300, 800], dtype=torch.int32)
+        pos0 = torch.tensor([600, 0], dtype=torch.int32)
+        ops.attention_prefill_tc(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
+                                 dev(c["table"]), 2, 500, nh, nkv, hd, 64, c["scale"], window)
+        ops.check_kernel_errors()
+        close(out, c["ref"], torch.bfloat16)
+        b, qpos, h, kpos = sharp[0]
+        row = (0 if b == 0 else 300) + qpos - int(pos0[b])
+        target = c["vs"][b][kpos, h // (nh // nkv)]
+        assert (((out[row].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit
