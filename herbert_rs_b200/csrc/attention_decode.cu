@@ -44,8 +44,8 @@ struct DecodeArgs {
 template <int HDM>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int hd = a.hd, G = a.nh / a.nkv;
@@ -71,20 +71,17 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
   for (int i = threadIdx.x; i < t1 - t0; i += AD_THREADS) page_ids[i] = pages[(t0 + i) / tiles_per_page];
   __syncthreads();
 
-  // This thread's first 16-byte chunk of a tile and the step to its next one (no division in the loop).
-  const int chunk_r0 = threadIdx.x / chunks_per_row, chunk_c0 = threadIdx.x % chunks_per_row;
-  const int step_r = AD_THREADS / chunks_per_row, step_c = AD_THREADS % chunks_per_row;
-  auto issue = [&](int tile, int stage) {
-    const int page = page_ids[tile - first_tile];
-    const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AD_TILE * hd;
-    const bf16* kg = a.kcache + off;
-    const bf16* vg = a.vcache + off;
-    unsigned char* ks = smem + (size_t)stage * 2 * tile_bytes;
-    unsigned char* vs = ks + tile_bytes;
-    int r = chunk_r0, cc = chunk_c0;
-    while (r < AD_TILE) {
-      cp_async16(ks + r * row_bytes + cc * 16, kg + (size_t)r * hd + cc * 8);
-      cp_async16(vs + r * row_bytes + cc * 16, vg + (size_t)r * hd + cc * 8);
+  // The 16-byte chunks of a tile this thread copies: offsets worked out once, so that issuing a
+  // tile's copies is one add per chunk.
+  constexpr int SLOTS = HDM / 16;            // 64 rows * (hd / 8) chunks / 128 threads, at hd = HDM
+  int g_off[SLOTS], s_off[SLOTS];
+  {
+    int r = threadIdx.x / chunks_per_row, cc = threadIdx.x % chunks_per_row;
+    const int step_r = AD_THREADS / chunks_per_row, step_c = AD_THREADS % chunks_per_row;
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i) {
+      g_off[i] = r * hd + cc * 8;
+      s_off[i] = r < AD_TILE ? r * row_bytes + cc * 16 : -1;
       r += step_r;
       cc += step_c;
       if (cc >= chunks_per_row) {
@@ -92,7 +89,27 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
         ++r;
       }
     }
+  }
+  const unsigned smem_u = (unsigned)__cvta_generic_to_shared(smem);
+  auto issue = [&](int tile, int stage) {
+    const int page = page_ids[tile - first_tile];
+    const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AD_TILE * hd;
+    const bf16* kg = a.kcache + off;
+    const bf16* vg = a.vcache + off;
+    const unsigned ks = smem_u + stage * 2 * tile_bytes;
+    const unsigned vs = ks + tile_bytes;
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i) {
+      if (s_off[i] >= 0) {
+        cp_async16_s(ks + s_off[i], kg + g_off[i]);
+        cp_async16_s(vs + s_off[i], vg + g_off[i]);
+      }
+    }
   };
+  // ldmatrix addresses of this lane inside a tile (the k or d step adds a constant)
+  const int lm = lane >> 3;
+  const unsigned k_lane = (unsigned)((warp * 16 + (lm >> 1) * 8 + (lane & 7)) * row_bytes + (lm & 1) * 16);
+  const unsigned v_lane = (unsigned)((warp * 16 + (lm & 1) * 8 + (lane & 7)) * row_bytes + (lm >> 1) * 16);
 
   // query fragments: rows = heads of the group (g and g + 8), zero beyond G
   unsigned qf[HDM / 16][4];
@@ -132,8 +149,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
     // groups committed so far: S - 1 + it + 1; the group of `tile` is done when at most S - 1 are pending
     if (S == 2) cp_async_wait<1>(); else if (S == 3) cp_async_wait<2>(); else cp_async_wait<3>();
     __syncthreads();
-    const unsigned char* ks = smem + (size_t)(it % S) * 2 * tile_bytes;
-    const unsigned char* vs = ks + tile_bytes;
+    const unsigned ks = smem_u + (unsigned)(it % S) * 2 * tile_bytes;
+    const unsigned vs = ks + tile_bytes;
     const int key0 = tile * AD_TILE + warp * 16;
     if (key0 <= p && key0 + 15 >= lo) {
       // ---- S = Q K^T for this warp's 16 keys -------------------------------------------------
@@ -141,10 +158,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
 #pragma unroll
       for (int kk = 0; kk < HDM / 16; ++kk) {
         if (kk * 16 < hd) {
-          const int mi = lane >> 3;
-          const int key = warp * 16 + (mi >> 1) * 8 + (lane & 7);
           unsigned b0, b1, b2, b3;
-          ldmatrix_x4(b0, b1, b2, b3, ks + key * row_bytes + (kk * 16 + (mi & 1) * 8) * 2);
+          ldmatrix_x4_s(b0, b1, b2, b3, ks + k_lane + kk * 32);
           mma16816(s[0], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
           mma16816(s[1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
         }
@@ -186,16 +201,17 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
       }
       const unsigned pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
       const unsigned pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
-      // ---- O = O * corr + P V -------------------------------------------------------------------
+      // ---- O = O * corr + P V (the rescale is skipped while no maximum of the warp's rows moved) ---
+      const bool rescale = __any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f);
 #pragma unroll
       for (int nd = 0; nd < HDM / 16; ++nd) {
         if (nd * 16 < hd) {
-          o[2 * nd][0] *= corr[0]; o[2 * nd][1] *= corr[0]; o[2 * nd][2] *= corr[1]; o[2 * nd][3] *= corr[1];
-          o[2 * nd + 1][0] *= corr[0]; o[2 * nd + 1][1] *= corr[0]; o[2 * nd + 1][2] *= corr[1]; o[2 * nd + 1][3] *= corr[1];
-          const int mi = lane >> 3;
-          const int key = warp * 16 + (mi & 1) * 8 + (lane & 7);
+          if (rescale) {
+            o[2 * nd][0] *= corr[0]; o[2 * nd][1] *= corr[0]; o[2 * nd][2] *= corr[1]; o[2 * nd][3] *= corr[1];
+            o[2 * nd + 1][0] *= corr[0]; o[2 * nd + 1][1] *= corr[0]; o[2 * nd + 1][2] *= corr[1]; o[2 * nd + 1][3] *= corr[1];
+          }
           unsigned b0, b1, b2, b3;
-          ldmatrix_x4_trans(b0, b1, b2, b3, vs + key * row_bytes + (nd * 16 + (mi >> 1) * 8) * 2);
+          ldmatrix_x4_trans_s(b0, b1, b2, b3, vs + v_lane + nd * 32);
           mma16816(o[2 * nd], pa0, pa1, pa2, pa3, b0, b1);
           mma16816(o[2 * nd + 1], pa0, pa1, pa2, pa3, b2, b3);
         }
@@ -252,8 +268,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
 // out[b][h][:] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int h = blockIdx.x, b = blockIdx.y;
   const size_t base = ((size_t)b * nh + h) * nsplit;
   float mm = -INFINITY;

@@ -45,8 +45,8 @@ struct PrefillArgs {
 template <int HDM>
 __global__ void __launch_bounds__(AP_THREADS) attention_prefill_kernel(PrefillArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int row0 = a.seq_start[b], qlen = a.seq_start[b + 1] - row0;
   if (qt * AP_QTILE >= qlen) return;

@@ -80,7 +80,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   auto bar = [&](int i) { return bars + i * 8; };
   volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + (bars - base) + 18 * 8);
 
-  pdl_launch();
   // the last query tiles have the longest key ranges: they go first, the short ones fill the tail
   const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int row0 = a.seq_start[b], qlen = a.seq_start[b + 1] - row0;
@@ -109,6 +108,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   tc_fence_after();
   pdl_wait();
+  pdl_launch();
   const unsigned tmem = *tmem_slot;
   const unsigned tm_s[2] = {tmem, tmem + 128u};
   const unsigned tm_o[2] = {tmem + 256u, tmem + 256u + (unsigned)HD};

@@ -34,8 +34,8 @@ struct AttnArgs {
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_simt_kernel(AttnArgs a) {
   __shared__ float qs[ATT_WARPS][ATT_MAX_HD];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * ATT_WARPS + warp;
   if (unit >= (long long)a.n_tokens * a.nh) return;

@@ -15,8 +15,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int hidden, int vocab) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * hidden;
@@ -50,8 +50,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                T* __restrict__ out, const int* __restrict__ rows, int dim, float eps) {
   __shared__ float red[32];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
   float s = 0.0f;
@@ -83,8 +83,8 @@ extern "C" int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, T* __restrict__ out, int ldo,
                               int inter, int interleave) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= inter) return;
@@ -146,8 +146,8 @@ struct QkvCacheArgs {
 
 template <typename T>
 __global__ void qk_norm_rope_cache_kernel(QkvCacheArgs a) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int heads_total = a.nh + 2 * a.nkv;
@@ -237,8 +237,8 @@ extern "C" int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* 
 // residual[t, :] += y[t, :] (for parts that cannot fuse the sum into their last product)
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ res, const T* __restrict__ y, int ld, int dim) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < dim) res[(size_t)t * dim + i] += to_f32(y[(size_t)t * ld + i]);

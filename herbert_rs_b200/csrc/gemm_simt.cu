@@ -20,8 +20,8 @@ gemm_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int 
                  int M, int N, int K) {
   __shared__ float As[TK][TM + 4];
   __shared__ float Ws[TK][TN + 4];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
   const int tx = tid & 15, ty = tid >> 4;  // outputs: rows ty*4.., cols tx*4..

@@ -67,9 +67,9 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
       rb[u] = (ok && hi_ok) ? ld_stream16(w_hi + k) : zero;
     }
   };
-  pdl_launch();
   load_w(warp, wa, wb);
   pdl_wait();
+  pdl_launch();
   for (int ks0 = warp; ks0 < ksteps; ks0 += SK_WARPS * UNROLL) {
     load_w(ks0 + SK_WARPS * UNROLL, na, nb);
 #pragma unroll

@@ -83,11 +83,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)slots)), "r"(a.tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  pdl_launch();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   pdl_wait();
+  pdl_launch();
   const unsigned tmem_acc = slots[0];
 
   if (warp == 0) {

@@ -77,11 +77,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  pdl_launch();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   pdl_wait();
+  pdl_launch();
   const unsigned tmem_base = *tmem_slot;
 
   // Tiles in the order m fastest: CTAs that run side by side share the same slab of W in L2.

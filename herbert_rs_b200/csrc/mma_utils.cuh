@@ -28,3 +28,14 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
+
+// The same with shared-memory addresses already converted (32-bit), for loops that run often.
+__device__ __forceinline__ void cp_async16_s(unsigned smem_addr, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gmem));
+}
+__device__ __forceinline__ void ldmatrix_x4_s(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned s) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans_s(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned s) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}

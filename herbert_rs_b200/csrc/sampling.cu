@@ -26,8 +26,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
   __shared__ float sv[32];
   __shared__ int si[32];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const float* row = logits + (size_t)blockIdx.x * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -80,8 +80,8 @@ __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, int ld, int vocab, float* __restrict__ pv, int* __restrict__ pi) {
   __shared__ float sv[8];
   __shared__ int si[8];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int chunk = blockIdx.x, row = blockIdx.y;
   const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
   const int beg = chunk * per, end = min(vocab, beg + per);
@@ -123,8 +123,8 @@ argmax_partial_kernel(const float* __restrict__ logits, int ld, int vocab, float
 
 __global__ void __launch_bounds__(32)
 argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int row = blockIdx.x, lane = threadIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -194,8 +194,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature, int top_k,
               float top_p, const float* __restrict__ uniforms, int* __restrict__ out) {
   __shared__ SampleShared sh;
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int tid = threadIdx.x;
   const float* row = logits + (size_t)blockIdx.x * ld;
 
