@@ -12,6 +12,8 @@
 // Warps, then splits, are merged with the usual rescaling; every split writes (m, l, O) to
 // scratch memory and a second kernel combines them:  out = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s.
 // Keys visible to the query at position p: lo..p, lo = max(0, p - window + 1) if window > 0.
+#include <stdlib.h>
+
 #include "api.h"
 #include "common.cuh"
 #include "mma_utils.cuh"
@@ -317,7 +319,12 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   HB_REQUIRE((long long)pages_stride * (page_size / AD_TILE) <= (long long)AD_MAX_TILES * nsplit,
              "attention_decode: %d pages per sequence in %d splits exceed %d tiles per CTA", pages_stride, nsplit, AD_MAX_TILES);
   cudaStream_t s = (cudaStream_t)stream;
-  int stages = 3;
+  static int want_stages = 0;
+  if (want_stages == 0) {
+    const char* e = getenv("HB_DECODE_STAGES");      // tuning knob: 2 or 3 (default 3 where it fits twice per SM)
+    want_stages = (e && (e[0] == '2' || e[0] == '3')) ? e[0] - '0' : 3;
+  }
+  int stages = want_stages;
   if (decode_smem_bytes(hd, stages) > 110 * 1024) stages = 2;
   const int smem = decode_smem_bytes(hd, stages);
   float* part_o = scratch;
