@@ -65,10 +65,61 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<T>((xr[i] * inv) * w[i]);
 }
 
+// The same with the row held in registers between the two passes and 16-byte loads: for rows of
+// at most 4 * RN_VEC * blockDim.x floats whose length is a multiple of 4.
+#define RN_VEC 4
+__device__ __forceinline__ void store4(float* o, float4 v) { *reinterpret_cast<float4*>(o) = v; }
+__device__ __forceinline__ void store4(bf16* o, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<unsigned*>(&a);
+  u.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(o) = u;
+}
+template <typename T>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                   T* __restrict__ out, const int* __restrict__ rows, int dim, float eps) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * dim);
+  const float4* wv = reinterpret_cast<const float4*>(w);
+  const int nvec = dim >> 2;
+  float4 v[RN_VEC];
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < RN_VEC; ++i) {
+    const int k = threadIdx.x + i * blockDim.x;
+    v[i] = k < nvec ? xr[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  s = block_sum(s, red);
+  const float inv = 1.0f / sqrtf(s / (float)dim + eps);
+  T* o = out + (size_t)r * dim;
+#pragma unroll
+  for (int i = 0; i < RN_VEC; ++i) {
+    const int k = threadIdx.x + i * blockDim.x;
+    if (k < nvec) {
+      const float4 ww = wv[k];
+      store4(o + 4 * k, make_float4((v[i].x * inv) * ww.x, (v[i].y * inv) * ww.y, (v[i].z * inv) * ww.z, (v[i].w * inv) * ww.w));
+    }
+  }
+}
+
 extern "C" int hb_rmsnorm(int dtype, const float* x, const float* w, void* out, const int* rows,
                           int n_rows, int dim, float eps, void* stream) {
   HB_REQUIRE(n_rows > 0 && dim > 0, "rmsnorm: sizes must be positive");
   int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  if (dim % 4 == 0 && dim <= 4 * RN_VEC * threads && aligned) {
+    if (dtype == HB_F32)
+      hb_launch(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x, w, (float*)out, rows, dim, eps);
+    else
+      hb_launch(rmsnorm_vec_kernel<bf16>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x, w, (bf16*)out, rows, dim, eps);
+    HB_CHECK_LAUNCH("rmsnorm");
+    return 0;
+  }
   if (dtype == HB_F32)
     hb_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x, w, (float*)out, rows, dim, eps);
   else
@@ -208,6 +259,92 @@ __global__ void qk_norm_rope_cache_kernel(QkvCacheArgs a) {
   }
 }
 
+// The common case made cheap: every head is rotated over its whole width (or not at all is not
+// handled here), head size a multiple of 4 up to 256.  One block per token; its 8 warps walk the
+// token's heads, so the position, the page, the cos/sin values and the norm weights a lane needs
+// are fetched once per token instead of once per head, and loads and stores move 2 elements.
+__device__ __forceinline__ float2 ld2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 ld2(const bf16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void st2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void st2(bf16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qk_norm_rope_cache_fast_kernel(QkvCacheArgs a) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hd = a.hd, half = hd >> 1;
+  const int pos = a.tok_pos[t], b = a.tok_seq[t];
+  const int trow = pos < a.table_rows ? pos : a.table_rows - 1;
+  const int page = a.write_cache ? a.seq_pages[(size_t)b * a.pages_stride + pos / a.page_size] : 0;
+  const int j[2] = {2 * lane, 2 * lane + 64};
+  float2 c[2], sn[2], qlo[2], qhi[2], klo[2], khi[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (j[i] < half) {
+      c[i] = ld2(a.cos_tab + (size_t)trow * half + j[i]);
+      sn[i] = ld2(a.sin_tab + (size_t)trow * half + j[i]);
+      if (a.qw) {
+        qlo[i] = ld2(a.qw + j[i]); qhi[i] = ld2(a.qw + j[i] + half);
+        klo[i] = ld2(a.kw + j[i]); khi[i] = ld2(a.kw + j[i] + half);
+      }
+    }
+  }
+  T* row = (T*)a.qkv + (size_t)t * a.ld;
+  const int heads_total = a.nh + 2 * a.nkv;
+  for (int h = warp; h < heads_total; h += 8) {
+    T* x = row + (size_t)h * hd;
+    const bool is_q = h < a.nh, is_v = h >= a.nh + a.nkv;
+    T* dst = x;
+    if (!is_q) {
+      if (!a.write_cache) continue;
+      const int kvh = is_v ? h - a.nh - a.nkv : h - a.nh;
+      T* basep = (T*)(is_v ? a.vcache : a.kcache);
+      dst = basep + (((size_t)page * a.nkv + kvh) * a.page_size + (pos % a.page_size)) * hd;
+    }
+    if (is_v) {
+      for (int d = 2 * lane; d < hd; d += 64) {
+        const float2 v = ld2(x + d);
+        st2(dst + d, v.x, v.y);
+      }
+      continue;
+    }
+    float2 lo[2], hi[2];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (j[i] < half) {
+        lo[i] = ld2(x + j[i]);
+        hi[i] = ld2(x + j[i] + half);
+        ss += lo[i].x * lo[i].x + lo[i].y * lo[i].y + hi[i].x * hi[i].x + hi[i].y * hi[i].y;
+      }
+    }
+    if (a.qw) {
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)hd + a.eps);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (j[i] < half) {
+          const float2 wl = is_q ? qlo[i] : klo[i], wh = is_q ? qhi[i] : khi[i];
+          lo[i].x = (lo[i].x * inv) * wl.x; lo[i].y = (lo[i].y * inv) * wl.y;
+          hi[i].x = (hi[i].x * inv) * wh.x; hi[i].y = (hi[i].y * inv) * wh.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (j[i] < half) {
+        st2(dst + j[i], lo[i].x * c[i].x - hi[i].x * sn[i].x, lo[i].y * c[i].y - hi[i].y * sn[i].y);
+        st2(dst + j[i] + half, lo[i].x * sn[i].x + hi[i].x * c[i].x, lo[i].y * sn[i].y + hi[i].y * c[i].y);
+      }
+    }
+  }
+}
+
 extern "C" int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* qw, const float* kw,
                                      float eps, const float* cos_tab, const float* sin_tab, int rot,
                                      int table_rows, const int* tok_seq, const int* tok_pos,
@@ -221,6 +358,19 @@ extern "C" int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* 
   HB_REQUIRE(ld >= (nh + 2 * nkv) * hd, "qk_norm_rope_cache: leading dimension %d < %d", ld, (nh + 2 * nkv) * hd);
   QkvCacheArgs a{qkv, ld, qw, kw, eps, cos_tab, sin_tab, rot, table_rows, tok_seq, tok_pos, seq_pages,
                  pages_stride, kcache, vcache, n_tokens, nh, nkv, hd, page_size, write_cache};
+  const int esz = dtype == HB_F32 ? 4 : 2;
+  const bool fast = cos_tab != nullptr && rot == hd && hd % 4 == 0 && hd <= 256 && ld % 2 == 0 &&
+                    ((uintptr_t)qkv % (2 * esz)) == 0 && ((uintptr_t)kcache % (2 * esz)) == 0 &&
+                    ((uintptr_t)vcache % (2 * esz)) == 0 && ((uintptr_t)cos_tab & 7) == 0 && ((uintptr_t)sin_tab & 7) == 0 &&
+                    (qw == nullptr || (((uintptr_t)qw & 7) == 0 && ((uintptr_t)kw & 7) == 0));
+  if (fast) {
+    if (dtype == HB_F32)
+      hb_launch(qk_norm_rope_cache_fast_kernel<float>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, a);
+    else
+      hb_launch(qk_norm_rope_cache_fast_kernel<bf16>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, a);
+    HB_CHECK_LAUNCH("qk_norm_rope_cache");
+    return 0;
+  }
   const long long units = (long long)n_tokens * (nh + 2 * nkv);
   const int wpb = 8;
   const long long blocks = ceil_div_ll(units, wpb);
