@@ -20,9 +20,9 @@ from . import lib as _libmod
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64
-# Which kernel serves products of at most 64 activation rows: "stream" (TMA + tcgen05, K slices) or
-# "skinny" (mma.sync with direct global loads).  Both are kept and tested; measurements decide.
-DECODE_GEMM = "skinny"
+# Which kernel serves products of at most 64 activation rows: "stream" (TMA + tcgen05, K slices),
+# "skinny" (mma.sync with direct global loads), or "auto" (by shape, see _decode_gemm).
+DECODE_GEMM = os.environ.get("HB_DECODE_GEMM", "auto")
 
 _SIGS = {
     "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -260,6 +260,31 @@ def _tcgen05_ok(a, w) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+_stream_plan_fn = None
+
+
+def _stream_uncut(M: int, N: int, K: int) -> bool:
+    """True if the streaming tcgen05 kernel would run this product without cutting K (enough tiles
+    of 128 weight rows to fill the GPU), the case in which it has no reduction to pay for."""
+    global _stream_plan_fn
+    if _stream_plan_fn is None:
+        _stream_plan_fn = _libmod.load().hb_gemm_stream_scratch_floats
+        _stream_plan_fn.argtypes = [c_int, c_int, c_int]
+        _stream_plan_fn.restype = ctypes.c_longlong
+    return _stream_plan_fn(M, N, K) == 0
+
+
+def _decode_gemm(a, w):
+    """Which kernel multiplies at most 64 activation rows.  Measured at Qwen3-8B shapes: the
+    mma.sync kernel wins up to 16 rows and wherever K would have to be cut; from 17 rows on its
+    activation reads through L1 dominate and the TMA/tcgen05 kernel is 2-3x faster when K is uncut."""
+    if DECODE_GEMM == "stream":
+        return gemm_stream
+    if DECODE_GEMM == "auto" and a.shape[0] > 16 and _stream_uncut(a.shape[0], w.shape[0], a.shape[1]):
+        return gemm_stream
+    return gemm_skinny
+
+
 def _skinny_ok(a, w) -> bool:
     return (a.dtype == torch.bfloat16 and a.shape[0] <= SKINNY_MAX_ROWS and a.shape[1] % 8 == 0
             and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -273,7 +298,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_
     bfloat16: tensor-core kernels where their size rules hold, else the any-shape kernel).
     """
     if _skinny_ok(a, w):
-        (gemm_stream if DECODE_GEMM == "stream" else gemm_skinny)(a, w, c, epilogue)
+        _decode_gemm(a, w)(a, w, c, epilogue)
     elif _tcgen05_ok(a, w):
         gemm_tcgen05(a, w, c, epilogue)
     else:
@@ -284,7 +309,7 @@ def gemm_swiglu(a: torch.Tensor, wgu: torch.Tensor, out: torch.Tensor, interleav
     """out = silu(gate) * up with [gate | up] = a @ wgu.T.  Fused into the product where a kernel can;
     otherwise the product goes to `scratch(shape, dtype)` and the SwiGLU kernel follows."""
     if interleave == 8 and _skinny_ok(a, wgu):
-        (gemm_stream if DECODE_GEMM == "stream" else gemm_skinny)(a, wgu, out, EPI_SWIGLU)
+        _decode_gemm(a, wgu)(a, wgu, out, EPI_SWIGLU)
         return
     if interleave == 8 and _tcgen05_ok(a, wgu):
         gemm_tcgen05(a, wgu, out, EPI_SWIGLU)
