@@ -39,10 +39,10 @@ void hb_set_error(const char* fmt, ...);
 // writes anything the predecessor may still read.  pdl_launch() tells the hardware that the next
 // kernel may start its own prologue; it is called after pdl_wait(), so that at most one kernel
 // ahead of the running one sits on the SMs (called before, the whole chain piles up there).  Both are no-ops for a kernel launched without the attribute.
-int hb_pdl_enabled(void);
+int hb_pdl_enabled(void);   // 0 off, 1 every kernel, 2 only the launches that ask for it (hb_launch_pdl)
 template <typename... KArgs, typename... Args>
-static inline cudaError_t hb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                    Args&&... args) {
+static inline cudaError_t hb_launch_ex(int want_pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -52,8 +52,20 @@ static inline cudaError_t hb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = hb_pdl_enabled() ? 1 : 0;
+  const int mode = hb_pdl_enabled();
+  cfg.numAttrs = (mode == 1 || (mode == 2 && want_pdl)) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t hb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  return hb_launch_ex(0, kernel, grid, block, smem, stream, static_cast<KArgs>(args)...);
+}
+// For kernels whose prologue is worth starting early (weight loads that do not depend on the predecessor).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t hb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        Args&&... args) {
+  return hb_launch_ex(1, kernel, grid, block, smem, stream, static_cast<KArgs>(args)...);
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -20,5 +20,5 @@ extern "C" int hb_abi_version(void) { return 1; }
 // Programmatic dependent launch between consecutive kernels of a stream (see common.cuh).
 static int g_pdl = 0;   // measured slower than plain stream order inside captured decode graphs: off unless asked for
 int hb_pdl_enabled(void) { return g_pdl; }
-extern "C" void hb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+extern "C" void hb_set_pdl(int mode) { g_pdl = (mode >= 0 && mode <= 2) ? mode : 0; }
 extern "C" int hb_get_pdl(void) { return g_pdl; }

@@ -135,10 +135,10 @@ static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C
                          int epi, cudaStream_t s) {
   const unsigned grid = (unsigned)ceil_div(N, 16);
   switch (epi) {
-    case HB_EPI_STORE: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_STORE_F32: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_RESIDUAL: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_SWIGLU: hb_launch(gemm_skinny_kernel<NT, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE_F32: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_RESIDUAL: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_SWIGLU: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
     default: HB_FAIL(2, "gemm_skinny: unknown epilogue %d", epi);
   }
   HB_CHECK_LAUNCH("gemm_skinny");
