@@ -12,6 +12,8 @@
 // The activation rows (at most 64 x K) come through L1/L2.  Partial sums of the 8 warps meet in
 // shared memory; the epilogue stores, adds into the float residual stream, or applies SwiGLU to
 // rows stored as 8 gate rows followed by the 8 up rows of the same channels.
+#include <stdlib.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -34,37 +36,53 @@ __device__ __forceinline__ void mma_bf16_16816(float* d, unsigned a0, unsigned a
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, int UNROLL, int EPI>
+// NT: 8-token tiles (M <= 8 * NT).  RG: groups of 16 weight rows per CTA; a warp multiplies each
+// activation fragment it loads with RG weight fragments, so the activation traffic per weight byte
+// falls with RG (with 16 rows per CTA and 8 tokens it is half the weight traffic).  UNROLL: k steps
+// of 32 per batch of loads; two batches are in flight.
+template <int NT, int RG, int UNROLL, int EPI>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, void* Cv, int ldc,
                    int M, int N, int K) {
-  __shared__ float red[SK_WARPS][16][NT * 8 + 1];
+  __shared__ float red[SK_WARPS][16 * RG][NT * 8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * 16;
-  const int r_lo = row0 + g, r_hi = row0 + g + 8;
-  const bf16* w_lo = W + (size_t)(r_lo < N ? r_lo : 0) * ldw;
-  const bf16* w_hi = W + (size_t)(r_hi < N ? r_hi : 0) * ldw;
-  const bool lo_ok = r_lo < N, hi_ok = r_hi < N;
+  const int row0 = blockIdx.x * 16 * RG;
+  const bf16* w_lo[RG];
+  const bf16* w_hi[RG];
+  bool lo_ok[RG], hi_ok[RG];
+#pragma unroll
+  for (int rg = 0; rg < RG; ++rg) {
+    const int r_lo = row0 + rg * 16 + g, r_hi = r_lo + 8;
+    lo_ok[rg] = r_lo < N;
+    hi_ok[rg] = r_hi < N;
+    w_lo[rg] = W + (size_t)(lo_ok[rg] ? r_lo : 0) * ldw;
+    w_hi[rg] = W + (size_t)(hi_ok[rg] ? r_hi : 0) * ldw;
+  }
 
-  float acc[NT][4];
+  float acc[RG][NT][4];
 #pragma unroll
-  for (int i = 0; i < NT; ++i)
+  for (int rg = 0; rg < RG; ++rg)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[rg][i][j] = 0.0f;
 
   const int ksteps = (K + 31) >> 5;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   // Weights never depend on the previous kernel: the first batch of loads is issued before the
   // wait on it, and every later batch is issued before the batch in hand is multiplied.
-  uint4 wa[UNROLL], wb[UNROLL], na[UNROLL], nb[UNROLL];
-  auto load_w = [&](int ks0, uint4* ra, uint4* rb) {
+  uint4 wa[RG][UNROLL], wb[RG][UNROLL], na[RG][UNROLL], nb[RG][UNROLL];
+  auto load_w = [&](int ks0, uint4 (*ra)[UNROLL], uint4 (*rb)[UNROLL]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (ks0 + u * SK_WARPS) * 32 + 8 * t;
       const bool ok = k < K;  // K is a multiple of 8: a lane's 8 elements are all inside or all outside
-      ra[u] = (ok && lo_ok) ? ld_stream16(w_lo + k) : zero;
-      rb[u] = (ok && hi_ok) ? ld_stream16(w_hi + k) : zero;
+#pragma unroll
+      for (int rg = 0; rg < RG; ++rg) {
+        ra[rg][u] = (ok && lo_ok[rg]) ? ld_stream16(w_lo[rg] + k) : zero;
+        rb[rg][u] = (ok && hi_ok[rg]) ? ld_stream16(w_hi[rg] + k) : zero;
+      }
     }
   };
   load_w(warp, wa, wb);
@@ -81,42 +99,49 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
         const int m = nt * 8 + g;
         uint4 x = zero;
         if (ok && m < M) x = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k));
-        mma_bf16_16816(acc[nt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, x.x, x.y);
-        mma_bf16_16816(acc[nt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, x.z, x.w);
+#pragma unroll
+        for (int rg = 0; rg < RG; ++rg) {
+          mma_bf16_16816(acc[rg][nt], wa[rg][u].x, wb[rg][u].x, wa[rg][u].y, wb[rg][u].y, x.x, x.y);
+          mma_bf16_16816(acc[rg][nt], wa[rg][u].z, wb[rg][u].z, wa[rg][u].w, wb[rg][u].w, x.z, x.w);
+        }
       }
     }
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      wa[u] = na[u];
-      wb[u] = nb[u];
-    }
-  }
-  // accumulator layout: acc[nt][0..1] = (weight row g,   tokens nt*8 + 2t, 2t+1); [2..3] = row g+8
+    for (int rg = 0; rg < RG; ++rg)
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    red[warp][g][nt * 8 + 2 * t] = acc[nt][0];
-    red[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
-    red[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2];
-    red[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+      for (int u = 0; u < UNROLL; ++u) {
+        wa[rg][u] = na[rg][u];
+        wb[rg][u] = nb[rg][u];
+      }
   }
+  // accumulator layout: acc[..][nt][0..1] = (weight row g, tokens nt*8 + 2t, 2t+1); [2..3] = row g+8
+#pragma unroll
+  for (int rg = 0; rg < RG; ++rg)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      red[warp][rg * 16 + g][nt * 8 + 2 * t] = acc[rg][nt][0];
+      red[warp][rg * 16 + g][nt * 8 + 2 * t + 1] = acc[rg][nt][1];
+      red[warp][rg * 16 + g + 8][nt * 8 + 2 * t] = acc[rg][nt][2];
+      red[warp][rg * 16 + g + 8][nt * 8 + 2 * t + 1] = acc[rg][nt][3];
+    }
   __syncthreads();
   if (EPI == HB_EPI_SWIGLU) {
-    // 8 channels x (NT*8) tokens; output column = block * 8 + channel
-    for (int idx = threadIdx.x; idx < 8 * NT * 8; idx += SK_THREADS) {
-      const int ch = idx & 7, m = idx >> 3;
+    // per group of 16 rows: 8 channels x (NT*8) tokens; output column = (row group) * 8 + channel
+    for (int idx = threadIdx.x; idx < RG * 8 * NT * 8; idx += SK_THREADS) {
+      const int ch = idx & 7, rg = (idx >> 3) % RG, m = idx / (8 * RG);
       if (m >= M) continue;
       float gate = 0.0f, up = 0.0f;
 #pragma unroll
       for (int w = 0; w < SK_WARPS; ++w) {
-        gate += red[w][ch][m];
-        up += red[w][ch + 8][m];
+        gate += red[w][rg * 16 + ch][m];
+        up += red[w][rg * 16 + ch + 8][m];
       }
-      const int col = blockIdx.x * 8 + ch;
-      if (row0 + ch + 8 < N) ((bf16*)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
+      const int col = (blockIdx.x * RG + rg) * 8 + ch;
+      if (row0 + rg * 16 + ch + 8 < N) ((bf16*)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
     }
   } else {
-    for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += SK_THREADS) {
-      const int r = idx & 15, m = idx >> 4;
+    for (int idx = threadIdx.x; idx < 16 * RG * NT * 8; idx += SK_THREADS) {
+      const int r = idx % (16 * RG), m = idx / (16 * RG);
       const int n = row0 + r;
       if (m >= M || n >= N) continue;
       float s = 0.0f;
@@ -130,15 +155,15 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
   }
 }
 
-template <int NT, int UNROLL>
+template <int NT, int RG, int UNROLL>
 static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C, int ldc, int M, int N, int K,
                          int epi, cudaStream_t s) {
-  const unsigned grid = (unsigned)ceil_div(N, 16);
+  const unsigned grid = (unsigned)ceil_div(N, 16 * RG);
   switch (epi) {
-    case HB_EPI_STORE: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_STORE_F32: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_RESIDUAL: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_SWIGLU: hb_launch_pdl(gemm_skinny_kernel<NT, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE_F32: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_RESIDUAL: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_SWIGLU: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
     default: HB_FAIL(2, "gemm_skinny: unknown epilogue %d", epi);
   }
   HB_CHECK_LAUNCH("gemm_skinny");
@@ -156,8 +181,18 @@ extern "C" int hb_gemm_skinny_bf16(const void* A, int lda, const void* W, int ld
   cudaStream_t s = (cudaStream_t)stream;
   const bf16* a = (const bf16*)A;
   const bf16* w = (const bf16*)W;
-  if (M <= 8) return skinny_launch<1, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
-  if (M <= 16) return skinny_launch<2, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
-  if (M <= 32) return skinny_launch<4, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
-  return skinny_launch<8, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+  static int rg_knob = -1;
+  if (rg_knob < 0) {
+    const char* e = getenv("HB_SKINNY_RG");        // tuning knob: 1 or 2 row groups per CTA; default by shape
+    rg_knob = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+  }
+  // Two row groups per CTA halve the activation traffic; worth it once there are several tokens
+  // and enough rows that the grid still fills the GPU.
+  const bool two = rg_knob ? rg_knob == 2 : (M > 1 && N >= 8192);
+  if (M <= 8) return two ? skinny_launch<1, 2, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s)
+                         : skinny_launch<1, 1, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+  if (M <= 16) return two ? skinny_launch<2, 2, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s)
+                          : skinny_launch<2, 1, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+  if (M <= 32) return skinny_launch<4, 1, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+  return skinny_launch<8, 1, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
 }

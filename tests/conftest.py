@@ -37,6 +37,6 @@ def model_dirs(tmp_path_factory):
     out = {}
     for name, cfg in TINY.items():
         d = tmp_path_factory.mktemp(f"tiny_{name}")
-        hb.write_random_model(cfg, str(d), seed={"A": 11, "B": 22, "C": 33}.get(name, 5))
+        hb.write_random_model(cfg, str(d), seed={"A": 11, "B": 22, "C": 33, "D": 44}.get(name, 5))
         out[name] = str(d)
     return out

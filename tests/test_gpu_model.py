@@ -40,19 +40,19 @@ def sharp_dir(tmp_path_factory, model_dirs):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_each_request_alone_and_whole(model_dirs, plain, name, dtype):
     eng = engine_for(model_dirs[name], dtype)
     rng = np.random.default_rng(5)
     V, P = plain[name].cfg["V"], plain[name].cfg["P"]
-    for n in [1, 2, 13, 64, 65, min(P, 200)]:
+    for n in [1, 2, 13, 64, 65, min(P, 200)] + ([300] if name == "D" else []):
         ids = random_ids(rng, V, n)
         assert_close(replay_whole(eng, ids), plain[name].logits(ids).numpy(), dtype, f"{name} whole n={n}")
     eng.cache.check()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_tokens_one_by_one(model_dirs, plain, name, dtype):
     eng = engine_for(model_dirs[name], dtype)
     rng = np.random.default_rng(6)
@@ -65,7 +65,7 @@ def test_last_32_tokens_one_by_one(model_dirs, plain, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "Bsharp"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "Bsharp"])
 def test_unequal_batches_one_after_another(model_dirs, sharp_dir, plain, name, dtype):
     d = sharp_dir if name == "Bsharp" else model_dirs[name]
     pm = PlainModel(d) if name == "Bsharp" else plain[name]

@@ -3,7 +3,14 @@ option: layers, width, heads and groups, head size, feed-forward width, vocabula
 base, norm eps, context, tied or separate head, and (C) windows per layer, a rotated width
 below the head size and an explicit attention scale.  Several sizes are no powers of two."""
 
+# "D" is not tiny in its head size: 128, the size the tensor-memory (tcgen05) attention and product
+# kernels serve, so that those kernels are also compared with the plain implementation inside a
+# whole model and in every way of cutting the work.
 TINY = {
+    "D": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=1000, hidden_size=512,
+              num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+              intermediate_size=1536, rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=1024,
+              tie_word_embeddings=False, eos_token_id=999),
     "A": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=256, hidden_size=64,
               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
               intermediate_size=128, rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=128,
