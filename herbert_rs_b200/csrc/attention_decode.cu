@@ -292,6 +292,15 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
   }
 }
 
+// Second stage alone, for kernels that write the same (m, l, o) partials (m in natural-log units).
+int hb_attention_decode_combine(const float* part_o, const float* part_ml, void* out, int ldo, int n_seqs, int nh, int hd,
+                                int nsplit, cudaStream_t s) {
+  dim3 cgrid(nh, n_seqs);
+  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
+  HB_CHECK_LAUNCH("attention_decode_combine");
+  return 0;
+}
+
 static int decode_smem_bytes(int hd, int stages) {
   const int pipeline = stages * 2 * AD_TILE * (hd * 2 + 16);
   const int merge = (2 * AD_WARPS * 16 + AD_WARPS * 16 * hd) * 4;

@@ -23,33 +23,6 @@
 #define PT_KEYS 128     // keys per tile
 #define PT_SUB (128 * 128)   // bytes of one [128 rows][64 columns] swizzled sub-tile
 
-__device__ __forceinline__ void mbar_arrive_cta(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// MN-major operand with the 128-byte swizzle: 64 contiguous elements of the MN axis per 128-byte row,
-// rows are consecutive K indices; lbo = bytes between 64-element MN blocks, 1024 between groups of 8 rows.
-__device__ __forceinline__ unsigned long long umma_desc_sw128_mn(unsigned smem_addr, unsigned lbo_bytes) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
-  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= (unsigned long long)1 << 46;
-  d |= (unsigned long long)2 << 61;
-  return d;
-}
-// 2^x by the hardware's approximation (about 2 ulp in float); the result is rounded to bfloat16 next.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ void tc_ld32f(unsigned taddr, float* r) {
-  unsigned u[32];
-  tc_ld32(taddr, u);
-#pragma unroll
-  for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
-}
-
 struct PrefillTcArgs {
   bf16* out;
   int ldo;
@@ -331,21 +304,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
-}
-
-// A [rows, cols] bf16 matrix with leading dimension ld, read in boxes of box_rows x 64 columns.
-static int make_map_cols(CUtensorMap* map, const void* ptr, long long rows, int cols, long long ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  HB_REQUIRE(fn != nullptr, "tensor map: the driver does not provide cuTensorMapEncodeTiled");
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  HB_REQUIRE(r == CUDA_SUCCESS, "tensor map: cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return 0;
 }
 
 // q: [n_tokens, ldq] with the query heads in its first nh*hd columns; the cache holds n_pages pages.

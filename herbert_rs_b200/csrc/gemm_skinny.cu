@@ -43,31 +43,29 @@ __device__ __forceinline__ void mma_bf16_16816(float* d, unsigned a0, unsigned a
 template <int NT, int RG, int UNROLL, int EPI>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, void* Cv, int ldc,
-                   int M, int N, int K) {
+                   int M, int N, int K, int units_per_cta) {
+  // A unit is 16 * RG weight rows.  A CTA walks units_per_cta consecutive units, so that the grid is
+  // no larger than what the GPU holds at once (no partly filled last wave) and every CTA streams
+  // the same number of bytes; the first weight loads of the next unit are issued before the
+  // current unit's partial sums are combined.
   __shared__ float red[SK_WARPS][16 * RG][NT * 8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * 16 * RG;
+  const int n_units = (N + 16 * RG - 1) / (16 * RG);
+  int unit = blockIdx.x * units_per_cta;
   const bf16* w_lo[RG];
   const bf16* w_hi[RG];
   bool lo_ok[RG], hi_ok[RG];
+  auto set_rows = [&](int u) {
 #pragma unroll
-  for (int rg = 0; rg < RG; ++rg) {
-    const int r_lo = row0 + rg * 16 + g, r_hi = r_lo + 8;
-    lo_ok[rg] = r_lo < N;
-    hi_ok[rg] = r_hi < N;
-    w_lo[rg] = W + (size_t)(lo_ok[rg] ? r_lo : 0) * ldw;
-    w_hi[rg] = W + (size_t)(hi_ok[rg] ? r_hi : 0) * ldw;
-  }
-
-  float acc[RG][NT][4];
-#pragma unroll
-  for (int rg = 0; rg < RG; ++rg)
-#pragma unroll
-    for (int i = 0; i < NT; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[rg][i][j] = 0.0f;
-
+    for (int rg = 0; rg < RG; ++rg) {
+      const int r_lo = (u * RG + rg) * 16 + g, r_hi = r_lo + 8;
+      lo_ok[rg] = r_lo < N;
+      hi_ok[rg] = r_hi < N;
+      w_lo[rg] = W + (size_t)(lo_ok[rg] ? r_lo : 0) * ldw;
+      w_hi[rg] = W + (size_t)(hi_ok[rg] ? r_hi : 0) * ldw;
+    }
+  };
   const int ksteps = (K + 31) >> 5;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   // Weights never depend on the previous kernel: the first batch of loads is issued before the
@@ -85,85 +83,115 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
       }
     }
   };
+  set_rows(unit);
   load_w(warp, wa, wb);
   pdl_wait();
   pdl_launch();
-  for (int ks0 = warp; ks0 < ksteps; ks0 += SK_WARPS * UNROLL) {
-    load_w(ks0 + SK_WARPS * UNROLL, na, nb);
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int k = (ks0 + u * SK_WARPS) * 32 + 8 * t;
-      const bool ok = k < K;
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int m = nt * 8 + g;
-        uint4 x = zero;
-        if (ok && m < M) x = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k));
-#pragma unroll
-        for (int rg = 0; rg < RG; ++rg) {
-          mma_bf16_16816(acc[rg][nt], wa[rg][u].x, wb[rg][u].x, wa[rg][u].y, wb[rg][u].y, x.x, x.y);
-          mma_bf16_16816(acc[rg][nt], wa[rg][u].z, wb[rg][u].z, wa[rg][u].w, wb[rg][u].w, x.z, x.w);
-        }
-      }
-    }
+  for (int iu = 0; iu < units_per_cta && unit < n_units; ++iu, ++unit) {
+    const int row0 = unit * 16 * RG;
+    float acc[RG][NT][4];
 #pragma unroll
     for (int rg = 0; rg < RG; ++rg)
 #pragma unroll
+      for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[rg][i][j] = 0.0f;
+
+    for (int ks0 = warp; ks0 < ksteps; ks0 += SK_WARPS * UNROLL) {
+      load_w(ks0 + SK_WARPS * UNROLL, na, nb);
+#pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
-        wa[rg][u] = na[rg][u];
-        wb[rg][u] = nb[rg][u];
+        const int k = (ks0 + u * SK_WARPS) * 32 + 8 * t;
+        const bool ok = k < K;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int m = nt * 8 + g;
+          uint4 x = zero;
+          if (ok && m < M) x = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k));
+#pragma unroll
+          for (int rg = 0; rg < RG; ++rg) {
+            mma_bf16_16816(acc[rg][nt], wa[rg][u].x, wb[rg][u].x, wa[rg][u].y, wb[rg][u].y, x.x, x.y);
+            mma_bf16_16816(acc[rg][nt], wa[rg][u].z, wb[rg][u].z, wa[rg][u].w, wb[rg][u].w, x.z, x.w);
+          }
+        }
       }
-  }
-  // accumulator layout: acc[..][nt][0..1] = (weight row g, tokens nt*8 + 2t, 2t+1); [2..3] = row g+8
 #pragma unroll
-  for (int rg = 0; rg < RG; ++rg)
+      for (int rg = 0; rg < RG; ++rg)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      red[warp][rg * 16 + g][nt * 8 + 2 * t] = acc[rg][nt][0];
-      red[warp][rg * 16 + g][nt * 8 + 2 * t + 1] = acc[rg][nt][1];
-      red[warp][rg * 16 + g + 8][nt * 8 + 2 * t] = acc[rg][nt][2];
-      red[warp][rg * 16 + g + 8][nt * 8 + 2 * t + 1] = acc[rg][nt][3];
+        for (int u = 0; u < UNROLL; ++u) {
+          wa[rg][u] = na[rg][u];
+          wb[rg][u] = nb[rg][u];
+        }
     }
-  __syncthreads();
-  if (EPI == HB_EPI_SWIGLU) {
-    // per group of 16 rows: 8 channels x (NT*8) tokens; output column = (row group) * 8 + channel
-    for (int idx = threadIdx.x; idx < RG * 8 * NT * 8; idx += SK_THREADS) {
-      const int ch = idx & 7, rg = (idx >> 3) % RG, m = idx / (8 * RG);
-      if (m >= M) continue;
-      float gate = 0.0f, up = 0.0f;
+    if (iu + 1 < units_per_cta && unit + 1 < n_units) {   // the next unit's first batch, under this unit's reduction
+      set_rows(unit + 1);
+      load_w(warp, wa, wb);
+    }
+    // accumulator layout: acc[..][nt][0..1] = (weight row g, tokens nt*8 + 2t, 2t+1); [2..3] = row g+8
 #pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) {
-        gate += red[w][rg * 16 + ch][m];
-        up += red[w][rg * 16 + ch + 8][m];
+    for (int rg = 0; rg < RG; ++rg)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        red[warp][rg * 16 + g][nt * 8 + 2 * t] = acc[rg][nt][0];
+        red[warp][rg * 16 + g][nt * 8 + 2 * t + 1] = acc[rg][nt][1];
+        red[warp][rg * 16 + g + 8][nt * 8 + 2 * t] = acc[rg][nt][2];
+        red[warp][rg * 16 + g + 8][nt * 8 + 2 * t + 1] = acc[rg][nt][3];
       }
-      const int col = (blockIdx.x * RG + rg) * 8 + ch;
-      if (row0 + rg * 16 + ch + 8 < N) ((bf16*)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
-    }
-  } else {
-    for (int idx = threadIdx.x; idx < 16 * RG * NT * 8; idx += SK_THREADS) {
-      const int r = idx % (16 * RG), m = idx / (16 * RG);
-      const int n = row0 + r;
-      if (m >= M || n >= N) continue;
-      float s = 0.0f;
+    __syncthreads();
+    if (EPI == HB_EPI_SWIGLU) {
+      // per group of 16 rows: 8 channels x (NT*8) tokens; output column = (row group) * 8 + channel
+      for (int idx = threadIdx.x; idx < RG * 8 * NT * 8; idx += SK_THREADS) {
+        const int ch = idx & 7, rg = (idx >> 3) % RG, m = idx / (8 * RG);
+        if (m >= M) continue;
+        float gate = 0.0f, up = 0.0f;
 #pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) s += red[w][r][m];
-      const size_t o = (size_t)m * ldc + n;
-      if (EPI == HB_EPI_STORE) ((bf16*)Cv)[o] = __float2bfloat16_rn(s);
-      else if (EPI == HB_EPI_STORE_F32) ((float*)Cv)[o] = s;
-      else ((float*)Cv)[o] += s;
+        for (int w = 0; w < SK_WARPS; ++w) {
+          gate += red[w][rg * 16 + ch][m];
+          up += red[w][rg * 16 + ch + 8][m];
+        }
+        const int col = (unit * RG + rg) * 8 + ch;
+        if (row0 + rg * 16 + ch + 8 < N) ((bf16*)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < 16 * RG * NT * 8; idx += SK_THREADS) {
+        const int r = idx % (16 * RG), m = idx / (16 * RG);
+        const int n = row0 + r;
+        if (m >= M || n >= N) continue;
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) s += red[w][r][m];
+        const size_t o = (size_t)m * ldc + n;
+        if (EPI == HB_EPI_STORE) ((bf16*)Cv)[o] = __float2bfloat16_rn(s);
+        else if (EPI == HB_EPI_STORE_F32) ((float*)Cv)[o] = s;
+        else ((float*)Cv)[o] += s;
+      }
     }
+    __syncthreads();   // the partial sums are read: the next unit may overwrite them
   }
 }
 
 template <int NT, int RG, int UNROLL>
 static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C, int ldc, int M, int N, int K,
                          int epi, cudaStream_t s) {
-  const unsigned grid = (unsigned)ceil_div(N, 16 * RG);
+  // as many CTAs as the GPU holds at once (asked of the runtime for this instantiation), each with
+  // an equal run of units
+  static int slots = 0;
+  if (slots == 0) {
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE>, SK_THREADS, 0) != cudaSuccess || per_sm <= 0) per_sm = 2;
+    slots = per_sm * sms;
+  }
+  const int n_units = ceil_div(N, 16 * RG);
+  // fewer than one and a half waves: one unit per CTA keeps more loads in flight than halving the grid
+  const int upc = (2 * n_units > 3 * slots) ? ceil_div(n_units, slots) : 1;
+  const unsigned grid = (unsigned)ceil_div(n_units, upc);
   switch (epi) {
-    case HB_EPI_STORE: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_STORE_F32: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_RESIDUAL: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
-    case HB_EPI_SWIGLU: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K); break;
+    case HB_EPI_STORE: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
+    case HB_EPI_STORE_F32: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
+    case HB_EPI_RESIDUAL: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
+    case HB_EPI_SWIGLU: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
     default: HB_FAIL(2, "gemm_skinny: unknown epilogue %d", epi);
   }
   HB_CHECK_LAUNCH("gemm_skinny");

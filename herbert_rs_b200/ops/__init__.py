@@ -45,6 +45,8 @@ _SIGS = {
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "hb_attention_decode_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
 }
@@ -68,7 +70,7 @@ def _fn(name: str):
 
 
 # kernels each launcher starts (for honest launch counts)
-_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2}
+_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_attention_decode_tc_bf16": 2, "hb_argmax": 2}
 _launches = 0
 
 
@@ -376,6 +378,28 @@ def _prefill_kernel_ok(out, head_dim, page_size) -> bool:
     return out.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and page_size % 64 == 0
 
 
+def attention_decode_tc(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch, num_heads, num_kv_heads,
+                        head_dim, page_size, nsplit, scale, window) -> None:
+    """The same on tcgen05 tensor cores (head size 128): keys as the M side, S^T and O^T in tensor memory."""
+    _check(out, torch.bfloat16, "out"); _check(scratch, torch.float32, "scratch")
+    n = out.shape[0]
+    if scratch.numel() < attention_decode_scratch_floats(n, num_heads, head_dim, nsplit):
+        raise BackendError("attention_decode_tc: scratch is too small")
+    _run("hb_attention_decode_tc_bf16", q.data_ptr(), int(ldq), q.shape[0], out.data_ptr(), out.stride(0),
+         k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], seq_len.data_ptr(), seq_pages.data_ptr(),
+         seq_pages.stride(0), scratch.data_ptr(), n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit),
+         float(scale), int(window or 0), _error_flag(out.device).data_ptr(), _stream())
+
+
+DECODE_ATTENTION = os.environ.get("HB_DECODE_ATTENTION", "mma")    # "tcgen05": the tensor-memory kernel (head 128); measured slower, see profiles/
+DECODE_TC_TARGET_CTAS = int(os.environ.get("HB_DECODE_TC_CTAS", "148"))   # one CTA per SM (200 KB of shared memory each)
+
+
+def _decode_tc_ok(q, ldq, out, num_heads, num_kv_heads, head_dim, page_size) -> bool:
+    return (DECODE_ATTENTION == "tcgen05" and out.dtype == torch.bfloat16 and head_dim == 128 and ldq % 128 == 0
+            and num_heads // num_kv_heads <= 16 and page_size % 64 == 0 and q.data_ptr() % 16 == 0)
+
+
 def _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size) -> bool:
     return (out.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
             and num_heads // num_kv_heads <= 16 and page_size % 64 == 0)
@@ -388,6 +412,13 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
     bfloat16 steps of one token per sequence take the split-key tensor-core kernel, other bfloat16
     steps the flash kernel; head sizes or pages those cannot serve, and the float32 path, take
     the any-shape kernel."""
+    if batch.is_decode and scratch is not None and _decode_tc_ok(q, ldq, out, num_heads, num_kv_heads, head_dim, page_size):
+        tiles = -(-seq_pages.shape[1] * page_size // 128)
+        nsplit = max(1, min(DECODE_TC_TARGET_CTAS // max(1, batch.n_seqs * num_kv_heads), tiles, 64))
+        buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
+        attention_decode_tc(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
+                            head_dim, page_size, nsplit, scale, window)
+        return
     if batch.is_decode and scratch is not None and _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size):
         tiles = seq_pages.shape[1] * (page_size // 64)
         nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)
