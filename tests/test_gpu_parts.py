@@ -286,3 +286,31 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache(tmp_path, dtype)
     ref = _looped_plain(pm.w, pm.cfg, ids)
     assert_close(replay_whole(eng, ids), ref, dtype, "looped whole")
     assert_close(replay_tail_one_by_one(eng, ids, 32), ref, dtype, "looped one by one")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_part_alone(dtype):
+    """The pre-norm block built from a spec: x + attn(norm1 x), then + ffn(norm2 .), against the plain layer."""
+    torch.manual_seed(3)
+    rt = hb.Runtime("cuda", TD[dtype], page_size=16)
+    H, nh, nkv, hd, inter = 48, 4, 2, 16, 88
+    norm = NormSpec(H, 1e-5)
+    spec = BlockSpec(mixer=AttentionSpec(H, nh, nkv, hd, scale=hd ** -0.5, qk_norm=NormSpec(hd, 1e-5),
+                                         position=PositionSpec(hd, hd, 1e4, 64)),
+                     ffn=SwiGLUSpec(H, inter), norm1=norm, norm2=norm)
+    block = hb.build_part("block", spec, rt=rt)
+    specs = block.param_specs()
+    assert "self_attn.q_proj.weight" in specs and "mlp.down_proj.weight" in specs and "input_layernorm.weight" in specs
+    w = {n: _bf(torch.randn(ps.shape) * 0.1 if ps.role == "matrix" else 1 + 0.1 * torch.randn(ps.shape)) for n, ps in specs.items()}
+    block.load({n: (t.float() if specs[n].role == "vector" else t.to(TD[dtype])).cuda() for n, t in w.items()})
+    cache = SequenceCache([block.cache_need()], [None], 8, 2, page_size=16, dtype=TD[dtype], device="cuda")
+    x0 = torch.randn(21, H)
+    slot = cache.alloc_slot()
+    rt.workspace.rewind()
+    b = _batch(cache, rt, [slot], [21])
+    x = x0.clone().cuda()
+    block.forward(x, b, cache.view(0))
+    cfg = dict(nh=nh, nkv=nkv, hd=hd, eps=1e-5, rot=hd, scale=hd ** -0.5, windows=[None])
+    cos, sin = P.rope_tables(hd, 1e4, 21, torch.float64)
+    ref = P.decoder_layer(x0.double(), {"model.layers.0." + k: v.float() for k, v in w.items()}, 0, cfg, cos, sin)
+    assert_close(to_np(x), ref.numpy(), dtype, "block part")
