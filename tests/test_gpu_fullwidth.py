@@ -1,0 +1,40 @@
+"""One layer at Qwen3-8B widths (hidden 4096, 32/8 heads of 128, feed-forward 12288): the kernels at
+the tile counts and strides they serve in production, against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import herbert_rs_b200 as hb
+from gpu_util import assert_close, engine_for, random_ids, replay_batches, replay_tail_one_by_one, replay_whole
+from plain_qwen3 import PlainModel
+
+pytestmark = pytest.mark.gpu
+
+WIDE = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=20040, hidden_size=4096,
+            num_hidden_layers=1, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+            intermediate_size=12288, rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=4096,
+            tie_word_embeddings=False, eos_token_id=3)
+
+
+@pytest.fixture(scope="module")
+def wide(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("wide"))
+    hb.write_random_model(WIDE, d, seed=55)
+    return d, PlainModel(d)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_every_cutting_at_production_widths(wide, dtype):
+    d, plain = wide
+    rng = np.random.default_rng(3)
+    reqs = [random_ids(rng, 20040, n) for n in (150, 9, 70)]
+    refs = [plain.logits(r, torch.float32).double().numpy() for r in reqs]     # float32 plain: float64 at this width is slow
+    eng = engine_for(d, dtype, max_tokens=1024, max_slots=4)
+    for r, ref in zip(reqs, refs):
+        assert_close(replay_whole(eng, r), ref, dtype, "wide whole")
+    assert_close(replay_tail_one_by_one(eng, reqs[0], 32), refs[0], dtype, "wide one by one")
+    got = replay_batches(eng, reqs, [100, 9, 3], [[0, 1, 2]])
+    for g, ref in zip(got, refs):
+        assert_close(g, ref, dtype, "wide batched")
+    from herbert_rs_b200 import ops
+    ops.check_kernel_errors()
