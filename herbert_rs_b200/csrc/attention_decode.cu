@@ -43,14 +43,15 @@ struct DecodeArgs {
 };
 
 // HDM: the largest head size this instantiation holds in registers (hd <= HDM, hd % 16 == 0).
-template <int HDM>
+// EXACT: hd == HDM is known at compile time, so every size test and stride folds away.
+template <int HDM, bool EXACT>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
   pdl_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int hd = a.hd, G = a.nh / a.nkv;
+  const int hd = EXACT ? HDM : a.hd, G = a.nh / a.nkv;
   const int row_bytes = hd * 2 + 16;                 // padded: conflict-free ldmatrix for any hd % 16 == 0
   const int tile_bytes = AD_TILE * row_bytes;
   const int chunks_per_row = hd >> 3;
@@ -168,12 +169,16 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
       }
       // ---- mask, online softmax ---------------------------------------------------------------
       float mx[2] = {-INFINITY, -INFINITY};
+      const bool edge = key0 + 15 > p || key0 < lo;      // only the first and last tiles of the range need the mask
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int key = key0 + nt * 8 + 2 * t + (j & 1);
-          const float v = (key <= p && key >= lo) ? s[nt][j] * a.scale : -INFINITY;
+          float v = s[nt][j] * a.scale;
+          if (edge) {
+            const int key = key0 + nt * 8 + 2 * t + (j & 1);
+            if (!(key <= p && key >= lo)) v = -INFINITY;
+          }
           s[nt][j] = v;
           mx[j >> 1] = fmaxf(mx[j >> 1], v);
         }
@@ -343,17 +348,21 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   dim3 grid(nsplit, nkv, n_seqs);
   cudaError_t e;
   if (hd <= 64) {
-    e = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(attention_decode_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_kernel<64>, dim3(grid), dim3(AD_THREADS), smem, s, a);
-  } else if (hd <= 128) {
-    e = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    hb_launch(attention_decode_kernel<64, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+  } else if (hd == 128) {
+    e = cudaFuncSetAttribute(attention_decode_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_kernel<128>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+    hb_launch(attention_decode_kernel<128, true>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+  } else if (hd < 128) {
+    e = cudaFuncSetAttribute(attention_decode_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    hb_launch(attention_decode_kernel<128, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   } else {
-    e = cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(attention_decode_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_kernel<256>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+    hb_launch(attention_decode_kernel<256, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   }
   HB_CHECK_LAUNCH("attention_decode");
   dim3 cgrid(nh, n_seqs);
