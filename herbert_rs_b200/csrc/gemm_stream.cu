@@ -15,6 +15,8 @@
 // last sums all partials in slice order (so the result does not depend on arrival order), applies
 // the epilogue and resets the counter.  Epilogues: store, store as float, add into the float
 // residual stream, SwiGLU over rows stored as 8 gate rows + 8 up rows.
+#include <stdlib.h>
+
 #include "api.h"
 #include "common.cuh"
 #include "tcgen05_utils.cuh"
@@ -236,8 +238,14 @@ static StreamPlan stream_plan(int M, int N, int K) {
   p.tiles = ceil_div(N, GS_BM);
   const int num_kb = ceil_div(K, TG_BK);
   const int slots = stream_sm_count() * 2;
+  static int max_slices = 0;
+  if (max_slices == 0) {
+    const char* e = getenv("HB_STREAM_MAX_SLICES");      // tuning knob
+    max_slices = e ? atoi(e) : 2;        // measured: more slices cost more in the ordered reduction than they gain
+    if (max_slices < 1) max_slices = 1;
+  }
   int s = slots / p.tiles;
-  if (s > 16) s = 16;
+  if (s > max_slices) s = max_slices;
   if (s > num_kb / 2) s = num_kb / 2;             // at least two k blocks per slice
   if (s < 1) s = 1;
   p.slices = s;

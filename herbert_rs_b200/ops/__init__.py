@@ -278,11 +278,12 @@ def _stream_uncut(M: int, N: int, K: int) -> bool:
 
 def _decode_gemm(a, w):
     """Which kernel multiplies at most 64 activation rows.  Measured at Qwen3-8B shapes: the
-    mma.sync kernel wins up to 16 rows and wherever K would have to be cut; from 17 rows on its
-    activation reads through L1 dominate and the TMA/tcgen05 kernel is 2-3x faster when K is uncut."""
+    mma.sync kernel wins up to 16 rows and on matrices of few rows (o, down: 32 tiles of 128 rows
+    cannot fill the GPU without cutting K deep); from 17 rows on its activation reads through L1
+    dominate and the TMA/tcgen05 kernel is 1.3-3x faster on matrices of at least 48 row tiles."""
     if DECODE_GEMM == "stream":
         return gemm_stream
-    if DECODE_GEMM == "auto" and a.shape[0] > 16 and _stream_uncut(a.shape[0], w.shape[0], a.shape[1]):
+    if DECODE_GEMM == "auto" and a.shape[0] > 16 and (w.shape[0] >= 6144 or _stream_uncut(a.shape[0], w.shape[0], a.shape[1])):
         return gemm_stream
     return gemm_skinny
 
