@@ -41,7 +41,7 @@ __device__ __forceinline__ void mma_bf16_16816(float* d, unsigned a0, unsigned a
 // falls with RG (with 16 rows per CTA and 8 tokens it is half the weight traffic).  UNROLL: k steps
 // of 32 per batch of loads; two batches are in flight.
 template <int NT, int RG, int UNROLL, int EPI>
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, (NT * RG <= 2) ? 3 : 2)
 gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, void* Cv, int ldc,
                    int M, int N, int K, int units_per_cta) {
   // A unit is 16 * RG weight rows.  A CTA walks units_per_cta consecutive units, so that the grid is
