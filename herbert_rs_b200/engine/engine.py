@@ -89,6 +89,12 @@ class Engine:
     def free_slot(self, slot: int) -> None:
         self.cache.free_slot(slot)
 
+    def check_kernels(self) -> None:
+        """Raise if a kernel gave up on one of its bounded waits since the last check (reads one
+        int from the device, so it waits for the work queued so far)."""
+        from .. import ops
+        ops.check_kernel_errors()
+
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 

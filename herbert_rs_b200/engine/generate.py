@@ -167,5 +167,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
         finally:
             for s in slots.values():
                 engine.free_slot(s)
+        if hasattr(engine, "check_kernels"):
+            engine.check_kernels()      # a kernel that gave up on a bounded wait invalidates the batch
     stats.generated_tokens = sum(len(o) for o in out)
     return GenerationResult(out, reasons, stats)
