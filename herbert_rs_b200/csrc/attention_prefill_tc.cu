@@ -8,7 +8,8 @@
 //   warp 1     one lane issues tcgen05.mma:  S = Q K^T  (M=128, N=128) into one of two S buffers in
 //              tensor memory, and  O_j = P V  (M=128, N=head size; V is the MN-major operand as it
 //              lies in the cache) into one of two O buffers;
-//   warps 2-5  one thread per query row: read its row of S from tensor memory (no shuffles), mask,
+//   warps 2-9  two threads per query row (each half of the tile's keys and of the output columns):
+//              read the row of S from tensor memory (no shuffles), mask,
 //              running maximum and sum in float, P = 2^(s*c - m) as bfloat16 into shared memory in
 //              the swizzled K-major layout the tensor cores read, and o = o * 2^(m_old - m_new) + O_j
 //              in registers; finally o / l goes to global memory.
@@ -18,7 +19,7 @@
 #include "common.cuh"
 #include "tcgen05_utils.cuh"
 
-#define PT_THREADS 192
+#define PT_THREADS 320     // TMA warp, MMA warp, 8 softmax warps (two threads per query row)
 #define PT_Q 128        // queries per CTA
 #define PT_KEYS 128     // keys per tile
 #define PT_SUB (128 * 128)   // bytes of one [128 rows][64 columns] swizzled sub-tile
@@ -52,6 +53,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   //           13 p_ready | 14,15 o_full | 16,17 o_empty
   auto bar = [&](int i) { return bars + i * 8; };
   volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + (bars - base) + 18 * 8);
+  float* xch = reinterpret_cast<float*>(gen + (bars - base) + 256);   // [2 tile parities][2 halves][128 rows] maxima, then [2][128] sums
 
   // the last query tiles have the longest key ranges: they go first, the short ones fill the tail
   const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -68,8 +70,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 18; ++i) {
-      const bool from_rows = (i == 11 || i == 12 || i == 13 || i == 16 || i == 17);   // arrived at by the 4 row warps
-      mbar_init(bar(i), from_rows ? 4 : 1);
+      const bool from_rows = (i == 11 || i == 12 || i == 13 || i == 16 || i == 17);   // arrived at by the 8 row warps
+      mbar_init(bar(i), from_rows ? 8 : 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -159,7 +161,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   } else {
+    // Two threads per query row: warps 2-5 take the first 64 keys of a tile and the first half of
+    // the head's output columns, warps 6-9 the second halves; a warp may only touch the 32 tensor
+    // memory lanes of its quadrant (warp index modulo 4), so the pair of a row sits in warps w, w+4.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;              // row of the tile
     const int qi = q_first + r;
     const bool valid = qi < qlen;
@@ -167,10 +173,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
     const int lo_last = (a.window > 0 && p_last - a.window + 1 > 0) ? p_last - a.window + 1 : 0;
     const unsigned lane_off = (unsigned)(quad * 32) << 16;
+    constexpr int HH = HD / 2;                    // output columns per thread
+    const unsigned s_col = (unsigned)(half * 64), o_col = (unsigned)(half * HH);
     float m = -INFINITY, l = 0.0f, m_acc = -INFINITY;   // m_acc: the maximum the rows of o are scaled to
-    float o[HD];
+    float o[HH];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.0f;
+    for (int i = 0; i < HH; ++i) o[i] = 0.0f;
     bool ok = true;
     auto accumulate = [&](int j) -> bool {        // o = o * 2^(m_acc - m_j) + O_j
       const int st = j & 1;
@@ -181,16 +189,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float m_tile[2] = {-INFINITY, -INFINITY};      // maximum in force when P of tile j was formed
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j & 1;
-      const int key0 = (tile_lo + j) * PT_KEYS;
+      const int key0 = (tile_lo + j) * PT_KEYS + half * 64;     // first key of this thread's 64
       if (!mbar_wait(bar(9 + st), (j >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 30); ok = false; break; }
       tc_fence_after();
-      const bool need_mask = (key0 + PT_KEYS - 1 > p_first) || (key0 < lo_last);
-      // pass 1: the row's maximum over this tile (of the raw scores: the scale is positive)
+      const bool need_mask = ((tile_lo + j) * PT_KEYS + PT_KEYS - 1 > p_first) || ((tile_lo + j) * PT_KEYS < lo_last);
+      // pass 1: the row's maximum over this thread's half of the tile (raw scores: the scale is positive)
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < PT_KEYS / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         float s[32];
-        tc_ld32f(tm_s[st] + lane_off + c * 32, s);
+        tc_ld32f(tm_s[st] + lane_off + s_col + c * 32, s);
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -203,6 +211,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       }
       mx *= a.scale_log2;
+      // the other half of the row: exchange through shared memory (buffers alternate with the tile)
+      float* xm = xch + (j & 1) * 256;
+      xm[half * 128 + r] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, xm[(half ^ 1) * 128 + r]);
       const float m_new = fmaxf(m, mx);
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
       // the previous tile's P V must be complete before P is overwritten; take its result in as well
@@ -213,9 +226,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float mt = m_tile[sp];
         const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {      // unrolled: o stays in registers
+        for (int c = 0; c < HH / 32; ++c) {      // unrolled: o stays in registers
           float t[32];
-          tc_ld32f(tm_o[sp] + lane_off + c * 32, t);
+          tc_ld32f(tm_o[sp] + lane_off + o_col + c * 32, t);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * f + t[i];
         }
@@ -224,12 +237,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         __syncwarp();
         if (lane == 0) mbar_arrive_cta(bar(16 + sp));    // O buffer free
       }
-      // pass 2: P = 2^(s*c - m) into shared memory (K-major, 128-byte swizzle), row sum in float
+      // pass 2: P = 2^(s*c - m) into shared memory (K-major, 128-byte swizzle), partial row sum in float
       float sum = 0.0f;
 #pragma unroll 1
-      for (int c = 0; c < PT_KEYS / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         float s[32];
-        tc_ld32f(tm_s[st] + lane_off + c * 32, s);
+        tc_ld32f(tm_s[st] + lane_off + s_col + c * 32, s);
         unsigned pk[16];
         if (need_mask) {
 #pragma unroll
@@ -247,16 +260,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           __nv_bfloat162 v = __floats2bfloat162_rn(s[i], s[i + 1]);
           pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
         }
-        // 32 keys = four 16-byte chunks of this row; chunk index within the 64-key sub-tile is xor-ed with row % 8
-        unsigned char* rowp = p_gen + (c >> 1) * PT_SUB + r * 128;
+        // 32 keys = four 16-byte chunks of this row in the sub-tile of this half; chunk index xor row % 8
+        unsigned char* rowp = p_gen + half * PT_SUB + r * 128;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
+          const int chunk = (c * 4 + q4) ^ (r & 7);
           *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
         }
       }
       const float corr = (m == -INFINITY) ? 0.0f : fast_exp2(m - m_use);
-      l = l * corr + sum;
+      l = l * corr + sum;          // this thread's share of the row sum; the two shares meet at the end
       m = m_new;
       m_tile[st] = m_new;
       // S buffer read, P written: hand both to the tensor cores
@@ -268,6 +281,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_arrive_cta(bar(13));
       }
     }
+    // the row sum is the sum of the two threads' shares (both scaled to the same final maximum)
+    float* xl = xch + 512;
+    xl[half * 128 + r] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += xl[(half ^ 1) * 128 + r];
     if (ok) {
       const int j = n_tiles - 1, sp = j & 1;
       ok = accumulate(j);
@@ -275,11 +293,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float mt = m_tile[sp];
         const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        bf16* dst = a.out + (size_t)(row0 + qi) * a.ldo + (size_t)h * HD;
+        bf16* dst = a.out + (size_t)(row0 + qi) * a.ldo + (size_t)h * HD + half * HH;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HH / 32; ++c) {
           float t[32];
-          tc_ld32f(tm_o[sp] + lane_off + c * 32, t);
+          tc_ld32f(tm_o[sp] + lane_off + o_col + c * 32, t);
           if (valid) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
@@ -333,7 +351,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
                   scale * 1.4426950408889634f, window, error_flag};
   dim3 grid(ceil_div(max_q_len, PT_Q), nh, n_seqs);
   cudaStream_t s = (cudaStream_t)stream;
-  const int smem = 6 * (hd / 64) * PT_SUB + 2 * PT_SUB - (hd / 64) * PT_SUB + 1024 + 256;
+  const int smem = 6 * (hd / 64) * PT_SUB + 2 * PT_SUB - (hd / 64) * PT_SUB + 1024 + 256 + 3072;   // tiles, slack, barriers, exchange
   cudaError_t e;
   if (hd == 128) {
     e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
