@@ -218,24 +218,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mx = fmaxf(mx, xm[(half ^ 1) * 128 + r]);
       const float m_new = fmaxf(m, mx);
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-      // the previous tile's P V must be complete before P is overwritten; take its result in as well
+      // the previous tile's P V must be complete before P is overwritten
       if (j > 0) {
         ok = accumulate(j - 1);
         if (!ok) break;
-        const int sp = (j - 1) & 1;
-        const float mt = m_tile[sp];
-        const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
-#pragma unroll
-        for (int c = 0; c < HH / 32; ++c) {      // unrolled: o stays in registers
-          float t[32];
-          tc_ld32f(tm_o[sp] + lane_off + o_col + c * 32, t);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * f + t[i];
-        }
-        m_acc = mt;
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cta(bar(16 + sp));    // O buffer free
       }
       // pass 2: P = 2^(s*c - m) into shared memory (K-major, 128-byte swizzle), partial row sum in float
       float sum = 0.0f;
@@ -279,6 +265,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (lane == 0) {
         mbar_arrive_cta(bar(11 + st));
         mbar_arrive_cta(bar(13));
+      }
+      // the previous tile's result goes into the registers now, while the tensor cores run this tile's P V
+      if (j > 0) {
+        const int sp = (j - 1) & 1;
+        const float mt = m_tile[sp];
+        const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
+#pragma unroll
+        for (int c = 0; c < HH / 32; ++c) {      // unrolled: o stays in registers
+          float t[32];
+          tc_ld32f(tm_o[sp] + lane_off + o_col + c * 32, t);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * f + t[i];
+        }
+        m_acc = mt;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cta(bar(16 + sp));    // O buffer free
       }
     }
     // the row sum is the sum of the two threads' shares (both scaled to the same final maximum)
