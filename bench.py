@@ -30,6 +30,14 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_si
                 num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                 intermediate_size=12288, rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960,
                 tie_word_embeddings=False, eos_token_id=151645)
+# The other two sizes the reference architecture is usually quoted at (same layer formulas).
+SIZES = {
+    "8b": {},
+    "0.6b": dict(hidden_size=1024, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=3072, tie_word_embeddings=True),
+    "32b": dict(hidden_size=5120, num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8,
+                intermediate_size=25600),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -110,7 +118,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--size", default="8b", choices=sorted(SIZES), help="layer sizes: Qwen3-8B (the headline), 0.6B or 32B")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the size has (both numbers are reported)")
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
@@ -133,6 +142,10 @@ def main() -> int:
 
     pk = peaks()
     cfg = dict(QWEN3_8B)
+    cfg.update(SIZES[args.size])
+    layers_full = cfg["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = layers_full
     cfg["num_hidden_layers"] = args.layers
     rt = hb.Runtime("cuda", torch.bfloat16)
     model = hb.random_model(cfg, 0, rt)
@@ -256,7 +269,7 @@ def main() -> int:
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random-init weights N(0, 0.02)",
         "impl": "ours", "gpu_launches": kernels_per_step * args.steps,
-        "config": {"model": "Qwen3-8B layer sizes", "layers": args.layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+        "config": {"model": f"Qwen3-{args.size.upper()} layer sizes", "layers": args.layers, "layers_full": layers_full,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": B, "seq_len": args.prompt_len, "context": args.context, "parallelism": "single-gpu",
