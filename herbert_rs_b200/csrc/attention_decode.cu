@@ -272,6 +272,234 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
   }
 }
 
+// The same work with the roles of the tensor-core operands turned round, for head size 128: the
+// 16 keys of a warp's slab are the M side, the (up to 8 * NH) query heads of the group the N side:
+//   S^T[16 keys x 8 heads] = K_slab Q^T,   O^T[128 x 8 heads] += V_slab^T P^T.
+// Half the MMAs of the kernel above (no rows of padding), half the accumulator registers, and a
+// thread owns two heads outright, so the running maximum needs three shuffles per slab and the
+// running sum none until the end.  P^T changes from accumulator to B-operand layout with movmatrix.
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned v) {
+  unsigned r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
+__device__ __forceinline__ void mma16816_ab(float* d, const unsigned* a4, unsigned b0, unsigned b1) {
+  mma16816(d, a4[0], a4[1], a4[2], a4[3], b0, b1);
+}
+
+template <int NH>
+__global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeArgs a) {
+  constexpr int HD = 128;
+  extern __shared__ __align__(16) unsigned char smem[];
+  pdl_wait();
+  pdl_launch();
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int G = a.nh / a.nkv;
+  constexpr int row_bytes = HD * 2 + 16;
+  constexpr int tile_bytes = AD_TILE * row_bytes;
+  constexpr int chunks_per_row = HD >> 3;
+
+  const int len = a.seq_len[b];
+  const int p = len - 1;
+  const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+  const int tile_lo = lo / AD_TILE, tile_hi = (len + AD_TILE - 1) / AD_TILE;
+  const int ntiles = tile_hi - tile_lo;
+  const int per = (ntiles + a.nsplit - 1) / a.nsplit;
+  const int t0 = tile_lo + split * per;
+  const int t1 = min(tile_hi, t0 + per);
+  const int tiles_per_page = a.page_size / AD_TILE;
+  const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
+  const size_t head_elems = (size_t)a.page_size * HD;
+  __shared__ int page_ids[AD_MAX_TILES];
+  for (int i = threadIdx.x; i < t1 - t0; i += AD_THREADS) page_ids[i] = pages[(t0 + i) / tiles_per_page];
+  __syncthreads();
+
+  constexpr int SLOTS = HD / 16;
+  int g_off[SLOTS], s_off[SLOTS];
+#pragma unroll
+  for (int i = 0; i < SLOTS; ++i) {
+    const int c = threadIdx.x + i * AD_THREADS;
+    const int r = c / chunks_per_row, cc = c % chunks_per_row;
+    g_off[i] = r * HD + cc * 8;
+    s_off[i] = r * row_bytes + cc * 16;
+  }
+  const unsigned smem_u = (unsigned)__cvta_generic_to_shared(smem);
+  auto issue = [&](int tile, int stage) {
+    const int page = page_ids[tile - t0];
+    const size_t off = ((size_t)page * a.nkv + kvh) * head_elems + (size_t)(tile % tiles_per_page) * AD_TILE * HD;
+    const bf16* kg = a.kcache + off;
+    const bf16* vg = a.vcache + off;
+    const unsigned ks = smem_u + stage * 2 * tile_bytes;
+    const unsigned vs = ks + tile_bytes;
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i) {
+      cp_async16_s(ks + s_off[i], kg + g_off[i]);
+      cp_async16_s(vs + s_off[i], vg + g_off[i]);
+    }
+  };
+  // A-operand fragments come from shared memory: K rows as they lie, V transposed
+  const int lm = lane >> 3;
+  const unsigned k_lane = (unsigned)((warp * 16 + (lm & 1) * 8 + (lane & 7)) * row_bytes + (lm >> 1) * 16);
+  const unsigned v_lane = (unsigned)((warp * 16 + (lm >> 1) * 8 + (lane & 7)) * row_bytes + (lm & 1) * 16);
+
+  // B operand of the first product: Q^T, head g of each 8-head tile, d pairs (2t, 2t+1) and (2t+8, 2t+9)
+  unsigned qf[NH][HD / 16][2];
+  {
+    const bf16* qb = a.q + (size_t)b * a.ldq + (size_t)kvh * G * HD;
+#pragma unroll
+    for (int n = 0; n < NH; ++n) {
+      const int h = n * 8 + g;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        qf[n][ks][0] = qf[n][ks][1] = 0u;
+        if (h < G) {
+          qf[n][ks][0] = *reinterpret_cast<const unsigned*>(qb + (size_t)h * HD + ks * 16 + 2 * t);
+          qf[n][ks][1] = *reinterpret_cast<const unsigned*>(qb + (size_t)h * HD + ks * 16 + 2 * t + 8);
+        }
+      }
+    }
+  }
+  // per thread: heads n*8 + 2t and n*8 + 2t + 1
+  float m[NH][2], l[NH][2], o[NH][HD / 16][4];
+#pragma unroll
+  for (int n = 0; n < NH; ++n) {
+    m[n][0] = m[n][1] = -INFINITY;
+    l[n][0] = l[n][1] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) o[n][i][0] = o[n][i][1] = o[n][i][2] = o[n][i][3] = 0.0f;
+  }
+
+  const int S = a.stages;
+  for (int i = 0; i < S - 1; ++i) {
+    if (t0 + i < t1) issue(t0 + i, i);
+    cp_async_commit();
+  }
+  for (int tile = t0; tile < t1; ++tile) {
+    const int it = tile - t0;
+    if (tile + S - 1 < t1) issue(tile + S - 1, (it + S - 1) % S);
+    cp_async_commit();
+    if (S == 2) cp_async_wait<1>(); else if (S == 3) cp_async_wait<2>(); else cp_async_wait<3>();
+    __syncthreads();
+    const unsigned ks = smem_u + (unsigned)(it % S) * 2 * tile_bytes;
+    const unsigned vs = ks + tile_bytes;
+    const int key0 = tile * AD_TILE + warp * 16;
+    if (key0 <= p && key0 + 15 >= lo) {
+      // ---- S^T = K Q^T: rows = this warp's 16 keys, columns = heads ------------------------------
+      float s[NH][4];
+#pragma unroll
+      for (int n = 0; n < NH; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        unsigned af[4];
+        ldmatrix_x4_s(af[0], af[1], af[2], af[3], ks + k_lane + kk * 32);
+#pragma unroll
+        for (int n = 0; n < NH; ++n) mma16816_ab(s[n], af, qf[n][kk][0], qf[n][kk][1]);
+      }
+      // s[n][0], s[n][1]: key g, heads 2t, 2t+1;  s[n][2], s[n][3]: key g + 8, the same heads
+      const bool edge = key0 + 15 > p || key0 < lo;
+      const bool k0_ok = !edge || (key0 + g <= p && key0 + g >= lo);
+      const bool k1_ok = !edge || (key0 + g + 8 <= p && key0 + g + 8 >= lo);
+      bool rescale = false;
+      float corr[NH][2];
+      unsigned pb[NH][2];
+#pragma unroll
+      for (int n = 0; n < NH; ++n) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float v0 = k0_ok ? s[n][j] * a.scale : -INFINITY;
+          float v1 = k1_ok ? s[n][2 + j] * a.scale : -INFINITY;
+          float mx = fmaxf(v0, v1);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m[n][j], mx);
+          const float mu = (m_new == -INFINITY) ? 0.0f : m_new;
+          corr[n][j] = (m_new == m[n][j]) ? 1.0f : __expf(m[n][j] - m_new);     // m = -inf before: exp(-inf) = 0
+          rescale |= corr[n][j] != 1.0f;
+          m[n][j] = m_new;
+          v0 = k0_ok ? __expf(v0 - mu) : 0.0f;
+          v1 = k1_ok ? __expf(v1 - mu) : 0.0f;
+          l[n][j] = l[n][j] * corr[n][j] + (v0 + v1);          // this thread's keys only; the lanes' shares meet at the end
+          s[n][j] = v0;
+          s[n][2 + j] = v1;
+        }
+        // P^T from accumulator layout (key g; heads 2t, 2t+1) to B-operand layout (head g; keys 2t, 2t+1)
+        pb[n][0] = movmatrix_trans(pack_bf16(s[n][0], s[n][1]));
+        pb[n][1] = movmatrix_trans(pack_bf16(s[n][2], s[n][3]));
+      }
+      rescale = __any_sync(0xffffffffu, rescale);
+      // ---- O^T += V^T P^T: rows = 16 values of the head size per step, columns = heads -------------
+#pragma unroll
+      for (int md = 0; md < HD / 16; ++md) {
+        unsigned af[4];
+        ldmatrix_x4_trans_s(af[0], af[1], af[2], af[3], vs + v_lane + md * 32);
+#pragma unroll
+        for (int n = 0; n < NH; ++n) {
+          if (rescale) {
+            o[n][md][0] *= corr[n][0]; o[n][md][1] *= corr[n][1];
+            o[n][md][2] *= corr[n][0]; o[n][md][3] *= corr[n][1];
+          }
+          mma16816_ab(o[n][md], af, pb[n][0], pb[n][1]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- merge the 4 warps through shared memory ---------------------------------------------------
+  constexpr int HP = 8 * NH;                               // heads, padded
+  float* sm_m = reinterpret_cast<float*>(smem);            // [4][HP]
+  float* sm_l = sm_m + AD_WARPS * HP;                      // [4][HP]
+  float* sm_o = sm_l + AD_WARPS * HP;                      // [4][HP][HD]
+#pragma unroll
+  for (int n = 0; n < NH; ++n) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float ll = l[n][j];                                  // sum over the 8 lanes that share these heads
+      ll += __shfl_xor_sync(0xffffffffu, ll, 4);
+      ll += __shfl_xor_sync(0xffffffffu, ll, 8);
+      ll += __shfl_xor_sync(0xffffffffu, ll, 16);
+      if (g == 0) {
+        sm_m[warp * HP + n * 8 + 2 * t + j] = m[n][j];
+        sm_l[warp * HP + n * 8 + 2 * t + j] = ll;
+      }
+    }
+#pragma unroll
+    for (int md = 0; md < HD / 16; ++md) {
+      float* c0 = sm_o + ((size_t)warp * HP + n * 8 + 2 * t) * HD + md * 16 + g;
+      c0[0] = o[n][md][0];            // head 2t,   d = md*16 + g
+      c0[HD] = o[n][md][1];           // head 2t+1, d = md*16 + g
+      c0[8] = o[n][md][2];            // head 2t,   d = md*16 + g + 8
+      c0[HD + 8] = o[n][md][3];       // head 2t+1, d = md*16 + g + 8
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += AD_THREADS) {
+    const int r = idx / HD, d = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) mm = fmaxf(mm, sm_m[w * HP + r]);
+    float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < AD_WARPS; ++w) {
+      const float mw = sm_m[w * HP + r];
+      const float f = (mw == -INFINITY) ? 0.0f : __expf(mw - mm);
+      acc += f * sm_o[((size_t)w * HP + r) * HD + d];
+      ll += f * sm_l[w * HP + r];
+    }
+    const int h = kvh * G + r;
+    const size_t pi = ((size_t)b * a.nh + h) * a.nsplit + split;
+    a.part_o[pi * HD + d] = acc;
+    if (d == 0) {
+      a.part_ml[pi * 2] = mm;
+      a.part_ml[pi * 2 + 1] = ll;
+    }
+  }
+}
+
 // out[b][h][:] = sum_s e^{m_s - m} O_s / sum_s e^{m_s - m} l_s
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 bf16* __restrict__ out, int ldo, int nh, int hd, int nsplit) {
@@ -304,6 +532,15 @@ int hb_attention_decode_combine(const float* part_o, const float* part_ml, void*
   hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
   HB_CHECK_LAUNCH("attention_decode_combine");
   return 0;
+}
+
+static bool use_old_layout() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HB_DECODE_HEADS_AS_M");     // tuning knob: 1 = the first kernel (query heads as the M side) also for head size 128
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
 }
 
 static int decode_smem_bytes(int hd, int stages) {
@@ -351,6 +588,16 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
     e = cudaFuncSetAttribute(attention_decode_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     hb_launch(attention_decode_kernel<64, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+  } else if (hd == 128 && !use_old_layout()) {
+    if (nh / nkv <= 8) {
+      e = cudaFuncSetAttribute(attention_decode_km_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      hb_launch(attention_decode_km_kernel<1>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+    } else {
+      e = cudaFuncSetAttribute(attention_decode_km_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      hb_launch(attention_decode_km_kernel<2>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+    }
   } else if (hd == 128) {
     e = cudaFuncSetAttribute(attention_decode_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));

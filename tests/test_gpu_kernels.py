@@ -318,7 +318,8 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
     ops.gemm(a, w, c)        # the dispatcher takes another kernel instead
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 3, 48), (32, 8, 128), (5, 5, 80), (16, 1, 64), (2, 1, 256), (12, 4, 112)])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 3, 48), (32, 8, 128), (5, 5, 80), (16, 1, 64), (2, 1, 256), (12, 4, 112),
+                                       (16, 1, 128), (8, 8, 128), (40, 8, 128), (24, 2, 128)])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("nsplit", [1, 3, 8])
 def test_attention_decode_kernel(nh, nkv, hd, window, nsplit):
