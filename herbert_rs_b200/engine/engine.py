@@ -56,6 +56,9 @@ class Engine:
         self._graph_ws = Workspace(self.rt.device)
         self._eager_ws = self.rt.workspace
         self.graph_replays = 0
+        self._decode_again = None      # (slots, batch, lengths after it): lets the next decode step of the same sequences update the step buffer in place
+        self._host_owner = None        # the batch whose arrays the pinned buffer holds
+        self.fast_decode_steps = 0
         self.kernels_per_graph: dict = {}   # batch size -> kernels in its captured decode step
         self.launches_last = 0
         self.h2d_bytes_last = 0
@@ -148,6 +151,49 @@ class Engine:
         self._copied.record()
         self.h2d_bytes_last = n * 4
         batch.bind(self._dev)
+        self._host_owner = batch
+        return batch
+
+    def _prepare_decode_again(self, entries, uniforms: Optional[np.ndarray]) -> Optional[StepBatch]:
+        """The next one-token step of the sequences of the previous step: instead of building the
+        step buffer anew, bump positions and lengths in place, write the new tokens (and page rows,
+        when a sequence enters a new page) and upload.  None if this is not such a step."""
+        st = self._decode_again
+        if st is None or self._host_owner is not st[1]:
+            return None
+        slots, batch, lens_after = st
+        if len(entries) != len(slots):
+            return None
+        lengths = self.cache.lengths
+        for i, (s, t) in enumerate(entries):
+            if s != slots[i] or len(t) != 1 or lengths[s] != lens_after[i] or not self.cache.slots.is_held(s):
+                return None
+        ps = self.rt.page_size
+        if -(-(max(lens_after) + 1) // ps) > batch.pages_width:
+            return None
+        V = self.vocab_size
+        toks = [t[0] for _, t in entries]
+        for s, x in zip(slots, toks):
+            if not (isinstance(x, (int, np.integer)) and 0 <= x < V):
+                raise RequestError(f"slot {s}: token id {x!r} is outside the vocabulary of {V}")
+        new_page = any(n % ps == 0 for n in lens_after)
+        self.cache.reserve([(s, 1) for s in slots])
+        B, o, host = len(slots), batch.layout.offsets, self._host.numpy()
+        self._copied.synchronize()
+        host[o["token_ids"]:o["token_ids"] + B] = toks
+        for name in ("tok_pos", "seq_pos0", "seq_len"):
+            host[o[name]:o[name] + B] += 1
+        if uniforms is not None:
+            host[o["uniforms"]:o["uniforms"] + B] = np.asarray(uniforms, dtype=np.float32).view(np.int32)
+        if new_page:
+            for g in range(self.cache.num_kv_groups):
+                rows = self.cache.page_rows(g, list(slots), batch.pages_width)
+                host[o[f"pages{g}"]:o[f"pages{g}"] + B * batch.pages_width] = rows.reshape(-1)
+        n = batch.layout.total
+        self._dev[:n].copy_(self._host[:n], non_blocking=True)
+        self._copied.record()
+        self.h2d_bytes_last = n * 4
+        self.fast_decode_steps += 1
         return batch
 
     def _forward(self, batch: StepBatch):
@@ -204,9 +250,13 @@ class Engine:
         chosen on the device; only the ids travel back to the host."""
         B = len(entries)
         u = None if uniforms is None else np.asarray(uniforms, dtype=np.float32)
-        batch = self._prepare(entries, "last", u)
+        batch = self._prepare_decode_again(entries, u) if self.use_graphs else None
+        if batch is None:
+            batch = self._prepare(entries, "last", u)
         logits = self._forward(batch)
         self._finish(batch)
+        if self.use_graphs and batch.is_decode:
+            self._decode_again = (tuple(batch.slots), batch, [self.cache.lengths[s] for s in batch.slots])
         out = self._tok_out[:B]
         device_choose(logits, params, batch.uniforms, out)
         self._tok_host[:B].copy_(out, non_blocking=True)

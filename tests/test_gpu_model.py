@@ -251,3 +251,23 @@ def test_captured_decode_steps_equal_eager_ones(model_dirs, plain, dtype):
     for x, y, ids in zip(a, b, reqs):
         assert np.abs(x - y).max() <= 1e-6          # same kernels, same arithmetic
         assert_close(y, plain["C"].logits(ids).numpy(), dtype, "graphed decode")
+
+
+def test_decode_steps_that_update_the_step_buffer_in_place(model_dirs, plain):
+    """Generation's decode steps reuse the previous step's buffer; the tokens must be those of an
+    engine that builds every step anew, also across page edges, early finishers and a new batch."""
+    rng = np.random.default_rng(18)
+    prompts = [random_ids(rng, 300, n) for n in (60, 3, 127, 64, 20)]
+    opt = hb.GenerationOptions(max_tokens=80, ignore_eos=True, max_batch=3)
+    fast = engine_for(model_dirs["C"], "float32")
+    slow = engine_for(model_dirs["C"], "float32", use_graphs=False)
+    a = hb.generate(fast, prompts, opt, hb.SamplingParams(temperature=0.7, top_k=30, top_p=0.95, seed=5)).tokens
+    b = hb.generate(slow, prompts, opt, hb.SamplingParams(temperature=0.7, top_k=30, top_p=0.95, seed=5)).tokens
+    assert a == b
+    assert fast.fast_decode_steps > 100 and slow.fast_decode_steps == 0
+    # one sequence stops early: the next step has other sequences and must not take the short cut blindly
+    stop = a[0][10]
+    c = hb.generate(fast, prompts[:3], hb.GenerationOptions(max_tokens=40, stop_token_ids=[stop]), hb.SamplingParams(temperature=0.7, top_k=30, top_p=0.95, seed=5)).tokens
+    d = hb.generate(slow, prompts[:3], hb.GenerationOptions(max_tokens=40, stop_token_ids=[stop]), hb.SamplingParams(temperature=0.7, top_k=30, top_p=0.95, seed=5)).tokens
+    assert c == d and len(c[0]) == 11
+    fast.cache.check()
