@@ -20,6 +20,7 @@
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
 #define HB_EPI_SWIGLU 3
+#define SK_NORM_ROWS 16
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
@@ -36,19 +37,34 @@ __device__ __forceinline__ void mma_bf16_16816(float* d, unsigned a0, unsigned a
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// A norm shared between two products.  RMSNorm is y = x * w / rms(x): the product that last adds
+// into the residual stream x can also write x * w (bfloat16) and, per group of its output columns,
+// the sum of x^2; the product that reads y takes x * w as its activation and multiplies its results
+// by 1 / rms, which it gets from those partial sums.  No kernel between the two, no pass over x.
+struct SkinnyNorm {
+  const float* in_sumsq;   // consumer: [in_parts][SK_NORM_ROWS] partial sums of x^2 of the activation rows, or null
+  int in_parts;
+  float in_eps;            // 1/rms = rsqrt(sum / K + eps)
+  const float* out_w;      // producer (residual epilogue): the next norm's weight [N], or null
+  bf16* out_xw;            // [M, out_ld] = residual * out_w
+  int out_ld;
+  float* out_sumsq;        // [units][SK_NORM_ROWS]
+};
+
 // NT: 8-token tiles (M <= 8 * NT).  RG: groups of 16 weight rows per CTA; a warp multiplies each
 // activation fragment it loads with RG weight fragments, so the activation traffic per weight byte
 // falls with RG (with 16 rows per CTA and 8 tokens it is half the weight traffic).  UNROLL: k steps
 // of 32 per batch of loads; two batches are in flight.
-template <int NT, int RG, int UNROLL, int EPI>
+template <int NT, int RG, int UNROLL, int EPI, bool NORM>
 __global__ void __launch_bounds__(SK_THREADS, (NT * RG <= 2) ? 3 : 2)
 gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, void* Cv, int ldc,
-                   int M, int N, int K, int units_per_cta) {
+                   int M, int N, int K, int units_per_cta, SkinnyNorm nm) {
   // A unit is 16 * RG weight rows.  A CTA walks units_per_cta consecutive units, so that the grid is
   // no larger than what the GPU holds at once (no partly filled last wave) and every CTA streams
   // the same number of bytes; the first weight loads of the next unit are issued before the
   // current unit's partial sums are combined.
   __shared__ float red[SK_WARPS][16 * RG][NT * 8 + 1];
+  __shared__ float inv_rms[NORM ? SK_NORM_ROWS : 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n_units = (N + 16 * RG - 1) / (16 * RG);
@@ -87,6 +103,17 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
   load_w(warp, wa, wb);
   pdl_wait();
   pdl_launch();
+  if (NORM) {
+    // 1 / rms of the activation rows from the producer's partial sums: warp w sums rows w and w + 8
+    // in a fixed order; the first __syncthreads() before an epilogue publishes them
+    for (int m = warp; m < NT * 8; m += SK_WARPS) {
+      float sum = 0.0f;
+      if (nm.in_sumsq != nullptr && m < M)
+        for (int i = lane; i < nm.in_parts; i += 32) sum += nm.in_sumsq[(size_t)i * SK_NORM_ROWS + m];
+      sum = warp_sum(sum);
+      if (lane == 0) inv_rms[m] = nm.in_sumsq != nullptr ? rsqrtf(sum / (float)K + nm.in_eps) : 1.0f;
+    }
+  }
   for (int iu = 0; iu < units_per_cta && unit < n_units; ++iu, ++unit) {
     const int row0 = unit * 16 * RG;
     float acc[RG][NT][4];
@@ -149,30 +176,52 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
           gate += red[w][rg * 16 + ch][m];
           up += red[w][rg * 16 + ch + 8][m];
         }
+        if (NORM) {
+          gate *= inv_rms[m];
+          up *= inv_rms[m];
+        }
         const int col = (unit * RG + rg) * 8 + ch;
         if (row0 + rg * 16 + ch + 8 < N) ((bf16*)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
       }
     } else {
+      // 16 * RG * NT * 8 is a multiple of 128: whole warps enter an iteration, and the 16 * RG
+      // consecutive lanes that share a token row can sum over their columns with shuffles
       for (int idx = threadIdx.x; idx < 16 * RG * NT * 8; idx += SK_THREADS) {
         const int r = idx % (16 * RG), m = idx / (16 * RG);
         const int n = row0 + r;
-        if (m >= M || n >= N) continue;
+        const bool ok = m < M && n < N;
         float s = 0.0f;
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) s += red[w][r][m];
+        if (NORM) s *= inv_rms[m];
         const size_t o = (size_t)m * ldc + n;
-        if (EPI == HB_EPI_STORE) ((bf16*)Cv)[o] = __float2bfloat16_rn(s);
-        else if (EPI == HB_EPI_STORE_F32) ((float*)Cv)[o] = s;
-        else ((float*)Cv)[o] += s;
+        float sq = 0.0f;
+        if (ok) {
+          if (EPI == HB_EPI_STORE) ((bf16*)Cv)[o] = __float2bfloat16_rn(s);
+          else if (EPI == HB_EPI_STORE_F32) ((float*)Cv)[o] = s;
+          else {
+            const float v = ((float*)Cv)[o] + s;
+            ((float*)Cv)[o] = v;
+            if (NORM && nm.out_w != nullptr) {
+              nm.out_xw[(size_t)m * nm.out_ld + n] = __float2bfloat16_rn(v * nm.out_w[n]);
+              sq = v * v;
+            }
+          }
+        }
+        if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) {
+#pragma unroll
+          for (int d = 1; d < 16 * RG; d <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+          if (r == 0 && m < SK_NORM_ROWS) nm.out_sumsq[(size_t)unit * SK_NORM_ROWS + m] = sq;
+        }
       }
     }
     __syncthreads();   // the partial sums are read: the next unit may overwrite them
   }
 }
 
-template <int NT, int RG, int UNROLL>
+template <int NT, int RG, int UNROLL, bool NORM = false>
 static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C, int ldc, int M, int N, int K,
-                         int epi, cudaStream_t s) {
+                         int epi, cudaStream_t s, SkinnyNorm nm = SkinnyNorm{}) {
   // as many CTAs as the GPU holds at once (asked of the runtime for this instantiation), each with
   // an equal run of units
   static int slots = 0;
@@ -180,7 +229,7 @@ static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C
     int dev = 0, sms = 0, per_sm = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE>, SK_THREADS, 0) != cudaSuccess || per_sm <= 0) per_sm = 2;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE, NORM>, SK_THREADS, 0) != cudaSuccess || per_sm <= 0) per_sm = 2;
     slots = per_sm * sms;
   }
   const int n_units = ceil_div(N, 16 * RG);
@@ -188,10 +237,10 @@ static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C
   const int upc = (2 * n_units > 3 * slots) ? ceil_div(n_units, slots) : 1;
   const unsigned grid = (unsigned)ceil_div(n_units, upc);
   switch (epi) {
-    case HB_EPI_STORE: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
-    case HB_EPI_STORE_F32: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE_F32>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
-    case HB_EPI_RESIDUAL: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_RESIDUAL>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
-    case HB_EPI_SWIGLU: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_SWIGLU>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc); break;
+    case HB_EPI_STORE: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE, NORM>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc, nm); break;
+    case HB_EPI_STORE_F32: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_STORE_F32, NORM>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc, nm); break;
+    case HB_EPI_RESIDUAL: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_RESIDUAL, NORM>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc, nm); break;
+    case HB_EPI_SWIGLU: hb_launch_pdl(gemm_skinny_kernel<NT, RG, UNROLL, HB_EPI_SWIGLU, NORM>, dim3(grid), dim3(SK_THREADS), 0, s, A, lda, W, ldw, C, ldc, M, N, K, upc, nm); break;
     default: HB_FAIL(2, "gemm_skinny: unknown epilogue %d", epi);
   }
   HB_CHECK_LAUNCH("gemm_skinny");
@@ -199,6 +248,21 @@ static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C
 }
 
 // epi HB_EPI_SWIGLU: W holds 2I rows in groups of 16 (8 gate, 8 up); C is [M, I] bfloat16.
+static int skinny_rg_knob() {
+  static int rg_knob = -1;
+  if (rg_knob < 0) {
+    const char* e = getenv("HB_SKINNY_RG");        // tuning knob: 1 or 2 row groups per CTA; default by shape
+    rg_knob = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+  }
+  return rg_knob;
+}
+// Two row groups per CTA halve the activation traffic; worth it once there are several tokens
+// and enough rows that the grid still fills the GPU.
+static bool skinny_two_groups(int M, int N) {
+  const int k = skinny_rg_knob();
+  return M <= 16 && (k ? k == 2 : (M > 1 && N >= 8192));
+}
+
 extern "C" int hb_gemm_skinny_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
                                    int K, int epi, void* stream) {
   HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_skinny: sizes must be positive");
@@ -209,18 +273,45 @@ extern "C" int hb_gemm_skinny_bf16(const void* A, int lda, const void* W, int ld
   cudaStream_t s = (cudaStream_t)stream;
   const bf16* a = (const bf16*)A;
   const bf16* w = (const bf16*)W;
-  static int rg_knob = -1;
-  if (rg_knob < 0) {
-    const char* e = getenv("HB_SKINNY_RG");        // tuning knob: 1 or 2 row groups per CTA; default by shape
-    rg_knob = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
-  }
-  // Two row groups per CTA halve the activation traffic; worth it once there are several tokens
-  // and enough rows that the grid still fills the GPU.
-  const bool two = rg_knob ? rg_knob == 2 : (M > 1 && N >= 8192);
+  const bool two = skinny_two_groups(M, N);
   if (M <= 8) return two ? skinny_launch<1, 2, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s)
                          : skinny_launch<1, 1, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
   if (M <= 16) return two ? skinny_launch<2, 2, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s)
                           : skinny_launch<2, 1, 4>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
   if (M <= 32) return skinny_launch<4, 1, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
   return skinny_launch<8, 1, 2>(a, lda, w, ldw, C, ldc, M, N, K, epi, s);
+}
+
+// How many groups of output columns the product of an [M, K] activation with an [N, K] matrix
+// writes partial sums for (the first dimension of out_sumsq).
+extern "C" int hb_gemm_skinny_norm_parts(int M, int N) {
+  return ceil_div(N, skinny_two_groups(M, N) ? 32 : 16);
+}
+
+// The same product with a shared norm on either side (M <= 16):
+//   in_sumsq != null: A holds x * w of a norm over K; results are multiplied by 1 / rms of the rows,
+//     rms^2 = sum over in_parts partial sums / K + in_eps;
+//   out_w != null (epi HB_EPI_RESIDUAL): besides C += ..., out_xw = C * out_w (bfloat16) and
+//     out_sumsq[hb_gemm_skinny_norm_parts(M, N)][16] = partial sums of C^2.
+extern "C" int hb_gemm_skinny_norm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M,
+                                        int N, int K, int epi, const float* in_sumsq, int in_parts, float in_eps,
+                                        const float* out_w, void* out_xw, int out_ld, float* out_sumsq,
+                                        void* stream) {
+  HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_skinny_norm: sizes must be positive");
+  HB_REQUIRE(M <= SK_NORM_ROWS, "gemm_skinny_norm: at most %d activation rows, got %d", SK_NORM_ROWS, M);
+  HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_skinny_norm: K (%d) and the leading dimensions (%d, %d) must be multiples of 8", K, lda, ldw);
+  HB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_skinny_norm: operands must be 16-byte aligned");
+  HB_REQUIRE(epi != HB_EPI_SWIGLU || N % 16 == 0, "gemm_skinny_norm: SwiGLU rows come in groups of 16, N=%d", N);
+  HB_REQUIRE(in_sumsq == nullptr || in_parts > 0, "gemm_skinny_norm: partial sums without a count");
+  HB_REQUIRE(out_w == nullptr || (epi == HB_EPI_RESIDUAL && out_xw != nullptr && out_sumsq != nullptr),
+             "gemm_skinny_norm: the next norm's input is written by the residual epilogue and needs both outputs");
+  SkinnyNorm nm{in_sumsq, in_parts, in_eps, out_w, (bf16*)out_xw, out_ld, out_sumsq};
+  cudaStream_t s = (cudaStream_t)stream;
+  const bf16* a = (const bf16*)A;
+  const bf16* w = (const bf16*)W;
+  const bool two = skinny_two_groups(M, N);
+  if (M <= 8) return two ? skinny_launch<1, 2, 2, true>(a, lda, w, ldw, C, ldc, M, N, K, epi, s, nm)
+                         : skinny_launch<1, 1, 4, true>(a, lda, w, ldw, C, ldc, M, N, K, epi, s, nm);
+  return two ? skinny_launch<2, 2, 2, true>(a, lda, w, ldw, C, ldc, M, N, K, epi, s, nm)
+             : skinny_launch<2, 1, 4, true>(a, lda, w, ldw, C, ldc, M, N, K, epi, s, nm);
 }

@@ -98,8 +98,18 @@ class DecoderModel:
         ws.rewind()
         x = ws.take((batch.n_tokens, self.spec.hidden_size), torch.float32)
         ops.embed(self.embed, batch.token_ids, x)
-        for i, st in enumerate(self.spec.schedule):
-            self.blocks[st.layer].forward(x, batch, cache.view(i))
+        # a block may begin the first norm of the block that runs after it (parts/base.py)
+        sched, pending = self.spec.schedule, None
+        for i, st in enumerate(sched):
+            block = self.blocks[st.layer]
+            if not block.chains_norms:
+                block.forward(x, batch, cache.view(i))
+                pending = None
+                continue
+            nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
+            nxt_norm = nxt.first_norm() if nxt is not None and nxt.chains_norms else None
+            pending = block.forward(x, batch, cache.view(i), normed=pending,
+                                    next_norm=nxt_norm.shareable() if nxt_norm is not None else None)
         if batch.n_want == 0:
             return None
         hn = ws.take((batch.n_want, self.spec.hidden_size), self.rt.dtype)

@@ -34,6 +34,9 @@ _SIGS = {
                               c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_simt": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "hb_gemm_skinny_norm_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                 c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "hb_finish_norm": [c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "hb_gemm_tcgen05_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
@@ -48,6 +51,7 @@ _SIGS = {
     "hb_attention_decode_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
+    "hb_gemm_skinny_norm_parts": [c_int, c_int],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
 }
 _fns: dict = {}
@@ -202,6 +206,63 @@ def gemm_skinny(a, w, c, epilogue=EPI_STORE) -> None:
          a.shape[0], w.shape[0], a.shape[1], epilogue, _stream())
 
 
+SHARED_NORM_MAX_ROWS = 16
+SHARED_NORM = os.environ.get("HB_SHARED_NORM", "1") != "0"     # 0: every norm is a kernel of its own
+
+
+class PendingNorm:
+    """An RMSNorm that the product before it has begun and the product after it will finish.
+
+    `xw` [T, D] is x * w in bfloat16; `sumsq` [parts, 16] holds partial sums of x^2 per row, so that
+    y = xw / sqrt(sum(sumsq[:, row]) / D + eps).  A product kernel that takes it multiplies its
+    results by that row factor; `finish_norm` makes the plain y for anyone else."""
+
+    __slots__ = ("xw", "sumsq", "parts", "eps")
+
+    def __init__(self, xw, sumsq, parts, eps):
+        self.xw, self.sumsq, self.parts, self.eps = xw, sumsq, parts, eps
+
+    shape = property(lambda self: self.xw.shape)
+    dtype = property(lambda self: self.xw.dtype)
+
+
+def shared_norm_ok(n_rows: int, dtype, dim: int) -> bool:
+    """Whether products of `n_rows` activation rows can carry a norm over `dim` between them."""
+    return SHARED_NORM and dtype == torch.bfloat16 and n_rows <= SHARED_NORM_MAX_ROWS and dim % 8 == 0
+
+
+def finish_norm(p: PendingNorm, out: torch.Tensor) -> None:
+    _check(out, torch.bfloat16, "out")
+    _run("hb_finish_norm", p.xw.data_ptr(), p.xw.stride(0), p.sumsq.data_ptr(), p.parts, float(p.eps), out.data_ptr(),
+         out.stride(0), p.xw.shape[0], p.xw.shape[1], _stream())
+
+
+def gemm_skinny_norm(a, w, c, epilogue=EPI_STORE, next_norm=None, scratch=None):
+    """gemm_skinny with a norm shared on either side (at most 16 rows).  `a` may be a PendingNorm.
+    next_norm = (weight [N] float, eps) with EPI_RESIDUAL: returns the PendingNorm of the updated c,
+    its buffers taken from `scratch(shape, dtype)`."""
+    pend = a if isinstance(a, PendingNorm) else None
+    x = pend.xw if pend is not None else a
+    _check(x, torch.bfloat16, "a"); _check(w, torch.bfloat16, "w"); _check(c, None, "c")
+    M, N, K = x.shape[0], w.shape[0], x.shape[1]
+    out = None
+    if next_norm is not None:
+        nw, eps = next_norm
+        _check(nw, torch.float32, "next norm weight")
+        if epilogue != EPI_RESIDUAL or nw.numel() != N:
+            raise BackendError("gemm_skinny_norm: the next norm needs the residual epilogue and a weight per output column")
+        parts = int(_fn("hb_gemm_skinny_norm_parts")(M, N))
+        out = PendingNorm(scratch((M, N), torch.bfloat16), scratch((parts, 16), torch.float32), parts, eps)
+    _run("hb_gemm_skinny_norm_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
+         M, N, K, epilogue,
+         pend.sumsq.data_ptr() if pend is not None else None, pend.parts if pend is not None else 0,
+         float(pend.eps) if pend is not None else 0.0,
+         nw.data_ptr() if out is not None else None,
+         out.xw.data_ptr() if out is not None else None, out.xw.stride(0) if out is not None else 0,
+         out.sumsq.data_ptr() if out is not None else None, _stream())
+    return out
+
+
 _error_flags: dict = {}
 
 
@@ -294,12 +355,28 @@ def _skinny_ok(a, w) -> bool:
 
 
 # ---------------------------------------------------------------------------------------------
-def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE) -> None:
+def _plain_input(a, scratch):
+    if isinstance(a, PendingNorm):
+        h = scratch(a.xw.shape, torch.bfloat16)
+        finish_norm(a, h)
+        return h
+    return a
+
+
+def gemm(a, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE, next_norm=None, scratch=None):
     """c (op)= a @ w.T with the kernel that fits dtype and sizes.
 
     a [M, K] and w [N, K] share a dtype (float32: the true 32-bit product on the CUDA cores;
     bfloat16: tensor-core kernels where their size rules hold, else the any-shape kernel).
+    `a` may be a PendingNorm; next_norm = (weight, eps) asks for the PendingNorm of the updated c
+    (EPI_RESIDUAL), which is returned where the kernel can make it and None otherwise.
     """
+    x = a.xw if isinstance(a, PendingNorm) else a
+    small = x.dtype == torch.bfloat16 and x.shape[0] <= SHARED_NORM_MAX_ROWS and _skinny_ok(x, w)
+    if small and (isinstance(a, PendingNorm) or next_norm is not None) and scratch is not None \
+            and shared_norm_ok(x.shape[0], x.dtype, w.shape[0] if next_norm is not None else 8):
+        return gemm_skinny_norm(a, w, c, epilogue, next_norm, scratch)
+    a = _plain_input(a, scratch)
     if _skinny_ok(a, w):
         _decode_gemm(a, w)(a, w, c, epilogue)
     elif _tcgen05_ok(a, w):
@@ -308,9 +385,14 @@ def gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_
         gemm_simt(a, w, c, epilogue)
 
 
-def gemm_swiglu(a: torch.Tensor, wgu: torch.Tensor, out: torch.Tensor, interleave: int, scratch) -> None:
+def gemm_swiglu(a, wgu: torch.Tensor, out: torch.Tensor, interleave: int, scratch) -> None:
     """out = silu(gate) * up with [gate | up] = a @ wgu.T.  Fused into the product where a kernel can;
     otherwise the product goes to `scratch(shape, dtype)` and the SwiGLU kernel follows."""
+    if isinstance(a, PendingNorm):
+        if interleave == 8 and _skinny_ok(a.xw, wgu) and a.xw.shape[0] <= SHARED_NORM_MAX_ROWS:
+            gemm_skinny_norm(a, wgu, out, EPI_SWIGLU)
+            return
+        a = _plain_input(a, scratch)
     if interleave == 8 and _skinny_ok(a, wgu):
         _decode_gemm(a, wgu)(a, wgu, out, EPI_SWIGLU)
         return

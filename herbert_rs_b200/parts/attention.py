@@ -56,10 +56,12 @@ class AttentionMixer(Mixer):
     def cache_need(self):
         return CacheNeed(kv=KVNeed(self.nkv, self.hd, self.spec.window))
 
-    def forward(self, h, residual, batch, cache):
+    shares_norms = True
+
+    def forward(self, h, residual, batch, cache, next_norm=None):
         ws, T = self.rt.workspace, h.shape[0]
         qkv = ws.take((T, self.qkv_dim), h.dtype)
-        ops.gemm(h, self.wqkv, qkv)
+        ops.gemm(h, self.wqkv, qkv, scratch=ws.take)
         pages = batch.pages[cache.kv_group]
         pos = self.position
         ops.qk_norm_rope_cache(
@@ -70,7 +72,7 @@ class AttentionMixer(Mixer):
         att = ws.take((T, self.q_dim), h.dtype)
         ops.attention(qkv, qkv.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd,
                       cache.page_size, self.spec.scale, self.spec.window, pages, scratch=ws.take)
-        ops.gemm(att, self.wo, residual, ops.EPI_RESIDUAL)
+        return ops.gemm(att, self.wo, residual, ops.EPI_RESIDUAL, next_norm=next_norm, scratch=ws.take)
 
 
 register_part("mixer", "attention", AttentionMixer)

@@ -12,6 +12,14 @@ them through `load()`, and runs through `forward()`.  No part knows which model 
 
 `h` is in the activation dtype (float32 on the 32-bit path, bfloat16 otherwise); the residual
 stream is float on both paths.  `batch` is a `StepBatch`; `cache` a `CacheView`.
+
+Optional: a norm shared between two products.  Between "add into the residual stream" and "the
+next product" lies only a norm, and for a few rows its kernel is all latency.  A mixer or
+feed-forward that says `shares_norms = True` (1) accepts an `ops.PendingNorm` in place of `h` and
+(2) takes a keyword `next_norm=(weight, eps)`: it may then return the PendingNorm of the residual
+stream it has just updated (or None, and the caller runs the norm).  A norm offers itself for
+this with `shareable()`.  Parts without the flag never see either; the block finishes or runs
+the norm for them.
 """
 
 from __future__ import annotations
@@ -45,6 +53,8 @@ class Part:
     # steps.  A part that branches on the batch's host-side values must say False; the engine
     # then runs the model's decode steps eagerly.
     graph_safe = True
+    # True if forward() accepts an ops.PendingNorm as its input and a `next_norm` keyword.
+    shares_norms = False
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {}
@@ -60,6 +70,11 @@ class Part:
 class Norm(Part):
     def forward(self, x, out, rows=None) -> None:
         raise NotImplementedError
+
+    def shareable(self):
+        """(weight [D] float, eps) if this is y = x * w / sqrt(mean(x^2) + eps), which a product
+        before it and a product after it can compute between them; else None."""
+        return None
 
 
 class Mixer(Part):
@@ -79,5 +94,17 @@ class Block(Part):
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
 
-    def forward(self, x, batch, cache) -> None:
+    # True if forward() takes the keywords `normed` and `next_norm` below; a block without the flag is
+    # called as forward(x, batch, cache) and its neighbours run their norms themselves.
+    chains_norms = False
+
+    def first_norm(self):
+        """The norm this block applies to the stream before anything else, which the block before
+        it may begin; None if there is none to share."""
+        return None
+
+    def forward(self, x, batch, cache, normed=None, next_norm=None):
+        """Update x.  With `chains_norms`: `normed` is the PendingNorm of x under `first_norm()`,
+        begun by the block before (or None); `next_norm` is the following block's first norm as
+        (weight, eps); the block may return the PendingNorm of its result under it, or None."""
         raise NotImplementedError

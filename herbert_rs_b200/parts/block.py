@@ -3,6 +3,7 @@
 
 from __future__ import annotations
 
+from .. import ops
 from ..registry import build_part, register_part
 from .base import Block
 
@@ -41,14 +42,35 @@ class PreNormBlock(Block):
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, x, batch, cache):
-        ws = self.rt.workspace
-        h = ws.take(x.shape, self.rt.dtype)
-        self.norm1.forward(x, h)
-        self.mixer.forward(h, x, batch, cache)
-        h2 = ws.take(x.shape, self.rt.dtype)
-        self.norm2.forward(x, h2)
+    chains_norms = True
+
+    def first_norm(self):
+        return self.norm1
+
+    def _input(self, pending, norm, part, x):
+        """What `part` reads: the pending norm itself if it can finish it, else the plain result."""
+        if pending is not None and part.shares_norms:
+            return pending
+        h = self.rt.workspace.take(x.shape, self.rt.dtype)
+        if pending is not None:
+            ops.finish_norm(pending, h)
+        else:
+            norm.forward(x, h)
+        return h
+
+    def forward(self, x, batch, cache, normed=None, next_norm=None):
+        share = ops.shared_norm_ok(x.shape[0], self.rt.dtype, x.shape[1])
+        h = self._input(normed, self.norm1, self.mixer, x)
+        mid = self.norm2.shareable() if share and self.mixer.shares_norms else None
+        if self.mixer.shares_norms:
+            pending = self.mixer.forward(h, x, batch, cache, next_norm=mid)
+        else:
+            pending = self.mixer.forward(h, x, batch, cache)
+        h2 = self._input(pending, self.norm2, self.ffn, x)
+        if self.ffn.shares_norms:
+            return self.ffn.forward(h2, x, batch, next_norm=next_norm if share else None)
         self.ffn.forward(h2, x, batch)
+        return None
 
 
 register_part("block", "prenorm", PreNormBlock)

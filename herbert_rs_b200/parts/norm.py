@@ -25,5 +25,8 @@ class RMSNorm(Norm):
     def forward(self, x, out, rows=None):
         ops.rmsnorm(x, self.weight, out, self.eps, rows)
 
+    def shareable(self):
+        return (self.weight, self.eps)
+
 
 register_part("norm", "rmsnorm", RMSNorm)

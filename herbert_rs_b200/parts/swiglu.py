@@ -49,11 +49,13 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return (self.wgu.numel() + self.wd.numel()) * self.wgu.element_size()
 
-    def forward(self, h, residual, batch):
+    shares_norms = True
+
+    def forward(self, h, residual, batch, next_norm=None):
         ws, T, inter = self.rt.workspace, h.shape[0], self.spec.intermediate_size
         act = ws.take((T, inter), h.dtype)
         ops.gemm_swiglu(h, self.wgu, act, self.interleave, ws.take)
-        ops.gemm(act, self.wd, residual, ops.EPI_RESIDUAL)
+        return ops.gemm(act, self.wd, residual, ops.EPI_RESIDUAL, next_norm=next_norm, scratch=ws.take)
 
 
 register_part("ffn", "swiglu", SwiGLU)

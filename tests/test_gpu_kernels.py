@@ -308,6 +308,72 @@ def test_gemm_skinny_every_epilogue(M, N, K):
         close(out, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("H,N2,eps", [(96, 64, 1e-5), (304, 16 * 1024, 1e-6), (1000, 48, 3e-3)])
+def test_gemm_skinny_with_a_norm_shared_between_two_products(M, H, N2, eps):
+    """First product: x += a w1^T, and it begins RMSNorm(x; nw, eps).  Second product: finishes the
+    norm and multiplies with w2 (store, SwiGLU and residual epilogues).  Reference: the norm as a
+    step of its own in double precision, rounded to bfloat16 where the engine's plain path rounds."""
+    torch.manual_seed(31)
+    K1 = 72
+    a = torch.randn(M, K1).to(torch.bfloat16)
+    w1 = (torch.randn(H, K1) * 0.3).to(torch.bfloat16)
+    x0 = torch.randn(M, H) * 3.0
+    x0[0] *= 40.0                                             # rows of very different size: one factor per row
+    nw = 1.0 + 0.1 * torch.randn(H)
+    w2 = (torch.randn(N2, H) * 0.1).to(torch.bfloat16)
+    x_ref = x0.double() + a.double() @ w1.double().T
+    y_ref = x_ref / torch.sqrt((x_ref ** 2).mean(dim=1, keepdim=True) + eps) * nw.double()
+    out_ref = y_ref @ w2.double().T
+
+    bufs = []
+    def scratch(shape, dtype):
+        bufs.append(torch.full(shape, float("nan"), device="cuda", dtype=dtype))
+        return bufs[-1]
+    x = dev(x0.clone())
+    pend = ops.gemm(dev(a), dev(w1), x, ops.EPI_RESIDUAL, next_norm=(dev(nw), eps), scratch=scratch)
+    assert isinstance(pend, ops.PendingNorm) and pend.parts == int(pend.sumsq.shape[0])
+    close(x, x_ref, torch.float32)
+    assert not torch.isnan(pend.xw).any() and not torch.isnan(pend.sumsq[:, :M]).any()
+    torch.testing.assert_close(pend.sumsq[:, :M].sum(dim=0).double().cpu(), (x_ref ** 2).sum(dim=1), rtol=1e-5, atol=0)
+
+    y = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    ops.finish_norm(pend, y)
+    close(y, y_ref, torch.bfloat16)
+
+    c = torch.empty(M, N2, device="cuda", dtype=torch.bfloat16)
+    assert ops.gemm(pend, dev(w2), c, ops.EPI_STORE, scratch=scratch) is None
+    close(c, out_ref, torch.bfloat16)
+    res = torch.randn(M, N2)
+    r = dev(res.clone())
+    ops.gemm(pend, dev(w2), r, ops.EPI_RESIDUAL, scratch=scratch)
+    close(r, res.double() + out_ref, torch.bfloat16)
+    act = torch.empty(M, N2 // 2, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_swiglu(pend, dev(w2), act, 8, scratch)
+    blocks = out_ref.view(M, N2 // 16, 2, 8)
+    gate, up = blocks[:, :, 0].reshape(M, -1), blocks[:, :, 1].reshape(M, -1)
+    close(act, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
+    # twice in a row gives the same bits: the partial sums meet in a fixed order
+    c2 = torch.empty_like(c)
+    ops.gemm(pend, dev(w2), c2, ops.EPI_STORE, scratch=scratch)
+    assert torch.equal(c, c2)
+
+
+def test_a_pending_norm_is_finished_for_kernels_that_cannot_take_it():
+    """More rows than the shared-norm kernel takes never get a PendingNorm; a product that cannot
+    use the kernel for its sizes (K not a multiple of 8 is impossible here, so: float32) refuses."""
+    torch.manual_seed(2)
+    a, w1 = torch.randn(17, 64).to(torch.bfloat16), torch.randn(96, 64).to(torch.bfloat16)
+    x = torch.zeros(17, 96, device="cuda")
+    got = ops.gemm(dev(a), dev(w1), x, ops.EPI_RESIDUAL, next_norm=(torch.ones(96, device="cuda"), 1e-6),
+                   scratch=lambda shape, dtype: torch.empty(shape, device="cuda", dtype=dtype))
+    assert got is None
+    close(x, a.double() @ w1.double().T, torch.float32)
+    with pytest.raises(BackendError, match="residual epilogue"):
+        ops.gemm_skinny_norm(dev(a[:4]), dev(w1), torch.zeros(4, 96, device="cuda", dtype=torch.bfloat16), ops.EPI_STORE,
+                             next_norm=(torch.ones(96, device="cuda"), 1e-6), scratch=lambda s, d: torch.empty(s, device="cuda", dtype=d))
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do():
     a, w = dev(torch.zeros(65, 64, dtype=torch.bfloat16)), dev(torch.zeros(32, 64, dtype=torch.bfloat16))
     c = torch.empty(65, 32, device="cuda", dtype=torch.bfloat16)
