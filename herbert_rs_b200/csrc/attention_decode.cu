@@ -42,6 +42,28 @@ struct DecodeArgs {
   int stages;
 };
 
+// What the fused variant of the keys-as-M kernel needs besides: it takes the raw q/k/v row of each
+// sequence's new token, applies the per-head RMSNorm and the rotation to the query heads it serves
+// (and, in the CTA whose keys include the new position, to the new key, which it stores in the
+// cache together with the new value before it reads its pages), and the split that finishes last
+// combines all splits' partial results.  Three kernels' work in one launch.
+struct DecodeFuse {
+  const bf16* qkv;       // [B, ld]: q heads, then k heads, then v heads of the new token, as the projection left them
+  int ld;
+  const float* qw;       // per-head norm weights [hd] (null: no norm)
+  const float* kw;
+  float eps;
+  const float* cos_tab;  // [table_rows][hd / 2]
+  const float* sin_tab;
+  int table_rows;
+  int write_cache;       // 0: a layer that reads another layer's cache stores nothing
+  bf16* kcache_w;        // the same cache, writable
+  bf16* vcache_w;
+  int* counters;         // [B * nkv], zero between launches
+  bf16* out;             // [B, ldo]
+  int ldo;
+};
+
 // HDM: the largest head size this instantiation holds in registers (hd <= HDM, hd % 16 == 0).
 // EXACT: hd == HDM is known at compile time, so every size test and stride folds away.
 template <int HDM, bool EXACT>
@@ -287,10 +309,41 @@ __device__ __forceinline__ void mma16816_ab(float* d, const unsigned* a4, unsign
   mma16816(d, a4[0], a4[1], a4[2], a4[3], b0, b1);
 }
 
-template <int NH>
-__global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeArgs a) {
+__device__ __forceinline__ float2 ld_bf2(const bf16* p) {
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+  return make_float2(__bfloat162float(v.x), __bfloat162float(v.y));
+}
+__device__ __forceinline__ void st_bf2(bf16* p, float x, float y) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
+}
+
+// One head of 128 values by one warp: RMSNorm with weight w (if any), then the rotation of the
+// pairs (j, j + 64) by the angles of table row `trow`; lane l holds j = 2l, 2l+1.  The same
+// arithmetic, in the same order, as the stand-alone norm/rotation kernel.
+__device__ __forceinline__ void norm_rotate_head128(const bf16* x, bf16* dst, const float* w, float eps,
+                                                    const float* cos_tab, const float* sin_tab, int trow, int lane) {
+  const int j = 2 * lane;
+  float2 lo = ld_bf2(x + j), hi = ld_bf2(x + j + 64);
+  if (w != nullptr) {
+    float ss = lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
+    const float2 wl = *reinterpret_cast<const float2*>(w + j), wh = *reinterpret_cast<const float2*>(w + j + 64);
+    lo.x = (lo.x * inv) * wl.x; lo.y = (lo.y * inv) * wl.y;
+    hi.x = (hi.x * inv) * wh.x; hi.y = (hi.y * inv) * wh.y;
+  }
+  const float2 c = *reinterpret_cast<const float2*>(cos_tab + (size_t)trow * 64 + j);
+  const float2 sn = *reinterpret_cast<const float2*>(sin_tab + (size_t)trow * 64 + j);
+  st_bf2(dst + j, lo.x * c.x - hi.x * sn.x, lo.y * c.y - hi.y * sn.y);
+  st_bf2(dst + j + 64, lo.x * sn.x + hi.x * c.x, lo.y * sn.y + hi.y * c.y);
+}
+
+template <int NH, bool FUSED>
+__global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeArgs a, DecodeFuse f) {
   constexpr int HD = 128;
   extern __shared__ __align__(16) unsigned char smem[];
+  __shared__ __align__(16) bf16 sm_q[FUSED ? 8 * NH * HD : 8];
+  __shared__ int s_last;
   pdl_wait();
   pdl_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -313,6 +366,19 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   const size_t head_elems = (size_t)a.page_size * HD;
   __shared__ int page_ids[AD_MAX_TILES];
   for (int i = threadIdx.x; i < t1 - t0; i += AD_THREADS) page_ids[i] = pages[(t0 + i) / tiles_per_page];
+  const bool writer = FUSED && f.write_cache && t0 < t1 && t1 == tile_hi;   // this CTA's keys end with the new position
+  if (writer) {
+    // store the new token's key (normed, rotated) and value before the pages are read
+    const int trow = p < f.table_rows ? p : f.table_rows - 1;
+    const bf16* row = f.qkv + (size_t)b * f.ld;
+    const size_t dst = (((size_t)pages[p / a.page_size] * a.nkv + kvh) * a.page_size + (p % a.page_size)) * HD;
+    if (warp == 0) {
+      norm_rotate_head128(row + (size_t)(a.nh + kvh) * HD, f.kcache_w + dst, f.kw, f.eps, f.cos_tab, f.sin_tab, trow, lane);
+    } else if (warp == 1) {
+      const bf16* v = row + (size_t)(a.nh + a.nkv + kvh) * HD;
+      *reinterpret_cast<uint2*>(f.vcache_w + dst + 4 * lane) = *reinterpret_cast<const uint2*>(v + 4 * lane);
+    }
+  }
   __syncthreads();
 
   constexpr int SLOTS = HD / 16;
@@ -343,23 +409,6 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   const unsigned k_lane = (unsigned)((warp * 16 + (lm & 1) * 8 + (lane & 7)) * row_bytes + (lm >> 1) * 16);
   const unsigned v_lane = (unsigned)((warp * 16 + (lm >> 1) * 8 + (lane & 7)) * row_bytes + (lm & 1) * 16);
 
-  // B operand of the first product: Q^T, head g of each 8-head tile, d pairs (2t, 2t+1) and (2t+8, 2t+9)
-  unsigned qf[NH][HD / 16][2];
-  {
-    const bf16* qb = a.q + (size_t)b * a.ldq + (size_t)kvh * G * HD;
-#pragma unroll
-    for (int n = 0; n < NH; ++n) {
-      const int h = n * 8 + g;
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        qf[n][ks][0] = qf[n][ks][1] = 0u;
-        if (h < G) {
-          qf[n][ks][0] = *reinterpret_cast<const unsigned*>(qb + (size_t)h * HD + ks * 16 + 2 * t);
-          qf[n][ks][1] = *reinterpret_cast<const unsigned*>(qb + (size_t)h * HD + ks * 16 + 2 * t + 8);
-        }
-      }
-    }
-  }
   // per thread: heads n*8 + 2t and n*8 + 2t + 1
   float m[NH][2], l[NH][2], o[NH][HD / 16][4];
 #pragma unroll
@@ -374,6 +423,31 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   for (int i = 0; i < S - 1; ++i) {
     if (t0 + i < t1) issue(t0 + i, i);
     cp_async_commit();
+  }
+  if (FUSED) {
+    // the query heads of this group, normed and rotated, while the first pages are on their way
+    const int trow = p < f.table_rows ? p : f.table_rows - 1;
+    const bf16* row = f.qkv + (size_t)b * f.ld;
+    for (int h = warp; h < G; h += AD_WARPS)
+      norm_rotate_head128(row + (size_t)(kvh * G + h) * HD, sm_q + h * HD, f.qw, f.eps, f.cos_tab, f.sin_tab, trow, lane);
+    __syncthreads();
+  }
+  // B operand of the first product: Q^T, head g of each 8-head tile, d pairs (2t, 2t+1) and (2t+8, 2t+9)
+  unsigned qf[NH][HD / 16][2];
+  {
+    const bf16* qb = FUSED ? sm_q : a.q + (size_t)b * a.ldq + (size_t)kvh * G * HD;
+#pragma unroll
+    for (int n = 0; n < NH; ++n) {
+      const int h = n * 8 + g;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        qf[n][ks][0] = qf[n][ks][1] = 0u;
+        if (h < G) {
+          qf[n][ks][0] = *reinterpret_cast<const unsigned*>(qb + (size_t)h * HD + ks * 16 + 2 * t);
+          qf[n][ks][1] = *reinterpret_cast<const unsigned*>(qb + (size_t)h * HD + ks * 16 + 2 * t + 8);
+        }
+      }
+    }
   }
   for (int tile = t0; tile < t1; ++tile) {
     const int it = tile - t0;
@@ -491,11 +565,72 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
       ll += f * sm_l[w * HP + r];
     }
     const int h = kvh * G + r;
+    if (FUSED && a.nsplit == 1) {                            // nothing to combine with: the result itself
+      const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+      f.out[(size_t)b * f.ldo + (size_t)h * HD + d] = __float2bfloat16_rn(acc * inv);
+      continue;
+    }
     const size_t pi = ((size_t)b * a.nh + h) * a.nsplit + split;
     a.part_o[pi * HD + d] = acc;
     if (d == 0) {
       a.part_ml[pi * 2] = mm;
       a.part_ml[pi * 2 + 1] = ll;
+    }
+  }
+  if (FUSED && a.nsplit > 1) {
+    // The split that arrives last at this (sequence, kv head)'s counter combines all of them, in
+    // the order of the splits whoever it is, with the arithmetic of the combine kernel below.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* ctr = f.counters + (size_t)b * a.nkv + kvh;
+      const int old = atomicAdd(ctr, 1);
+      s_last = old == a.nsplit - 1;
+      if (s_last) *ctr = 0;                                  // every split has arrived: ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int ns = a.nsplit;
+    float* sm_ms = reinterpret_cast<float*>(smem);           // [G][ns] maxima, then [G][ns] sums (the pipeline's memory is free)
+    float* sm_ls = sm_ms + G * ns;
+    for (int idx = threadIdx.x; idx < G * ns; idx += AD_THREADS) {
+      const size_t e = ((size_t)b * a.nh + kvh * G) * ns + idx;   // heads of the group and their splits are contiguous
+      sm_ms[idx] = __ldcg(a.part_ml + e * 2);
+      sm_ls[idx] = __ldcg(a.part_ml + e * 2 + 1);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * (HD / 4); idx += AD_THREADS) {       // four values of one head per thread
+      const int r = idx / (HD / 4), d = (idx % (HD / 4)) * 4, h = kvh * G + r;
+      const float* po = a.part_o + ((size_t)b * a.nh + h) * ns * HD + d;
+      float mm = -INFINITY;
+      for (int sp = 0; sp < ns; ++sp) mm = fmaxf(mm, sm_ms[r * ns + sp]);
+      float ll = 0.0f;
+      for (int sp = 0; sp < ns; ++sp) {
+        const float ms = sm_ms[r * ns + sp];
+        if (ms != -INFINITY) ll += __expf(ms - mm) * sm_ls[r * ns + sp];
+      }
+      const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int sp0 = 0; sp0 < ns; sp0 += 8) {
+        float4 o8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          o8[j] = sp0 + j < ns ? __ldcg(reinterpret_cast<const float4*>(po + (size_t)(sp0 + j) * HD)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (sp0 + j < ns) {
+            const float ms = sm_ms[r * ns + sp0 + j];
+            if (ms != -INFINITY) {
+              const float e = __expf(ms - mm);
+              acc.x += e * o8[j].x; acc.y += e * o8[j].y; acc.z += e * o8[j].z; acc.w += e * o8[j].w;
+            }
+          }
+        }
+      }
+      bf16* dst = f.out + (size_t)b * f.ldo + (size_t)h * HD + d;
+      st_bf2(dst, acc.x * inv, acc.y * inv);
+      st_bf2(dst + 2, acc.z * inv, acc.w * inv);
     }
   }
 }
@@ -590,13 +725,13 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
     hb_launch(attention_decode_kernel<64, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   } else if (hd == 128 && !use_old_layout()) {
     if (nh / nkv <= 8) {
-      e = cudaFuncSetAttribute(attention_decode_km_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      e = cudaFuncSetAttribute(attention_decode_km_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-      hb_launch(attention_decode_km_kernel<1>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+      hb_launch(attention_decode_km_kernel<1, false>, dim3(grid), dim3(AD_THREADS), smem, s, a, DecodeFuse{});
     } else {
-      e = cudaFuncSetAttribute(attention_decode_km_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      e = cudaFuncSetAttribute(attention_decode_km_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-      hb_launch(attention_decode_km_kernel<2>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+      hb_launch(attention_decode_km_kernel<2, false>, dim3(grid), dim3(AD_THREADS), smem, s, a, DecodeFuse{});
     }
   } else if (hd == 128) {
     e = cudaFuncSetAttribute(attention_decode_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -615,5 +750,60 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   dim3 cgrid(nh, n_seqs);
   hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
   HB_CHECK_LAUNCH("attention_decode_combine");
+  return 0;
+}
+
+// Head size 128, one launch: per-head norm and rotation of the new token's q and k, the cache
+// write, attention over the cache, and the combination of the key splits.
+//   qkv [n_seqs, ld]: raw rows (q heads | k heads | v heads); qw/kw: norm weights [128] or both null;
+//   cos_tab/sin_tab [table_rows, 64]: the rotation covers the whole head;
+//   counters: n_seqs * nkv ints, zero before the first launch (the kernel leaves them zero);
+//   scratch as for hb_attention_decode_bf16.  seq_len counts the new token; its position is seq_len - 1.
+extern "C" int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out, int ldo, void* kcache, void* vcache,
+                                              const float* qw, const float* kw, float eps, const float* cos_tab,
+                                              const float* sin_tab, int table_rows, int write_cache,
+                                              const int* seq_len, const int* seq_pages, int pages_stride,
+                                              float* scratch, int* counters, int n_seqs, int nh, int nkv,
+                                              int page_size, int nsplit, float scale, int window, void* stream) {
+  const int hd = 128;
+  HB_REQUIRE(n_seqs > 0 && nh > 0 && nkv > 0, "attention_decode_fused: sizes must be positive");
+  HB_REQUIRE(nh % nkv == 0, "attention_decode_fused: %d query heads are not a multiple of %d key/value heads", nh, nkv);
+  HB_REQUIRE(nh / nkv <= 16, "attention_decode_fused: at most 16 query heads per key/value head, got %d", nh / nkv);
+  HB_REQUIRE(page_size % AD_TILE == 0, "attention_decode_fused: page size %d must be a multiple of %d", page_size, AD_TILE);
+  HB_REQUIRE(nsplit >= 1 && nsplit <= 65535 && n_seqs <= 65535 && nkv <= 65535, "attention_decode_fused: grid too large");
+  HB_REQUIRE(ld % 4 == 0 && ((uintptr_t)qkv & 7) == 0, "attention_decode_fused: q/k/v rows must be 8-byte aligned");
+  HB_REQUIRE(ldo % 2 == 0 && ((uintptr_t)out & 3) == 0, "attention_decode_fused: output rows must be 4-byte aligned");
+  HB_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "attention_decode_fused: cache must be 16-byte aligned");
+  HB_REQUIRE((qw == nullptr) == (kw == nullptr), "attention_decode_fused: norm weights for both q and k, or for neither");
+  HB_REQUIRE(qw == nullptr || ((((uintptr_t)qw | (uintptr_t)kw) & 7) == 0), "attention_decode_fused: norm weights must be 8-byte aligned");
+  HB_REQUIRE(cos_tab != nullptr && sin_tab != nullptr && table_rows > 0 && ((((uintptr_t)cos_tab | (uintptr_t)sin_tab) & 7) == 0),
+             "attention_decode_fused: needs rotation tables, 8-byte aligned");
+  HB_REQUIRE(window >= 0, "attention_decode_fused: window must be >= 0");
+  HB_REQUIRE(counters != nullptr && scratch != nullptr, "attention_decode_fused: needs counters and scratch");
+  HB_REQUIRE((long long)(nh / nkv) * nsplit * 8 <= 64 * 1024, "attention_decode_fused: %d heads per group x %d splits exceed the combine's shared memory", nh / nkv, nsplit);
+  HB_REQUIRE((long long)pages_stride * (page_size / AD_TILE) <= (long long)AD_MAX_TILES * nsplit,
+             "attention_decode_fused: %d pages per sequence in %d splits exceed %d tiles per CTA", pages_stride, nsplit, AD_MAX_TILES);
+  cudaStream_t s = (cudaStream_t)stream;
+  int stages = 3;
+  if (decode_smem_bytes(hd, stages) > 110 * 1024) stages = 2;
+  const int smem = decode_smem_bytes(hd, stages);
+  float* part_o = scratch;
+  float* part_ml = scratch + (size_t)n_seqs * nh * nsplit * hd;
+  DecodeArgs a{nullptr, 0, (const bf16*)kcache, (const bf16*)vcache, seq_len, seq_pages, pages_stride,
+               part_o, part_ml, nh, nkv, hd, page_size, nsplit, scale, window, stages};
+  DecodeFuse f{(const bf16*)qkv, ld, qw, kw, eps, cos_tab, sin_tab, table_rows, write_cache, (bf16*)kcache, (bf16*)vcache,
+               counters, (bf16*)out, ldo};
+  dim3 grid(nsplit, nkv, n_seqs);
+  cudaError_t e;
+  if (nh / nkv <= 8) {
+    e = cudaFuncSetAttribute(attention_decode_km_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_decode_fused: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    hb_launch(attention_decode_km_kernel<1, true>, dim3(grid), dim3(AD_THREADS), smem, s, a, f);
+  } else {
+    e = cudaFuncSetAttribute(attention_decode_km_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) HB_FAIL(3, "attention_decode_fused: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    hb_launch(attention_decode_km_kernel<2, true>, dim3(grid), dim3(AD_THREADS), smem, s, a, f);
+  }
+  HB_CHECK_LAUNCH("attention_decode_fused");
   return 0;
 }

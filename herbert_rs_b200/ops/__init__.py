@@ -44,6 +44,9 @@ _SIGS = {
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_decode_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "hb_attention_decode_fused_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                       c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -427,6 +430,36 @@ def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch,
     _run("hb_attention_decode_bf16", q.data_ptr(), int(ldq), out.data_ptr(), out.stride(0), k_cache.data_ptr(),
          v_cache.data_ptr(), seq_len.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0), scratch.data_ptr(),
          n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0), _stream())
+
+
+DECODE_FUSED = os.environ.get("HB_DECODE_FUSED", "1") != "0"   # 0: norm/rotation/cache write, attention and combine as separate kernels
+_DECODE_COUNTERS = 65536
+_decode_counters: dict = {}
+
+
+def attention_decode_fused_ok(qkv, out, num_heads, num_kv_heads, head_dim, page_size, rotary_dim, n_seqs) -> bool:
+    """Whether one launch can do norm, rotation, cache write, attention and combine for this step."""
+    return (DECODE_FUSED and DECODE_ATTENTION == "mma" and out.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
+            and head_dim == 128 and rotary_dim == head_dim and num_heads // num_kv_heads <= 16 and page_size % 64 == 0
+            and qkv.stride(0) % 4 == 0 and qkv.data_ptr() % 8 == 0 and n_seqs * num_kv_heads <= _DECODE_COUNTERS)
+
+
+def attention_decode_fused(qkv, out, k_cache, v_cache, q_weight, k_weight, eps, cos, sin, write_cache, seq_len,
+                           seq_pages, scratch, num_heads, num_kv_heads, page_size, nsplit, scale, window) -> None:
+    """Head size 128: the new token's q and k get their per-head norm and rotation, k and v go into
+    the cache, every query attends its sequence's keys, and the key splits are combined: one kernel."""
+    _check(out, torch.bfloat16, "out"); _check(scratch, torch.float32, "scratch"); _check(qkv, torch.bfloat16, "qkv")
+    n = out.shape[0]
+    if scratch.numel() < attention_decode_scratch_floats(n, num_heads, 128, nsplit):
+        raise BackendError("attention_decode_fused: scratch is too small")
+    key = str(out.device)
+    if key not in _decode_counters:
+        _decode_counters[key] = torch.zeros(_DECODE_COUNTERS, dtype=torch.int32, device=out.device)
+    _run("hb_attention_decode_fused_bf16", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0),
+         k_cache.data_ptr(), v_cache.data_ptr(), _ptr(q_weight), _ptr(k_weight), float(eps), cos.data_ptr(), sin.data_ptr(),
+         cos.shape[0], 1 if write_cache else 0, seq_len.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0),
+         scratch.data_ptr(), _decode_counters[key].data_ptr(), n, num_heads, num_kv_heads, page_size, int(nsplit),
+         float(scale), int(window or 0), _stream())
 
 
 def attention_prefill(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq_pages, n_seqs, max_q_len,

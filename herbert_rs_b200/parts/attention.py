@@ -64,14 +64,23 @@ class AttentionMixer(Mixer):
         ops.gemm(h, self.wqkv, qkv, scratch=ws.take)
         pages = batch.pages[cache.kv_group]
         pos = self.position
-        ops.qk_norm_rope_cache(
-            qkv, self.q_norm, self.k_norm, self.spec.qk_norm.eps if self.spec.qk_norm is not None else 0.0,
-            pos.cos if pos is not None else None, pos.sin if pos is not None else None,
-            pos.rotary_dim if pos is not None else 0, batch.tok_seq, batch.tok_pos, pages,
-            cache.k, cache.v, self.nh, self.nkv, self.hd, cache.page_size, write_cache=cache.writes_kv)
         att = ws.take((T, self.q_dim), h.dtype)
-        ops.attention(qkv, qkv.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd,
-                      cache.page_size, self.spec.scale, self.spec.window, pages, scratch=ws.take)
+        norm_eps = self.spec.qk_norm.eps if self.spec.qk_norm is not None else 0.0
+        if batch.is_decode and pos is not None and ops.attention_decode_fused_ok(
+                qkv, att, self.nh, self.nkv, self.hd, cache.page_size, pos.rotary_dim, batch.n_seqs):
+            nsplit = ops.decode_splits(batch.n_seqs, self.nkv, pages.shape[1] * (cache.page_size // 64))
+            buf = ws.take((ops.attention_decode_scratch_floats(batch.n_seqs, self.nh, self.hd, nsplit),), torch.float32)
+            ops.attention_decode_fused(qkv, att, cache.k, cache.v, self.q_norm, self.k_norm, norm_eps, pos.cos, pos.sin,
+                                       cache.writes_kv, batch.seq_len, pages, buf, self.nh, self.nkv, cache.page_size,
+                                       nsplit, self.spec.scale, self.spec.window)
+        else:
+            ops.qk_norm_rope_cache(
+                qkv, self.q_norm, self.k_norm, norm_eps,
+                pos.cos if pos is not None else None, pos.sin if pos is not None else None,
+                pos.rotary_dim if pos is not None else 0, batch.tok_seq, batch.tok_pos, pages,
+                cache.k, cache.v, self.nh, self.nkv, self.hd, cache.page_size, write_cache=cache.writes_kv)
+            ops.attention(qkv, qkv.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd,
+                          cache.page_size, self.spec.scale, self.spec.window, pages, scratch=ws.take)
         return ops.gemm(att, self.wo, residual, ops.EPI_RESIDUAL, next_norm=next_norm, scratch=ws.take)
 
 

@@ -398,6 +398,54 @@ def test_attention_decode_kernel(nh, nkv, hd, window, nsplit):
     close(out, c["ref"], torch.bfloat16)
 
 
+@pytest.mark.parametrize("nh,nkv,window,nsplit,norm", [(8, 2, 0, 1, True), (8, 2, 0, 3, True), (4, 4, 100, 2, False),
+                                                       (12, 1, 0, 4, True), (16, 8, 70, 5, True)])
+def test_attention_decode_fused_equals_the_three_kernels_it_replaces(nh, nkv, window, nsplit, norm):
+    """Norm + rotation + cache write, attention, combine in one launch (head size 128) against the
+    same work as separate kernels: the bits of the output and of the cache must agree, the counters
+    must be back at zero (second call), and a reader of another layer's cache writes nothing."""
+    torch.manual_seed(21)
+    hd, page, eps = 128, 64, 1e-6
+    lens = [1, 64, 65, 300, 129, 17, 128]          # lengths after the step: new tokens at 0, 63, 64 (a new page), ...
+    B = len(lens)
+    n_pages = sum(-(-n // page) for n in lens) + 3
+    order = torch.randperm(n_pages, generator=torch.Generator().manual_seed(3)).tolist()
+    P = max(-(-n // page) for n in lens)
+    table = torch.zeros(B, P, dtype=torch.int32)
+    for b, n in enumerate(lens):
+        for lp in range(-(-n // page)):
+            table[b, lp] = order.pop()
+    kc = torch.randn(n_pages, nkv, page, hd).to(torch.bfloat16).cuda()
+    vc = torch.randn(n_pages, nkv, page, hd).to(torch.bfloat16).cuda()
+    qkv = (torch.randn(B, (nh + 2 * nkv) * hd + 8) * 2).to(torch.bfloat16).cuda()
+    qw, kw = (dev(1 + 0.1 * torch.randn(hd)), dev(1 + 0.1 * torch.randn(hd))) if norm else (None, None)
+    cos, sin = (dev(t) for t in rope_tables(hd, 10000.0, 320, torch.float32))
+    seq_len = dev(torch.tensor(lens, dtype=torch.int32))
+    tok_seq = dev(torch.arange(B, dtype=torch.int32))
+    tok_pos = dev(torch.tensor([n - 1 for n in lens], dtype=torch.int32))
+    scale = hd ** -0.5
+    n_scratch = ops.attention_decode_scratch_floats(B, nh, hd, nsplit)
+
+    k1, v1, q1 = kc.clone(), vc.clone(), qkv.clone()
+    ops.qk_norm_rope_cache(q1, qw, kw, eps, cos, sin, hd, tok_seq, tok_pos, dev(table), k1, v1, nh, nkv, hd, page)
+    ref = torch.empty(B, nh * hd, device="cuda", dtype=torch.bfloat16)
+    ops.attention_decode(q1, q1.stride(0), ref, k1, v1, seq_len, dev(table), torch.empty(n_scratch, device="cuda"),
+                         nh, nkv, hd, page, nsplit, scale, window)
+    for _ in range(2):
+        k2, v2 = kc.clone(), vc.clone()
+        out = torch.full((B, nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.attention_decode_fused(qkv, out, k2, v2, qw, kw, eps, cos, sin, True, seq_len, dev(table),
+                                   torch.full((n_scratch,), float("nan"), device="cuda"), nh, nkv, page, nsplit, scale, window)
+        assert torch.equal(out, ref)
+        assert torch.equal(k2, k1) and torch.equal(v2, v1)
+    # write_cache=False: the cache already holds the new position (written by the layer that owns it)
+    k3, v3 = k1.clone(), v1.clone()
+    out = torch.empty_like(ref)
+    ops.attention_decode_fused(qkv, out, k3, v3, qw, kw, eps, cos, sin, False, seq_len, dev(table),
+                               torch.empty(n_scratch, device="cuda"), nh, nkv, page, nsplit, scale, window)
+    assert torch.equal(out, ref) and torch.equal(k3, k1) and torch.equal(v3, v1)
+
+
 def test_attention_decode_finds_a_far_key_and_the_windows_edge():
     nh, nkv, hd = 8, 2, 128
     lens = [1500, 700]
