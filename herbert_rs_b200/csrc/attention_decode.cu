@@ -83,9 +83,10 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs
   const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
   const int tile_lo = lo / AD_TILE, tile_hi = (len + AD_TILE - 1) / AD_TILE;   // tiles [tile_lo, tile_hi)
   const int ntiles = tile_hi - tile_lo;
-  const int per = (ntiles + a.nsplit - 1) / a.nsplit;
-  const int t0 = tile_lo + split * per;
-  const int t1 = min(tile_hi, t0 + per);
+  // tiles dealt evenly: the first ntiles % nsplit splits take one more than the others
+  const int per = ntiles / a.nsplit, extra = ntiles % a.nsplit;
+  const int t0 = tile_lo + split * per + min(split, extra);
+  const int t1 = t0 + per + (split < extra ? 1 : 0);
   const int tiles_per_page = a.page_size / AD_TILE;
   const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
   const size_t head_elems = (size_t)a.page_size * hd;
@@ -358,9 +359,10 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
   const int tile_lo = lo / AD_TILE, tile_hi = (len + AD_TILE - 1) / AD_TILE;
   const int ntiles = tile_hi - tile_lo;
-  const int per = (ntiles + a.nsplit - 1) / a.nsplit;
-  const int t0 = tile_lo + split * per;
-  const int t1 = min(tile_hi, t0 + per);
+  // tiles dealt evenly: the first ntiles % nsplit splits take one more than the others
+  const int per = ntiles / a.nsplit, extra = ntiles % a.nsplit;
+  const int t0 = tile_lo + split * per + min(split, extra);
+  const int t1 = t0 + per + (split < extra ? 1 : 0);
   const int tiles_per_page = a.page_size / AD_TILE;
   const int* pages = a.seq_pages + (size_t)b * a.pages_stride;
   const size_t head_elems = (size_t)a.page_size * HD;
@@ -684,6 +686,15 @@ static int decode_smem_bytes(int hd, int stages) {
   return pipeline > merge ? pipeline : merge;
 }
 
+static int decode_stages(int hd) {
+  static int want_stages = 0;
+  if (want_stages == 0) {
+    const char* e = getenv("HB_DECODE_STAGES");      // tuning knob: 2 or 3 (default 3 where it fits twice per SM)
+    want_stages = (e && (e[0] == '2' || e[0] == '3')) ? e[0] - '0' : 3;
+  }
+  return decode_smem_bytes(hd, want_stages) > 110 * 1024 ? 2 : want_stages;
+}
+
 extern "C" long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int hd, int nsplit) {
   return (long long)n_seqs * nh * nsplit * (hd + 2);
 }
@@ -705,13 +716,7 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   HB_REQUIRE((long long)pages_stride * (page_size / AD_TILE) <= (long long)AD_MAX_TILES * nsplit,
              "attention_decode: %d pages per sequence in %d splits exceed %d tiles per CTA", pages_stride, nsplit, AD_MAX_TILES);
   cudaStream_t s = (cudaStream_t)stream;
-  static int want_stages = 0;
-  if (want_stages == 0) {
-    const char* e = getenv("HB_DECODE_STAGES");      // tuning knob: 2 or 3 (default 3 where it fits twice per SM)
-    want_stages = (e && (e[0] == '2' || e[0] == '3')) ? e[0] - '0' : 3;
-  }
-  int stages = want_stages;
-  if (decode_smem_bytes(hd, stages) > 110 * 1024) stages = 2;
+  const int stages = decode_stages(hd);
   const int smem = decode_smem_bytes(hd, stages);
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)n_seqs * nh * nsplit * hd;
@@ -784,8 +789,7 @@ extern "C" int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out
   HB_REQUIRE((long long)pages_stride * (page_size / AD_TILE) <= (long long)AD_MAX_TILES * nsplit,
              "attention_decode_fused: %d pages per sequence in %d splits exceed %d tiles per CTA", pages_stride, nsplit, AD_MAX_TILES);
   cudaStream_t s = (cudaStream_t)stream;
-  int stages = 3;
-  if (decode_smem_bytes(hd, stages) > 110 * 1024) stages = 2;
+  const int stages = decode_stages(hd);
   const int smem = decode_smem_bytes(hd, stages);
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)n_seqs * nh * nsplit * hd;
