@@ -406,27 +406,27 @@ extern "C" int hb_add_residual(int dtype, float* res, const void* y, int ld, int
 }
 
 // Finishes a norm that a product left half done: out = xw / rms, with rms^2 = sum of the row's
-// partial sums / dim + eps (xw = x * w in bfloat16, sumsq [parts][16]).  For consumers that cannot
-// apply the row factor themselves.
+// partial sums / dim + eps (xw = x * w in bfloat16, sumsq [parts][stride]).  For consumers that
+// cannot apply the row factor themselves.
 __global__ void finish_norm_kernel(const bf16* __restrict__ xw, int ld, const float* __restrict__ sumsq, int parts,
-                                   float eps, bf16* __restrict__ out, int ldo, int dim) {
+                                   int stride, float eps, bf16* __restrict__ out, int ldo, int dim) {
   __shared__ float red[32];
   pdl_wait();
   pdl_launch();
   const int m = blockIdx.x;
   float s = 0.0f;
-  for (int i = threadIdx.x; i < parts; i += blockDim.x) s += sumsq[(size_t)i * 16 + m];
+  for (int i = threadIdx.x; i < parts; i += blockDim.x) s += sumsq[(size_t)i * stride + m];
   s = block_sum(s, red);
   const float inv = rsqrtf(s / (float)dim + eps);
   for (int k = threadIdx.x; k < dim; k += blockDim.x)
     out[(size_t)m * ldo + k] = __float2bfloat16_rn(__bfloat162float(xw[(size_t)m * ld + k]) * inv);
 }
 
-extern "C" int hb_finish_norm(const void* xw, int ld, const float* sumsq, int parts, float eps, void* out, int ldo,
-                              int n_rows, int dim, void* stream) {
-  HB_REQUIRE(n_rows > 0 && n_rows <= 16 && dim > 0 && parts > 0, "finish_norm: 1..16 rows, positive sizes");
-  hb_launch(finish_norm_kernel, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (const bf16*)xw, ld, sumsq, parts, eps,
-            (bf16*)out, ldo, dim);
+extern "C" int hb_finish_norm(const void* xw, int ld, const float* sumsq, int parts, int stride, float eps, void* out,
+                              int ldo, int n_rows, int dim, void* stream) {
+  HB_REQUIRE(n_rows > 0 && dim > 0 && parts > 0 && stride >= n_rows, "finish_norm: positive sizes, row stride >= rows");
+  hb_launch(finish_norm_kernel, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (const bf16*)xw, ld, sumsq, parts, stride,
+            eps, (bf16*)out, ldo, dim);
   HB_CHECK_LAUNCH("finish_norm");
   return 0;
 }

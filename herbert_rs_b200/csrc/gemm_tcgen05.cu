@@ -40,10 +40,25 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int BN, int EPI>
+// A norm shared between two products (see gemm_skinny.cu): RMSNorm y = x * w / rms(x) between "add
+// into the residual stream x" and "the next product".  The residual epilogue also writes x * w in
+// bfloat16 and, per tile of BN output columns, each row's sum of x^2; the product that reads x * w
+// multiplies its results by 1 / rms, summed from those partial sums in the order of the tiles.
+struct TgNorm {
+  const float* in_sumsq;   // consumer: [in_parts][in_stride] partial sums of the activation rows, or null
+  int in_parts, in_stride;
+  float in_eps;
+  const float* out_w;      // producer (residual epilogue): the next norm's weight [N], or null
+  bf16* out_xw;            // [M, out_ld]
+  int out_ld;
+  float* out_sumsq;        // [ceil(N / BN)][out_stride]
+  int out_stride;
+};
+
+template <int BN, int EPI, bool NORM>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
-                    int ldc, int M, int N, int K, int* error_flag) {
+                    int ldc, int M, int N, int K, int* error_flag, TgNorm nm) {
   constexpr int STAGES = TgSmem<BN>::kStages;
   constexpr int STAGE_BYTES = TgSmem<BN>::kStageBytes;
   extern __shared__ unsigned char smem_raw[];
@@ -149,6 +164,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const int buf = local & 1;
       const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+      const int m = m0 + quad * 32 + lane;
+      float inv_rms = 1.0f, sq = 0.0f;
+      if (NORM && nm.in_sumsq != nullptr && m < M) {         // while the tensor cores still work on this tile
+        float sum = 0.0f;
+        for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
+        inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+      }
       if (!mbar_wait(acc_full(buf), (local >> 1) & 1)) {
         if (lane == 0) atomicExch(error_flag, 3);
         ok = false;
@@ -156,7 +178,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       tc_fence_after();
       const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
-      const int m = m0 + quad * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         unsigned r[32];
@@ -169,6 +190,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         const int n = n0 + c * 32;
         if (m < M) {
+          if (NORM) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * inv_rms);
+          }
           if (EPI == HB_EPI_SWIGLU) {
             // columns: [8 gate | 8 up] x 2 -> 16 outputs; output column = n/2 + ...
             bf16* out = (bf16*)Cv + (size_t)m * ldc + (n >> 1);
@@ -215,28 +240,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
           } else {
             float* out = (float*)Cv + (size_t)m * ldc + n;
-            if (n + 32 <= N && ((((size_t)m * ldc + n) & 3) == 0)) {
+            const bool begin_norm = NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr;
+            bf16* xw = begin_norm ? nm.out_xw + (size_t)m * nm.out_ld + n : nullptr;
+            if (n + 32 <= N && ((((size_t)m * ldc + n) & 3) == 0) && (!begin_norm || ((((size_t)m * nm.out_ld + n) & 7) == 0))) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                float4* o4 = reinterpret_cast<float4*>(out + j);
-                if (EPI == HB_EPI_RESIDUAL) {
-                  const float4 old = *o4;
-                  v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
+#pragma unroll
+                for (int h = 0; h < 8; h += 4) {
+                  float4* o4 = reinterpret_cast<float4*>(out + j + h);
+                  float4 t4 = make_float4(__uint_as_float(r[j + h]), __uint_as_float(r[j + h + 1]), __uint_as_float(r[j + h + 2]), __uint_as_float(r[j + h + 3]));
+                  if (EPI == HB_EPI_RESIDUAL) {
+                    const float4 old = *o4;
+                    t4.x += old.x; t4.y += old.y; t4.z += old.z; t4.w += old.w;
+                  }
+                  *o4 = t4;
+                  v[h] = t4.x; v[h + 1] = t4.y; v[h + 2] = t4.z; v[h + 3] = t4.w;
                 }
-                *o4 = v;
+                if (begin_norm) {
+                  const float4 w0 = *reinterpret_cast<const float4*>(nm.out_w + n + j), w1 = *reinterpret_cast<const float4*>(nm.out_w + n + j + 4);
+#pragma unroll
+                  for (int h = 0; h < 8; ++h) sq += v[h] * v[h];
+                  uint4 pk;
+                  pk.x = pack2(v[0] * w0.x, v[1] * w0.y); pk.y = pack2(v[2] * w0.z, v[3] * w0.w);
+                  pk.z = pack2(v[4] * w1.x, v[5] * w1.y); pk.w = pack2(v[6] * w1.z, v[7] * w1.w);
+                  *reinterpret_cast<uint4*>(xw + j) = pk;
+                }
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (n + j < N) {
-                  if (EPI == HB_EPI_RESIDUAL) out[j] += __uint_as_float(r[j]);
-                  else out[j] = __uint_as_float(r[j]);
+                  float v = __uint_as_float(r[j]);
+                  if (EPI == HB_EPI_RESIDUAL) v += out[j];
+                  out[j] = v;
+                  if (begin_norm) {
+                    xw[j] = __float2bfloat16_rn(v * nm.out_w[n + j]);
+                    sq += v * v;
+                  }
                 }
             }
           }
         }
       }
+      if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr && m < M)
+        nm.out_sumsq[(size_t)(tile / tiles_m) * nm.out_stride + m] = sq;
     }
   }
   tc_fence_before();
@@ -247,13 +295,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool NORM>
 static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int* err,
-                     cudaStream_t s) {
+                     cudaStream_t s, const TgNorm& nm) {
   const int smem = TgSmem<BN>::kBytes;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
@@ -265,19 +313,19 @@ static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
   }
   const int tiles = ceil_div(M, TG_BM) * ceil_div(N, BN);
   dim3 grid(tiles < sms ? tiles : sms);
-  hb_launch(gemm_tcgen05_kernel<BN, EPI>, dim3(grid), dim3(TG_THREADS), smem, s, ma, mw, C, ldc, M, N, K, err);
+  hb_launch(gemm_tcgen05_kernel<BN, EPI, NORM>, dim3(grid), dim3(TG_THREADS), smem, s, ma, mw, C, ldc, M, N, K, err, nm);
   HB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }
 
-template <int BN>
+template <int BN, bool NORM>
 static int tg_dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int epi,
-                       int* err, cudaStream_t s) {
+                       int* err, cudaStream_t s, const TgNorm& nm) {
   switch (epi) {
-    case HB_EPI_STORE: return tg_launch<BN, HB_EPI_STORE>(ma, mw, C, ldc, M, N, K, err, s);
-    case HB_EPI_STORE_F32: return tg_launch<BN, HB_EPI_STORE_F32>(ma, mw, C, ldc, M, N, K, err, s);
-    case HB_EPI_RESIDUAL: return tg_launch<BN, HB_EPI_RESIDUAL>(ma, mw, C, ldc, M, N, K, err, s);
-    case HB_EPI_SWIGLU: return tg_launch<BN, HB_EPI_SWIGLU>(ma, mw, C, ldc, M, N, K, err, s);
+    case HB_EPI_STORE: return tg_launch<BN, HB_EPI_STORE, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
+    case HB_EPI_STORE_F32: return tg_launch<BN, HB_EPI_STORE_F32, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
+    case HB_EPI_RESIDUAL: return tg_launch<BN, HB_EPI_RESIDUAL, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
+    case HB_EPI_SWIGLU: return tg_launch<BN, HB_EPI_SWIGLU, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
   }
   HB_FAIL(2, "gemm_tcgen05: unknown epilogue %d", epi);
 }
@@ -298,6 +346,40 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   rc = make_map(&mw, W, N, K, ldw, BN);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  return BN == 256 ? tg_dispatch<256>(ma, mw, C, ldc, M, N, K, epi, error_flag, s)
-                   : tg_dispatch<128>(ma, mw, C, ldc, M, N, K, epi, error_flag, s);
+  const TgNorm none{};
+  return BN == 256 ? tg_dispatch<256, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none)
+                   : tg_dispatch<128, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
+}
+
+// Tiles of output columns, i.e. rows of out_sumsq, of a product with N output columns.
+extern "C" int hb_gemm_tcgen05_norm_parts(int N) { return ceil_div(N, N > 128 ? 256 : 128); }
+
+// The same product with a shared norm on either side (any M):
+//   in_sumsq != null: A holds x * w of a norm over K; results are multiplied by 1 / rms of the rows,
+//     rms^2 = sum_i in_sumsq[i * in_stride + row] / K + in_eps, i < in_parts;
+//   out_w != null (epi HB_EPI_RESIDUAL): besides C += ..., out_xw = C * out_w (bfloat16) and
+//     out_sumsq[hb_gemm_tcgen05_norm_parts(N)][out_stride] = partial sums of C^2 (out_stride >= M).
+extern "C" int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M,
+                                         int N, int K, int epi, const float* in_sumsq, int in_parts, int in_stride,
+                                         float in_eps, const float* out_w, void* out_xw, int out_ld,
+                                         float* out_sumsq, int out_stride, int* error_flag, void* stream) {
+  HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05_norm: sizes must be positive");
+  HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05_norm: K (%d) and the leading dimensions (%d, %d) must be multiples of 8 (16-byte rows for TMA)", K, lda, ldw);
+  HB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tcgen05_norm: operands must be 16-byte aligned");
+  HB_REQUIRE(epi != HB_EPI_SWIGLU || N % 16 == 0, "gemm_tcgen05_norm: SwiGLU columns come in groups of 16, N=%d", N);
+  HB_REQUIRE(error_flag != nullptr, "gemm_tcgen05_norm: an error flag is required");
+  HB_REQUIRE(in_sumsq == nullptr || (in_parts > 0 && in_stride >= M), "gemm_tcgen05_norm: partial sums need a count and a row stride >= M");
+  HB_REQUIRE(out_w == nullptr || (epi == HB_EPI_RESIDUAL && out_xw != nullptr && out_sumsq != nullptr && out_stride >= M),
+             "gemm_tcgen05_norm: the next norm's input is written by the residual epilogue and needs both outputs, row stride >= M");
+  HB_REQUIRE(out_w == nullptr || (((uintptr_t)out_w & 15) == 0), "gemm_tcgen05_norm: the norm weight must be 16-byte aligned");
+  CUtensorMap ma, mw;
+  const int BN = N > 128 ? 256 : 128;
+  int rc = make_map(&ma, A, M, K, lda, TG_BM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, ldw, BN);
+  if (rc) return rc;
+  const TgNorm nm{in_sumsq, in_parts, in_stride, in_eps, out_w, (bf16*)out_xw, out_ld, out_sumsq, out_stride};
+  cudaStream_t s = (cudaStream_t)stream;
+  return BN == 256 ? tg_dispatch<256, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm)
+                   : tg_dispatch<128, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
 }

@@ -36,7 +36,10 @@ _SIGS = {
     "hb_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "hb_gemm_skinny_norm_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                  c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
-    "hb_finish_norm": [c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "hb_finish_norm": [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    "hb_gemm_tcgen05_norm_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                  c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
+    "hb_gemm_tcgen05_norm_parts": [c_int],
     "hb_gemm_tcgen05_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
@@ -216,8 +219,8 @@ SHARED_NORM = os.environ.get("HB_SHARED_NORM", "1") != "0"     # 0: every norm i
 class PendingNorm:
     """An RMSNorm that the product before it has begun and the product after it will finish.
 
-    `xw` [T, D] is x * w in bfloat16; `sumsq` [parts, 16] holds partial sums of x^2 per row, so that
-    y = xw / sqrt(sum(sumsq[:, row]) / D + eps).  A product kernel that takes it multiplies its
+    `xw` [T, D] is x * w in bfloat16; `sumsq` [parts, stride] holds partial sums of x^2 per row, so
+    that y = xw / sqrt(sum(sumsq[:, row]) / D + eps).  A product kernel that takes it multiplies its
     results by that row factor; `finish_norm` makes the plain y for anyone else."""
 
     __slots__ = ("xw", "sumsq", "parts", "eps")
@@ -225,19 +228,23 @@ class PendingNorm:
     def __init__(self, xw, sumsq, parts, eps):
         self.xw, self.sumsq, self.parts, self.eps = xw, sumsq, parts, eps
 
+    stride = property(lambda self: self.sumsq.stride(0))
+
     shape = property(lambda self: self.xw.shape)
     dtype = property(lambda self: self.xw.dtype)
 
 
 def shared_norm_ok(n_rows: int, dtype, dim: int) -> bool:
-    """Whether products of `n_rows` activation rows can carry a norm over `dim` between them."""
-    return SHARED_NORM and dtype == torch.bfloat16 and n_rows <= SHARED_NORM_MAX_ROWS and dim % 8 == 0
+    """Whether products of `n_rows` activation rows can carry a norm over `dim` between them: the
+    kernels for at most 16 rows and the tensor-memory kernel for more than 64 can."""
+    return (SHARED_NORM and dtype == torch.bfloat16 and dim % 8 == 0
+            and (n_rows <= SHARED_NORM_MAX_ROWS or n_rows > SKINNY_MAX_ROWS))
 
 
 def finish_norm(p: PendingNorm, out: torch.Tensor) -> None:
     _check(out, torch.bfloat16, "out")
-    _run("hb_finish_norm", p.xw.data_ptr(), p.xw.stride(0), p.sumsq.data_ptr(), p.parts, float(p.eps), out.data_ptr(),
-         out.stride(0), p.xw.shape[0], p.xw.shape[1], _stream())
+    _run("hb_finish_norm", p.xw.data_ptr(), p.xw.stride(0), p.sumsq.data_ptr(), p.parts, p.stride, float(p.eps),
+         out.data_ptr(), out.stride(0), p.xw.shape[0], p.xw.shape[1], _stream())
 
 
 def gemm_skinny_norm(a, w, c, epilogue=EPI_STORE, next_norm=None, scratch=None):
@@ -297,6 +304,31 @@ def gemm_tcgen05(a, w, c, epilogue=EPI_STORE) -> None:
 _stream_bufs: dict = {}
 STREAM_SCRATCH_FLOATS = 296 * 64 * 128     # most (tile, slice) pairs a call cuts K into, at 64 padded rows
 STREAM_COUNTERS = 8192
+
+
+def gemm_tcgen05_norm(a, w, c, epilogue=EPI_STORE, next_norm=None, scratch=None):
+    """gemm_tcgen05 with a norm shared on either side (see gemm_skinny_norm): `a` may be a
+    PendingNorm; next_norm = (weight, eps) with EPI_RESIDUAL returns the PendingNorm of the updated c."""
+    pend = a if isinstance(a, PendingNorm) else None
+    x = pend.xw if pend is not None else a
+    _check(x, torch.bfloat16, "a"); _check(w, torch.bfloat16, "w"); _check(c, None, "c")
+    M, N, K = x.shape[0], w.shape[0], x.shape[1]
+    out, nw = None, None
+    if next_norm is not None:
+        nw, eps = next_norm
+        _check(nw, torch.float32, "next norm weight")
+        if epilogue != EPI_RESIDUAL or nw.numel() != N:
+            raise BackendError("gemm_tcgen05_norm: the next norm needs the residual epilogue and a weight per output column")
+        parts = int(_fn("hb_gemm_tcgen05_norm_parts")(N))
+        out = PendingNorm(scratch((M, N), torch.bfloat16), scratch((parts, (M + 3) // 4 * 4), torch.float32), parts, eps)
+    _run("hb_gemm_tcgen05_norm_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
+         M, N, K, epilogue,
+         pend.sumsq.data_ptr() if pend is not None else None, pend.parts if pend is not None else 0,
+         pend.stride if pend is not None else 0, float(pend.eps) if pend is not None else 0.0,
+         nw.data_ptr() if out is not None else None, out.xw.data_ptr() if out is not None else None,
+         out.xw.stride(0) if out is not None else 0, out.sumsq.data_ptr() if out is not None else None,
+         out.stride if out is not None else 0, _error_flag(c.device).data_ptr(), _stream())
+    return out
 
 
 def _stream_buffers(device):
@@ -375,10 +407,12 @@ def gemm(a, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE, next_no
     (EPI_RESIDUAL), which is returned where the kernel can make it and None otherwise.
     """
     x = a.xw if isinstance(a, PendingNorm) else a
-    small = x.dtype == torch.bfloat16 and x.shape[0] <= SHARED_NORM_MAX_ROWS and _skinny_ok(x, w)
-    if small and (isinstance(a, PendingNorm) or next_norm is not None) and scratch is not None \
+    if (isinstance(a, PendingNorm) or next_norm is not None) and scratch is not None \
             and shared_norm_ok(x.shape[0], x.dtype, w.shape[0] if next_norm is not None else 8):
-        return gemm_skinny_norm(a, w, c, epilogue, next_norm, scratch)
+        if x.shape[0] <= SHARED_NORM_MAX_ROWS and _skinny_ok(x, w):
+            return gemm_skinny_norm(a, w, c, epilogue, next_norm, scratch)
+        if x.shape[0] > SKINNY_MAX_ROWS and _tcgen05_ok(x, w) and (next_norm is None or next_norm[0].data_ptr() % 16 == 0):
+            return gemm_tcgen05_norm(a, w, c, epilogue, next_norm, scratch)
     a = _plain_input(a, scratch)
     if _skinny_ok(a, w):
         _decode_gemm(a, w)(a, w, c, epilogue)
@@ -394,6 +428,9 @@ def gemm_swiglu(a, wgu: torch.Tensor, out: torch.Tensor, interleave: int, scratc
     if isinstance(a, PendingNorm):
         if interleave == 8 and _skinny_ok(a.xw, wgu) and a.xw.shape[0] <= SHARED_NORM_MAX_ROWS:
             gemm_skinny_norm(a, wgu, out, EPI_SWIGLU)
+            return
+        if interleave == 8 and a.xw.shape[0] > SKINNY_MAX_ROWS and _tcgen05_ok(a.xw, wgu):
+            gemm_tcgen05_norm(a, wgu, out, EPI_SWIGLU)
             return
         a = _plain_input(a, scratch)
     if interleave == 8 and _skinny_ok(a, wgu):

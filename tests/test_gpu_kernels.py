@@ -308,11 +308,12 @@ def test_gemm_skinny_every_epilogue(M, N, K):
         close(out, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 65, 200, 333])
 @pytest.mark.parametrize("H,N2,eps", [(96, 64, 1e-5), (304, 16 * 1024, 1e-6), (1000, 48, 3e-3)])
-def test_gemm_skinny_with_a_norm_shared_between_two_products(M, H, N2, eps):
+def test_products_with_a_norm_shared_between_them(M, H, N2, eps):
     """First product: x += a w1^T, and it begins RMSNorm(x; nw, eps).  Second product: finishes the
-    norm and multiplies with w2 (store, SwiGLU and residual epilogues).  Reference: the norm as a
+    norm and multiplies with w2 (store, SwiGLU and residual epilogues).  Up to 16 rows the decode
+    kernel does it, beyond 64 the tensor-memory kernel.  Reference: the norm as a
     step of its own in double precision, rounded to bfloat16 where the engine's plain path rounds."""
     torch.manual_seed(31)
     K1 = 72
