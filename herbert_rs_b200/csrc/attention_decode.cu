@@ -17,6 +17,7 @@
 #include "api.h"
 #include "common.cuh"
 #include "mma_utils.cuh"
+#include "qk_norm.cuh"
 
 // exp: the hardware's fast exponential (ex2.approx, about 2 ulp in float).  The probabilities are
 // rounded to bfloat16 for the P V product right after, so nothing is lost; sums stay in float.
@@ -310,33 +311,8 @@ __device__ __forceinline__ void mma16816_ab(float* d, const unsigned* a4, unsign
   mma16816(d, a4[0], a4[1], a4[2], a4[3], b0, b1);
 }
 
-__device__ __forceinline__ float2 ld_bf2(const bf16* p) {
-  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
-  return make_float2(__bfloat162float(v.x), __bfloat162float(v.y));
-}
 __device__ __forceinline__ void st_bf2(bf16* p, float x, float y) {
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
-}
-
-// One head of 128 values by one warp: RMSNorm with weight w (if any), then the rotation of the
-// pairs (j, j + 64) by the angles of table row `trow`; lane l holds j = 2l, 2l+1.  The same
-// arithmetic, in the same order, as the stand-alone norm/rotation kernel.
-__device__ __forceinline__ void norm_rotate_head128(const bf16* x, bf16* dst, const float* w, float eps,
-                                                    const float* cos_tab, const float* sin_tab, int trow, int lane) {
-  const int j = 2 * lane;
-  float2 lo = ld_bf2(x + j), hi = ld_bf2(x + j + 64);
-  if (w != nullptr) {
-    float ss = lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
-    const float2 wl = *reinterpret_cast<const float2*>(w + j), wh = *reinterpret_cast<const float2*>(w + j + 64);
-    lo.x = (lo.x * inv) * wl.x; lo.y = (lo.y * inv) * wl.y;
-    hi.x = (hi.x * inv) * wh.x; hi.y = (hi.y * inv) * wh.y;
-  }
-  const float2 c = *reinterpret_cast<const float2*>(cos_tab + (size_t)trow * 64 + j);
-  const float2 sn = *reinterpret_cast<const float2*>(sin_tab + (size_t)trow * 64 + j);
-  st_bf2(dst + j, lo.x * c.x - hi.x * sn.x, lo.y * c.y - hi.y * sn.y);
-  st_bf2(dst + j + 64, lo.x * sn.x + hi.x * c.x, lo.y * sn.y + hi.y * c.y);
 }
 
 template <int NH, bool FUSED>
@@ -375,7 +351,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
     const bf16* row = f.qkv + (size_t)b * f.ld;
     const size_t dst = (((size_t)pages[p / a.page_size] * a.nkv + kvh) * a.page_size + (p % a.page_size)) * HD;
     if (warp == 0) {
-      norm_rotate_head128(row + (size_t)(a.nh + kvh) * HD, f.kcache_w + dst, f.kw, f.eps, f.cos_tab, f.sin_tab, trow, lane);
+      norm_rotate_head128<bf16>(lane < 16, row + (size_t)(a.nh + kvh) * HD, f.kcache_w + dst, f.kw, f.eps,
+                                f.cos_tab + (size_t)trow * 64, f.sin_tab + (size_t)trow * 64, lane & 15);
     } else if (warp == 1) {
       const bf16* v = row + (size_t)(a.nh + a.nkv + kvh) * HD;
       *reinterpret_cast<uint2*>(f.vcache_w + dst + 4 * lane) = *reinterpret_cast<const uint2*>(v + 4 * lane);
@@ -430,8 +407,12 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
     // the query heads of this group, normed and rotated, while the first pages are on their way
     const int trow = p < f.table_rows ? p : f.table_rows - 1;
     const bf16* row = f.qkv + (size_t)b * f.ld;
-    for (int h = warp; h < G; h += AD_WARPS)
-      norm_rotate_head128(row + (size_t)(kvh * G + h) * HD, sm_q + h * HD, f.qw, f.eps, f.cos_tab, f.sin_tab, trow, lane);
+    for (int h0 = 0; h0 < G; h0 += 2 * AD_WARPS) {           // a head per half-warp
+      const int h = h0 + 2 * warp + (lane >> 4);
+      const int hc = h < G ? h : 0;
+      norm_rotate_head128<bf16>(h < G, row + (size_t)(kvh * G + hc) * HD, sm_q + hc * HD, f.qw, f.eps,
+                                f.cos_tab + (size_t)trow * 64, f.sin_tab + (size_t)trow * 64, lane & 15);
+    }
     __syncthreads();
   }
   // B operand of the first product: Q^T, head g of each 8-head tile, d pairs (2t, 2t+1) and (2t+8, 2t+9)
@@ -780,9 +761,9 @@ extern "C" int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out
   HB_REQUIRE(ldo % 2 == 0 && ((uintptr_t)out & 3) == 0, "attention_decode_fused: output rows must be 4-byte aligned");
   HB_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "attention_decode_fused: cache must be 16-byte aligned");
   HB_REQUIRE((qw == nullptr) == (kw == nullptr), "attention_decode_fused: norm weights for both q and k, or for neither");
-  HB_REQUIRE(qw == nullptr || ((((uintptr_t)qw | (uintptr_t)kw) & 7) == 0), "attention_decode_fused: norm weights must be 8-byte aligned");
-  HB_REQUIRE(cos_tab != nullptr && sin_tab != nullptr && table_rows > 0 && ((((uintptr_t)cos_tab | (uintptr_t)sin_tab) & 7) == 0),
-             "attention_decode_fused: needs rotation tables, 8-byte aligned");
+  HB_REQUIRE(qw == nullptr || ((((uintptr_t)qw | (uintptr_t)kw) & 15) == 0), "attention_decode_fused: norm weights must be 16-byte aligned");
+  HB_REQUIRE(cos_tab != nullptr && sin_tab != nullptr && table_rows > 0 && ((((uintptr_t)cos_tab | (uintptr_t)sin_tab) & 15) == 0),
+             "attention_decode_fused: needs rotation tables, 16-byte aligned");
   HB_REQUIRE(window >= 0, "attention_decode_fused: window must be >= 0");
   HB_REQUIRE(counters != nullptr && scratch != nullptr, "attention_decode_fused: needs counters and scratch");
   HB_REQUIRE((long long)(nh / nkv) * nsplit * 8 <= 64 * 1024, "attention_decode_fused: %d heads per group x %d splits exceed the combine's shared memory", nh / nkv, nsplit);

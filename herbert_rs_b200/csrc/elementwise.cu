@@ -10,6 +10,7 @@
 // All arithmetic is float; T is only the storage type.
 #include "api.h"
 #include "common.cuh"
+#include "qk_norm.cuh"
 
 // ---------------------------------------------------------------------------------------------
 template <typename T>
@@ -345,6 +346,37 @@ __global__ void __launch_bounds__(256) qk_norm_rope_cache_fast_kernel(QkvCacheAr
   }
 }
 
+// Head size 128 rotated over its whole width: a head per half-warp, 8- or 16-byte loads and stores
+// (the arithmetic lives in qk_norm.cuh).  One block per token; its 16 half-warps walk the heads.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_norm_rope_cache_128_kernel(QkvCacheArgs a) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x, hw = threadIdx.x >> 4, l = threadIdx.x & 15;
+  const int pos = a.tok_pos[t], b = a.tok_seq[t];
+  const int trow = pos < a.table_rows ? pos : a.table_rows - 1;
+  const float* cos_row = a.cos_tab + (size_t)trow * 64;
+  const float* sin_row = a.sin_tab + (size_t)trow * 64;
+  const int page = a.write_cache ? a.seq_pages[(size_t)b * a.pages_stride + pos / a.page_size] : 0;
+  T* row = (T*)a.qkv + (size_t)t * a.ld;
+  const int n_qk = a.nh + a.nkv, heads_total = a.nh + 2 * a.nkv;
+  for (int h0 = 0; h0 < heads_total; h0 += 16) {          // uniform trip count: the shuffles inside need whole warps
+    const int h = h0 + hw;
+    const bool is_q = h < a.nh, is_k = !is_q && h < n_qk, is_v = h >= n_qk && h < heads_total;
+    const size_t slot = is_q ? 0 : (((size_t)page * a.nkv + (is_k ? h - a.nh : h - n_qk)) * a.page_size + (pos % a.page_size)) * 128;
+    const T* x = row + (size_t)(h < heads_total ? h : 0) * 128;
+    T* dst = is_q ? row + (size_t)h * 128 : (T*)(is_k ? a.kcache : a.vcache) + slot;
+    norm_rotate_head128<T>(is_q || (is_k && a.write_cache), x, dst, is_q ? a.qw : a.kw, a.eps, cos_row, sin_row, l);
+    if (is_v && a.write_cache) {
+      float v[4];
+      Vec4<T>::load(x + 4 * l, v);
+      Vec4<T>::store(dst + 4 * l, v);
+      Vec4<T>::load(x + 64 + 4 * l, v);
+      Vec4<T>::store(dst + 64 + 4 * l, v);
+    }
+  }
+}
+
 extern "C" int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* qw, const float* kw,
                                      float eps, const float* cos_tab, const float* sin_tab, int rot,
                                      int table_rows, const int* tok_seq, const int* tok_pos,
@@ -363,6 +395,18 @@ extern "C" int hb_qk_norm_rope_cache(int dtype, void* qkv, int ld, const float* 
                     ((uintptr_t)qkv % (2 * esz)) == 0 && ((uintptr_t)kcache % (2 * esz)) == 0 &&
                     ((uintptr_t)vcache % (2 * esz)) == 0 && ((uintptr_t)cos_tab & 7) == 0 && ((uintptr_t)sin_tab & 7) == 0 &&
                     (qw == nullptr || (((uintptr_t)qw & 7) == 0 && ((uintptr_t)kw & 7) == 0));
+  const int vec = 4 * esz;     // bytes of four elements
+  const bool fast128 = fast && hd == 128 && ld % 4 == 0 && ((uintptr_t)qkv % vec) == 0 && ((uintptr_t)kcache % vec) == 0 &&
+                       ((uintptr_t)vcache % vec) == 0 && ((uintptr_t)cos_tab & 15) == 0 && ((uintptr_t)sin_tab & 15) == 0 &&
+                       (qw == nullptr || (((uintptr_t)qw & 15) == 0 && ((uintptr_t)kw & 15) == 0));
+  if (fast128) {
+    if (dtype == HB_F32)
+      hb_launch(qk_norm_rope_cache_128_kernel<float>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, a);
+    else
+      hb_launch(qk_norm_rope_cache_128_kernel<bf16>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, a);
+    HB_CHECK_LAUNCH("qk_norm_rope_cache");
+    return 0;
+  }
   if (fast) {
     if (dtype == HB_F32)
       hb_launch(qk_norm_rope_cache_fast_kernel<float>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, a);

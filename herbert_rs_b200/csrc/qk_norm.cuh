@@ -1,0 +1,72 @@
+// Per-head RMSNorm and rotation of one head of 128 values by half a warp, shared by the
+// stand-alone norm/rotation/cache kernel and the fused decode attention so that both give the
+// same bits.  Lane l (0..15 of its half-warp) holds x[4l..4l+3] and x[64+4l..64+4l+3]: the two
+// halves that the rotation pairs (crates/backends/backend_common/src/kernels.rs: rotate-half
+// form, pairs (j, j + rot/2)).
+#pragma once
+
+#include "common.cuh"
+
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float* v) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x), b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __bfloat162float(a.x); v[1] = __bfloat162float(a.y); v[2] = __bfloat162float(b.x); v[3] = __bfloat162float(b.y);
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float* v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<const unsigned*>(&a);
+    t.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+  }
+};
+
+// Every lane of the warp must call this (the sums use full-warp shuffles that stay inside a
+// half-warp); a half-warp with nothing to do passes active = false and touches no memory.
+// x, dst: 8-byte (bfloat16) or 16-byte (float) aligned; w: norm weight [128] or null;
+// cos_row, sin_row: the 64 angles of the token's position, 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ void norm_rotate_head128(bool active, const T* x, T* dst, const float* w, float eps,
+                                                    const float* cos_row, const float* sin_row, int l) {
+  float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    Vec4<T>::load(x + 4 * l, lo);
+    Vec4<T>::load(x + 64 + 4 * l, hi);
+  }
+  if (w != nullptr) {
+    float ss = lo[0] * lo[0] + lo[1] * lo[1] + lo[2] * lo[2] + lo[3] * lo[3] + hi[0] * hi[0] + hi[1] * hi[1] + hi[2] * hi[2] + hi[3] * hi[3];
+    ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    if (active) {
+      const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
+      const float4 wl = *reinterpret_cast<const float4*>(w + 4 * l), wh = *reinterpret_cast<const float4*>(w + 64 + 4 * l);
+      lo[0] = (lo[0] * inv) * wl.x; lo[1] = (lo[1] * inv) * wl.y; lo[2] = (lo[2] * inv) * wl.z; lo[3] = (lo[3] * inv) * wl.w;
+      hi[0] = (hi[0] * inv) * wh.x; hi[1] = (hi[1] * inv) * wh.y; hi[2] = (hi[2] * inv) * wh.z; hi[3] = (hi[3] * inv) * wh.w;
+    }
+  }
+  if (active) {
+    const float4 c4 = *reinterpret_cast<const float4*>(cos_row + 4 * l), s4 = *reinterpret_cast<const float4*>(sin_row + 4 * l);
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+    float olo[4], ohi[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      olo[i] = lo[i] * c[i] - hi[i] * s[i];
+      ohi[i] = lo[i] * s[i] + hi[i] * c[i];
+    }
+    Vec4<T>::store(dst + 4 * l, olo);
+    Vec4<T>::store(dst + 64 + 4 * l, ohi);
+  }
+}

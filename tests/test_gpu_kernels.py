@@ -118,7 +118,7 @@ def _paged(k, page, n_pages_total, perm_seed):
 
 
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (6, 3, 48, 24, True), (8, 1, 128, 128, False),
+@pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (6, 3, 48, 24, True), (8, 1, 128, 128, False), (5, 5, 128, 128, True),
                                                 (3, 3, 80, 80, True), (2, 1, 256, 64, True)])
 def test_qk_norm_rope_cache_write(dtype, nh, nkv, hd, rot, norm):
     torch.manual_seed(4)
