@@ -55,10 +55,60 @@ struct TgNorm {
   int out_stride;
 };
 
+// How the tiles are dealt to the CTAs.  Whole rounds of G tiles run one tile per CTA and round.  The
+// tiles left over (fewer than G) would keep only some SMs busy for a whole tile's time; instead
+// their k blocks are laid end to end ("units") and cut into G equal runs, so every CTA gets the
+// same amount of work: at most the tail of one tile and the head of the next.  A tile shared by
+// several CTAs is finished by whichever of them arrives last at the tile's counter: every piece is
+// written to the workspace as float, and the last one adds the pieces in the order of their k
+// ranges (so the sum does not depend on who is last) and runs the epilogue.  Nobody waits for
+// anybody.
+struct TgSched {
+  int full_rounds;   // rounds of one whole tile per CTA (the last may be ragged when sk_tiles == 0)
+  int sk_tiles;      // tiles cut into runs of k blocks, starting at tile sk_first
+  int sk_first;
+  int per;           // k blocks per CTA in that part (< k blocks of a tile: a CTA touches at most two tiles)
+  float* ws;         // [G][2] pieces of 128 x BN floats, each stored as [BN / 4][128][4]
+  int* counters;     // [sk_tiles], zero between launches
+};
+
+struct TgSegments {
+  int b, G, num_tiles, num_kb, r, u, u1;
+  TgSched sc;
+  __device__ TgSegments(const TgSched& s, int num_tiles_, int num_kb_)
+      : b((int)blockIdx.x), G((int)gridDim.x), num_tiles(num_tiles_), num_kb(num_kb_), r(0), sc(s) {
+    u = b * sc.per;
+    const int total = sc.sk_tiles * num_kb;
+    u1 = u + sc.per < total ? u + sc.per : total;
+  }
+  // The shared tiles come first: their pieces meet early, and whoever finishes one does so while
+  // the tensor cores are already at work on its next (whole) tile.
+  __device__ bool next(int& tile, int& kb0, int& kb1) {
+    if (u < u1) {
+      const int t = u / num_kb;
+      kb0 = u - t * num_kb;
+      kb1 = kb0 + (u1 - u) < num_kb ? kb0 + (u1 - u) : num_kb;
+      tile = sc.sk_first + t;
+      u += kb1 - kb0;
+      return true;
+    }
+    while (r < sc.full_rounds) {
+      tile = b + r * G;
+      ++r;
+      if (tile < num_tiles) {
+        kb0 = 0;
+        kb1 = num_kb;
+        return true;
+      }
+    }
+    return false;
+  }
+};
+
 template <int BN, int EPI, bool NORM>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
-                    int ldc, int M, int N, int K, int* error_flag, TgNorm nm) {
+                    int ldc, int M, int N, int K, int* error_flag, TgNorm nm, TgSched sc) {
   constexpr int STAGES = TgSmem<BN>::kStages;
   constexpr int STAGE_BYTES = TgSmem<BN>::kStageBytes;
   extern __shared__ unsigned char smem_raw[];
@@ -67,6 +117,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the tensor-memory slot
   const unsigned bars = base + STAGES * STAGE_BYTES;
   volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8);
+  volatile int* sk_last = reinterpret_cast<volatile int*>(gen + STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 8);
   auto full_bar = [&](int s) { return bars + s * 8; };
   auto empty_bar = [&](int s) { return bars + (STAGES + s) * 8; };
   auto acc_full = [&](int b) { return bars + (2 * STAGES + b) * 8; };
@@ -104,9 +155,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       int it = 0;        // k blocks issued so far, over all tiles of this CTA
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      TgSegments segs(sc, num_tiles, num_kb);
+      int tile, kb0, kb1;
+      while (ok && segs.next(tile, kb0, kb1)) {
         const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1)) {
             atomicExch(error_flag, 1);
@@ -126,7 +179,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
       int it = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      TgSegments segs(sc, num_tiles, num_kb);
+      int tile, kb0, kb1;
+      for (; ok && segs.next(tile, kb0, kb1); ++local) {
         const int buf = local & 1;
         // the epilogue must have drained this accumulator (its previous use was tile local - 2)
         if (local >= 2 && !mbar_wait(acc_empty(buf), ((local >> 1) - 1) & 1)) {
@@ -136,7 +191,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         tc_fence_after();
         const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(full_bar(s), (it / STAGES) & 1)) {
             atomicExch(error_flag, 2);
@@ -149,7 +204,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int k = 0; k < TG_BK / 16; ++k) {
             tc_mma_bf16(tmem_acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(w_addr + k * 32), idesc,
-                        (kb > 0 || k > 0) ? 1u : 0u);
+                        (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(s));     // arrives when these MMAs have finished reading the stage
         }
@@ -161,7 +216,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quad = warp & 3;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    TgSegments segs(sc, num_tiles, num_kb);
+    int tile, kb0, kb1;
+    for (; ok && segs.next(tile, kb0, kb1); ++local) {
       const int buf = local & 1;
       const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
       const int m = m0 + quad * 32 + lane;
@@ -178,15 +235,78 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       tc_fence_after();
       const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
+      const bool whole = kb0 == 0 && kb1 == num_kb;
+      // pieces of a shared tile: CTA first_cta + j holds the j-th k range; its slot in the workspace
+      // is 2 * cta + (index of the tile among the at most two that CTA touches)
+      const int tsk = tile - sc.sk_first;
+      int first_cta = 0, n_pieces = 1;
+      bool finish = true;
+      if (!whole) {
+        first_cta = (tsk * num_kb) / sc.per;
+        n_pieces = ((tsk + 1) * num_kb - 1) / sc.per - first_cta + 1;
+        // a piece is stored as [group of 4 columns][row][4]: the 32 lanes (rows) of a warp write 512 contiguous bytes
+        float* mine = sc.ws + (size_t)(2 * blockIdx.x + (tsk - ((int)blockIdx.x * sc.per) / num_kb)) * TG_BM * BN + (quad * 32 + lane) * 4;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          unsigned r[32];
+          tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(mine + (size_t)(c * 8 + (j >> 2)) * TG_BM * 4) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(buf));
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
+        if (threadIdx.x == 64) {
+          const int old = atomicAdd(sc.counters + tsk, 1);
+          *sk_last = old == n_pieces - 1;
+          if (*sk_last) sc.counters[tsk] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        finish = *sk_last != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // everyone has read the flag before it is written again
+        if (finish) __threadfence();
+      }
+      if (!finish) continue;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         unsigned r[32];
-        tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
-        if (c == BN / 32 - 1) {
-          // everything of this accumulator is in registers: the tensor cores may have it back
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty(buf));
+        if (whole) {
+          tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+          if (c == BN / 32 - 1) {
+            // everything of this accumulator is in registers: the tensor cores may have it back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
+          }
+        } else {
+          // the pieces in the order of their k ranges, four pieces' loads in flight at a time
+          float acc[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+          for (int p0 = 0; p0 < n_pieces; p0 += 4) {
+            float4 v[4][8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int cta = first_cta + (p0 + q < n_pieces ? p0 + q : p0);
+              const float* src = sc.ws + (size_t)(2 * cta + (tsk - (cta * sc.per) / num_kb)) * TG_BM * BN + (quad * 32 + lane) * 4 + (size_t)c * 8 * TG_BM * 4;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[q][j] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)j * TG_BM * 4));
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (p0 + q < n_pieces) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  acc[4 * j] += v[q][j].x; acc[4 * j + 1] += v[q][j].y; acc[4 * j + 2] += v[q][j].z; acc[4 * j + 3] += v[q][j].w;
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(acc[j]);
         }
         const int n = n0 + c * 32;
         if (m < M) {
@@ -295,6 +415,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
+// The workspace the launcher may use for shared tiles: floats and counters for a grid of `sms` CTAs.
+#define TG_WS_FLOATS_PER_CTA (2 * TG_BM * 256)
+static float* g_tg_ws = nullptr;        // set by hb_gemm_tcgen05_set_workspace
+static int* g_tg_counters = nullptr;
+static int g_tg_ws_ctas = 0;
+
 template <int BN, int EPI, bool NORM>
 static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int* err,
                      cudaStream_t s, const TgNorm& nm) {
@@ -312,8 +438,27 @@ static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   }
   const int tiles = ceil_div(M, TG_BM) * ceil_div(N, BN);
-  dim3 grid(tiles < sms ? tiles : sms);
-  hb_launch(gemm_tcgen05_kernel<BN, EPI, NORM>, dim3(grid), dim3(TG_THREADS), smem, s, ma, mw, C, ldc, M, N, K, err, nm);
+  const int num_kb = ceil_div(K, TG_BK);
+  int G = tiles < sms ? tiles : sms;
+  TgSched sc{ceil_div(tiles, G), 0, 0, 1, nullptr, nullptr};
+  // Leftover tiles are cut into equal runs of k blocks when that pays: a workspace is there, the
+  // leftover would leave at least half of the GPU idle, and a run is at least a few k blocks.
+  // (Measured at the 8B sizes: with 48 leftover tiles the down projection takes 62 instead of 88 us;
+  // with 108 or 128 leftover tiles the products with K = 4096..12288 get slower, because CTAs that
+  // start at different k no longer share the weight slabs in L2 in lockstep.)
+  const int rem = tiles % sms;
+  if (g_tg_ws != nullptr && g_tg_ws_ctas >= sms && rem > 0 && rem * 2 <= sms && num_kb >= 8 &&
+      (long long)rem * num_kb >= 4LL * sms) {
+    G = sms;
+    sc.full_rounds = tiles / sms;
+    sc.sk_tiles = rem;
+    sc.sk_first = sc.full_rounds * sms;
+    sc.per = ceil_div(rem * num_kb, sms);
+    sc.ws = g_tg_ws;
+    sc.counters = g_tg_counters;
+  }
+  dim3 grid(G);
+  hb_launch(gemm_tcgen05_kernel<BN, EPI, NORM>, dim3(grid), dim3(TG_THREADS), smem, s, ma, mw, C, ldc, M, N, K, err, nm, sc);
   HB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }
@@ -328,6 +473,18 @@ static int tg_dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, in
     case HB_EPI_SWIGLU: return tg_launch<BN, HB_EPI_SWIGLU, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
   }
   HB_FAIL(2, "gemm_tcgen05: unknown epilogue %d", epi);
+}
+
+// Gives the products a workspace for tiles shared between CTAs: `floats` must hold
+// hb_gemm_tcgen05_workspace_floats(ctas) floats and `counters` ctas ints, zero, for ctas >= the
+// number of SMs.  Without it (null) every tile is computed by one CTA.  Calls that use the same
+// workspace must be on one stream.
+extern "C" long long hb_gemm_tcgen05_workspace_floats(int ctas) { return (long long)ctas * TG_WS_FLOATS_PER_CTA; }
+extern "C" int hb_gemm_tcgen05_set_workspace(float* floats, int* counters, int ctas) {
+  g_tg_ws = floats;
+  g_tg_counters = counters;
+  g_tg_ws_ctas = floats != nullptr && counters != nullptr ? ctas : 0;
+  return 0;
 }
 
 // error_flag: one int in device memory, zero before the call; non-zero afterwards means a bounded

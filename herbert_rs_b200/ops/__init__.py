@@ -294,9 +294,36 @@ def check_kernel_errors() -> None:
             raise BackendError(f"a kernel on {key} gave up waiting on a barrier (code {code}); its output is not valid")
 
 
+PREFILL_SPLIT_TILES = os.environ.get("HB_PREFILL_SPLIT_TILES", "1") != "0"   # 0: every output tile by one CTA
+_tcgen05_ws: dict = {}
+
+
+def _tcgen05_workspace(device) -> None:
+    """Once per device: hand the prefill product the workspace in which CTAs that share an output
+    tile leave their pieces (about 39 MB on 148 SMs)."""
+    key = str(device)
+    if key in _tcgen05_ws:
+        return
+    if not PREFILL_SPLIT_TILES:
+        _tcgen05_ws[key] = None
+        return
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    lib = _libmod.load()
+    lib.hb_gemm_tcgen05_workspace_floats.restype = ctypes.c_longlong
+    lib.hb_gemm_tcgen05_workspace_floats.argtypes = [c_int]
+    n = int(lib.hb_gemm_tcgen05_workspace_floats(sms))
+    floats = torch.empty(n, dtype=torch.float32, device=device)
+    counters = torch.zeros(sms, dtype=torch.int32, device=device)
+    lib.hb_gemm_tcgen05_set_workspace.argtypes = [c_void_p, c_void_p, c_int]
+    lib.hb_gemm_tcgen05_set_workspace.restype = c_int
+    lib.hb_gemm_tcgen05_set_workspace(floats.data_ptr(), counters.data_ptr(), sms)
+    _tcgen05_ws[key] = (floats, counters)
+
+
 def gemm_tcgen05(a, w, c, epilogue=EPI_STORE) -> None:
     """c (op)= a @ w.T on tcgen05 tensor cores with TMA-fed tiles (bfloat16, K a multiple of 8)."""
     _check(a, torch.bfloat16, "a"); _check(w, torch.bfloat16, "w"); _check(c, None, "c")
+    _tcgen05_workspace(c.device)
     _run("hb_gemm_tcgen05_bf16", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
          a.shape[0], w.shape[0], a.shape[1], epilogue, _error_flag(a.device).data_ptr(), _stream())
 
@@ -321,6 +348,7 @@ def gemm_tcgen05_norm(a, w, c, epilogue=EPI_STORE, next_norm=None, scratch=None)
             raise BackendError("gemm_tcgen05_norm: the next norm needs the residual epilogue and a weight per output column")
         parts = int(_fn("hb_gemm_tcgen05_norm_parts")(N))
         out = PendingNorm(scratch((M, N), torch.bfloat16), scratch((parts, (M + 3) // 4 * 4), torch.float32), parts, eps)
+    _tcgen05_workspace(c.device)
     _run("hb_gemm_tcgen05_norm_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
          M, N, K, epilogue,
          pend.sumsq.data_ptr() if pend is not None else None, pend.parts if pend is not None else 0,

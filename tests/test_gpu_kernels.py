@@ -506,6 +506,43 @@ def test_gemm_tcgen05_every_epilogue(M, N, K):
     ops.check_kernel_errors()
 
 
+@pytest.mark.parametrize("M,N,K", [(200, 4112, 2056), (700, 6512, 4800), (129, 4096, 4096)])
+def test_gemm_tcgen05_tiles_shared_between_ctas(M, N, K):
+    """Sizes whose leftover tiles are cut into runs of k blocks (all 34 tiles; 8 of 156; 32 tiles):
+    every epilogue, the norm begun by the residual epilogue, twice the same bits, and the counters
+    back at zero (the second and third call)."""
+    torch.manual_seed(19)
+    a, w = dev(torch.randn(M, K).to(torch.bfloat16)), dev((torch.randn(N, K) * 0.1).to(torch.bfloat16))
+    ref = a.double() @ w.double().T
+    c32 = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_tcgen05(a, w, c32, ops.EPI_STORE_F32)
+    close(c32, ref, torch.float32, scale=4.0)          # float sums of up to 4,800 bfloat16 products
+    again = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_tcgen05(a, w, again, ops.EPI_STORE_F32)
+    assert torch.equal(c32, again)
+    res = torch.randn(M, N, device="cuda")
+    nw = dev(1.0 + 0.1 * torch.randn(N))
+    r = res.clone()
+    bufs = []
+    def scratch(shape, dtype):
+        bufs.append(torch.full(shape, float("nan"), device="cuda", dtype=dtype))
+        return bufs[-1]
+    pend = ops.gemm(a, w, r, ops.EPI_RESIDUAL, next_norm=(nw, 1e-6), scratch=scratch)
+    x_ref = res.double() + ref
+    close(r, x_ref, torch.float32, scale=4.0)
+    assert isinstance(pend, ops.PendingNorm)
+    y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ops.finish_norm(pend, y)
+    close(y, x_ref / torch.sqrt((x_ref ** 2).mean(dim=1, keepdim=True) + 1e-6) * nw.double(), torch.bfloat16)
+    if N % 16 == 0:
+        out = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_tcgen05(a, w, out, ops.EPI_SWIGLU)
+        blocks = ref.view(M, N // 16, 2, 8)
+        gate, up = blocks[:, :, 0].reshape(M, -1), blocks[:, :, 1].reshape(M, -1)
+        close(out, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
+    ops.check_kernel_errors()
+
+
 def test_gemm_tcgen05_refuses_rows_tma_cannot_address():
     a, w = dev(torch.zeros(16, 60, dtype=torch.bfloat16)), dev(torch.zeros(32, 60, dtype=torch.bfloat16))
     with pytest.raises(BackendError, match="multiples of 8"):
