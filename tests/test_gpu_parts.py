@@ -16,7 +16,7 @@ from herbert_rs_b200.cache import CacheNeed, SequenceCache, StateNeed
 from herbert_rs_b200.config import (AttentionSpec, BlockSpec, ModelSpec, NormSpec, PositionSpec, ScheduleStep,
                                     SwiGLUSpec)
 from herbert_rs_b200.engine.batch import StepBatch
-from herbert_rs_b200.parts import Mixer, ParamSpec
+from herbert_rs_b200.parts import FeedForward, Mixer, ParamSpec, Part
 from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
@@ -230,6 +230,171 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     with pytest.raises(hb.CacheError, match="cannot be rolled back"):
         eng.truncate(s, 1)
     eng.free_slot(s)
+
+
+# ---- a toy feed-forward with routing and a toy position encoding, defined here ---------------------
+@dataclass(frozen=True)
+class RoutedSpec:
+    hidden_size: int
+    num_experts: int
+    expert_size: int
+    kind: str = "toy_routed"
+
+
+class RoutedFeedForward(FeedForward):
+    """Each token goes to the one expert its router row scores highest (router logits in float);
+    an expert is relu(h W1^T) W2^T.  Written with torch operations on device tensors only (every
+    expert is evaluated and the choice is a mask), so its steps can be replayed from a CUDA graph;
+    it neither takes nor begins a shared norm."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+
+    def param_specs(self):
+        s = self.spec
+        p = {"router.weight": ParamSpec((s.num_experts, s.hidden_size))}
+        for e in range(s.num_experts):
+            p[f"experts.{e}.w1.weight"] = ParamSpec((s.expert_size, s.hidden_size))
+            p[f"experts.{e}.w2.weight"] = ParamSpec((s.hidden_size, s.expert_size))
+        return p
+
+    def load(self, tensors):
+        E = self.spec.num_experts
+        self.router = tensors["router.weight"].float()
+        self.w1 = torch.stack([tensors[f"experts.{e}.w1.weight"].float() for e in range(E)])
+        self.w2 = torch.stack([tensors[f"experts.{e}.w2.weight"].float() for e in range(E)])
+        self.expert_ids = torch.arange(E, device=self.router.device)
+
+    def forward(self, h, residual, batch):
+        x = h.float()
+        choice = torch.argmax(x @ self.router.T, dim=1)                            # [T]
+        y = torch.stack([torch.relu(x @ self.w1[e].T) @ self.w2[e].T for e in range(self.spec.num_experts)])   # [E, T, H]
+        mask = (choice[None, :] == self.expert_ids[:, None]).unsqueeze(-1).to(y.dtype)                             # [E, T, 1]
+        residual += (y * mask).sum(dim=0)
+
+
+@dataclass(frozen=True)
+class SlowedRopeSpec:
+    """Rotary tables whose positions are divided by `factor` (angles = pos / factor * inv_freq)."""
+    head_dim: int
+    rotary_dim: int
+    theta: float
+    max_position: int
+    factor: float
+    kind: str = "toy_slowed_rope"
+
+
+class SlowedRope(Part):
+    """Another position encoding for the attention mixer: it only has to offer cos/sin tables
+    [max_position, rotary_dim / 2] in float and `rotary_dim`; the mixer and its kernels take it as is."""
+
+    def __init__(self, spec, rt):
+        self.rotary_dim, self.max_position = spec.rotary_dim, spec.max_position
+        cos, sin = _slowed_tables(spec.rotary_dim, spec.theta, spec.max_position, spec.factor, torch.float32)
+        self.cos, self.sin = cos.to(rt.device), sin.to(rt.device)
+
+
+def _slowed_tables(rot, theta, n_pos, factor, dtype):
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    inv = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float64), 2.0 * i / float(rot))
+    ang = (torch.arange(n_pos, dtype=torch.float64) / factor)[:, None] * inv[None, :]
+    return torch.cos(ang).to(dtype).contiguous(), torch.sin(ang).to(dtype).contiguous()
+
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    """Every layer: attention with the slowed rotation; the feed-forward is routed in odd layers and
+    the dense SwiGLU in even ones.  Head size 128 in order to meet the fused decode kernel too."""
+    vocab_size: int
+    hidden_size: int
+    num_hidden_layers: int
+    num_experts: int
+    expert_size: int
+    intermediate_size: int
+    rope_factor: float
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(*(d[k] for k in ("vocab_size", "hidden_size", "num_hidden_layers", "num_experts", "expert_size",
+                                    "intermediate_size", "rope_factor")))
+
+    def to_dict(self):
+        return dict(architectures=["ToyRoutedForCausalLM"], **self.__dict__)
+
+    def model_spec(self):
+        H = self.hidden_size
+        norm = NormSpec(H, 1e-6)
+        att = AttentionSpec(H, 2, 1, 128, scale=128 ** -0.5, qk_norm=NormSpec(128, 1e-6),
+                            position=SlowedRopeSpec(128, 128, 1e4, 512, self.rope_factor))
+        blocks = tuple(BlockSpec(mixer=att, ffn=RoutedSpec(H, self.num_experts, self.expert_size) if i % 2 else SwiGLUSpec(H, self.intermediate_size),
+                                 norm1=norm, norm2=norm,
+                                 names=(("norm1", "input_layernorm"), ("mixer", "self_attn"),
+                                        ("norm2", "post_attention_layernorm"), ("ffn", "moe" if i % 2 else "mlp")))
+                       for i in range(self.num_hidden_layers))
+        return ModelSpec("ToyRoutedForCausalLM", self.vocab_size, H, blocks,
+                         tuple(ScheduleStep(i) for i in range(self.num_hidden_layers)), norm, True, 512)
+
+
+def _routed_plain(w, cfg, ids, store=None):
+    st = store or (lambda t: t)
+    x = P.embedding(w["model.embed_tokens.weight"], ids, torch.float64)
+    T = len(ids)
+    cos, sin = _slowed_tables(128, 1e4, T, cfg["rope_factor"], torch.float64)
+    acfg = dict(nh=2, nkv=1, hd=128, eps=1e-6, rot=128, scale=128 ** -0.5)
+    margins = []
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        x = x + P.attention_block(P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6), w, p + "self_attn.", acfg, cos, sin, None)
+        n2 = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-6)
+        if i % 2:
+            logits = n2 @ w[p + "moe.router.weight"].double().T
+            top2 = torch.topk(logits, 2, dim=1).values
+            margins.append((top2[:, 0] - top2[:, 1]).min().item())
+            choice = torch.argmax(logits, dim=1)
+            out = torch.zeros_like(x)
+            for t in range(T):
+                e = int(choice[t])
+                out[t] = torch.relu(n2[t] @ w[p + f"moe.experts.{e}.w1.weight"].double().T) @ w[p + f"moe.experts.{e}.w2.weight"].double().T
+            x = x + out
+        else:
+            x = x + P.swiglu_mlp(n2, w, p + "mlp.")
+    logits = P.linear(P.rms_norm(x, w["model.norm.weight"], 1e-6), w["model.embed_tokens.weight"]).numpy()
+    return logits, min(margins)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path, dtype):
+    """Both are defined and registered here; the framework's files do not know them.  The model mixes
+    parts that share norms (attention, SwiGLU) with one that does not (the routed feed-forward), runs
+    its decode steps from CUDA graphs, and meets the fused decode attention (head size 128) with the
+    toy tables."""
+    hb.register_part("ffn", "toy_routed", RoutedFeedForward)
+    hb.register_part("position", "toy_slowed_rope", SlowedRope)
+    hb.register_architecture("ToyRoutedForCausalLM", RoutedConfig)
+    cfg = dict(architectures=["ToyRoutedForCausalLM"], vocab_size=150, hidden_size=64, num_hidden_layers=4,
+               num_experts=3, expert_size=40, intermediate_size=96, rope_factor=3.0)
+    d = hb.write_random_model(cfg, str(tmp_path / "routed"), seed=6)
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    assert "model.layers.1.moe.experts.2.w2.weight" in w and "model.layers.0.mlp.gate_proj.weight" in w
+    eng = engine_for(d, dtype, max_tokens=64 * 8, max_slots=3)
+    assert eng.model.graph_safe
+    rng = np.random.default_rng(3)
+    reqs, refs = [], []
+    while len(reqs) < 3:                         # keep prompts whose routing is not a near tie: a rounding must not flip an expert
+        r = random_ids(rng, 150, int(rng.integers(20, 90)))
+        ref, margin = _routed_plain(w, cfg, r)
+        if margin > (1e-3 if dtype == "float32" else 2e-2):
+            reqs.append(r); refs.append(ref)
+    for r, ref in zip(reqs[:2], refs):
+        assert_close(replay_whole(eng, r), ref, dtype, "routed whole")
+        assert_close(replay_tail_one_by_one(eng, r, 12), ref, dtype, "routed one by one")
+    got = replay_batches(eng, reqs, [len(r) - 6 for r in reqs], [[0, 1, 2]])
+    for g, ref in zip(got, refs):
+        assert_close(g, ref, dtype, "routed batched")
+    assert eng.graph_replays > 0
+    # a different factor gives different logits: the tables are really the toy's
+    cfg2 = dict(cfg, rope_factor=1.0)
+    assert np.abs(_routed_plain(w, cfg2, reqs[0])[0] - refs[0]).max() > 1e-3
 
 
 # ---- the order of layers is data -----------------------------------------------------------------
