@@ -53,7 +53,8 @@ _SIGS = {
     "hb_attention_prefill_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+                                     c_void_p],
     "hb_attention_decode_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                     c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
@@ -548,7 +549,20 @@ def attention_prefill_tc(q, ldq, out, k_cache, v_cache, seq_start, seq_pos0, seq
     _run("hb_attention_prefill_tc_bf16", q.data_ptr(), int(ldq), q.shape[0], out.data_ptr(), out.stride(0),
          k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], seq_start.data_ptr(), seq_pos0.data_ptr(),
          seq_pages.data_ptr(), seq_pages.stride(0), int(n_seqs), int(max_q_len), num_heads, num_kv_heads, head_dim,
-         page_size, float(scale), int(window or 0), _error_flag(out.device).data_ptr(), _stream())
+         page_size, float(scale), int(window or 0), _error_flag(out.device).data_ptr(),
+         _work_counter(out.device).data_ptr(), _stream())
+
+
+_work_counters: dict = {}
+
+
+def _work_counter(device) -> torch.Tensor:
+    """One int per device from which the CTAs of a persistent kernel take their next item of work
+    (the launcher zeroes it on the stream before the kernel)."""
+    key = str(device)
+    if key not in _work_counters:
+        _work_counters[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _work_counters[key]
 
 
 PREFILL_ATTENTION = os.environ.get("HB_PREFILL_ATTENTION", "tcgen05")   # or "mma": the mma.sync kernel for every size
