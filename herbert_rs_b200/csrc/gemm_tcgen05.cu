@@ -363,28 +363,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool begin_norm = NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr;
             bf16* xw = begin_norm ? nm.out_xw + (size_t)m * nm.out_ld + n : nullptr;
             if (n + 32 <= N && ((((size_t)m * ldc + n) & 3) == 0) && (!begin_norm || ((((size_t)m * nm.out_ld + n) & 7) == 0))) {
+              // every load first, then the arithmetic, then every store: the compiler cannot tell that the
+              // three arrays do not overlap and would otherwise wait for each store before the next load
+              float4 old4[8], w4[8];
+              if (EPI == HB_EPI_RESIDUAL) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float v[8];
+                for (int q = 0; q < 8; ++q) old4[q] = *reinterpret_cast<const float4*>(out + 4 * q);
+              }
+              if (begin_norm) {
 #pragma unroll
-                for (int h = 0; h < 8; h += 4) {
-                  float4* o4 = reinterpret_cast<float4*>(out + j + h);
-                  float4 t4 = make_float4(__uint_as_float(r[j + h]), __uint_as_float(r[j + h + 1]), __uint_as_float(r[j + h + 2]), __uint_as_float(r[j + h + 3]));
-                  if (EPI == HB_EPI_RESIDUAL) {
-                    const float4 old = *o4;
-                    t4.x += old.x; t4.y += old.y; t4.z += old.z; t4.w += old.w;
-                  }
-                  *o4 = t4;
-                  v[h] = t4.x; v[h + 1] = t4.y; v[h + 2] = t4.z; v[h + 3] = t4.w;
+                for (int q = 0; q < 8; ++q) w4[q] = *reinterpret_cast<const float4*>(nm.out_w + n + 4 * q);
+              }
+              float v[32];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                v[4 * q] = __uint_as_float(r[4 * q]); v[4 * q + 1] = __uint_as_float(r[4 * q + 1]);
+                v[4 * q + 2] = __uint_as_float(r[4 * q + 2]); v[4 * q + 3] = __uint_as_float(r[4 * q + 3]);
+                if (EPI == HB_EPI_RESIDUAL) {
+                  v[4 * q] += old4[q].x; v[4 * q + 1] += old4[q].y; v[4 * q + 2] += old4[q].z; v[4 * q + 3] += old4[q].w;
                 }
-                if (begin_norm) {
-                  const float4 w0 = *reinterpret_cast<const float4*>(nm.out_w + n + j), w1 = *reinterpret_cast<const float4*>(nm.out_w + n + j + 4);
+              }
 #pragma unroll
-                  for (int h = 0; h < 8; ++h) sq += v[h] * v[h];
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(out + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              if (begin_norm) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sq += v[j] * v[j];
+#pragma unroll
+                for (int q = 0; q < 8; q += 2) {
                   uint4 pk;
-                  pk.x = pack2(v[0] * w0.x, v[1] * w0.y); pk.y = pack2(v[2] * w0.z, v[3] * w0.w);
-                  pk.z = pack2(v[4] * w1.x, v[5] * w1.y); pk.w = pack2(v[6] * w1.z, v[7] * w1.w);
-                  *reinterpret_cast<uint4*>(xw + j) = pk;
+                  pk.x = pack2(v[4 * q] * w4[q].x, v[4 * q + 1] * w4[q].y);
+                  pk.y = pack2(v[4 * q + 2] * w4[q].z, v[4 * q + 3] * w4[q].w);
+                  pk.z = pack2(v[4 * q + 4] * w4[q + 1].x, v[4 * q + 5] * w4[q + 1].y);
+                  pk.w = pack2(v[4 * q + 6] * w4[q + 1].z, v[4 * q + 7] * w4[q + 1].w);
+                  *reinterpret_cast<uint4*>(xw + 4 * q) = pk;
                 }
               }
             } else {
