@@ -253,14 +253,15 @@ def test_captured_decode_steps_equal_eager_ones(model_dirs, plain, dtype):
         assert_close(y, plain["C"].logits(ids).numpy(), dtype, "graphed decode")
 
 
-def test_decode_steps_that_update_the_step_buffer_in_place(model_dirs, plain):
+@pytest.mark.parametrize("which,dtype", [("C", "float32"), ("D", "bfloat16")])
+def test_decode_steps_that_update_the_step_buffer_in_place(model_dirs, plain, which, dtype):
     """Generation's decode steps reuse the previous step's buffer; the tokens must be those of an
     engine that builds every step anew, also across page edges, early finishers and a new batch."""
     rng = np.random.default_rng(18)
     prompts = [random_ids(rng, 300, n) for n in (60, 3, 127, 64, 20)]
     opt = hb.GenerationOptions(max_tokens=80, ignore_eos=True, max_batch=3)
-    fast = engine_for(model_dirs["C"], "float32")
-    slow = engine_for(model_dirs["C"], "float32", use_graphs=False)
+    fast = engine_for(model_dirs[which], dtype)          # D in bfloat16: the fused decode attention, shared norms, graphs
+    slow = engine_for(model_dirs[which], dtype, use_graphs=False)
     a = hb.generate(fast, prompts, opt, hb.SamplingParams(temperature=0.7, top_k=30, top_p=0.95, seed=5)).tokens
     b = hb.generate(slow, prompts, opt, hb.SamplingParams(temperature=0.7, top_k=30, top_p=0.95, seed=5)).tokens
     assert a == b
