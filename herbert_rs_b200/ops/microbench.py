@@ -1,0 +1,139 @@
+"""Times single kernels with CUDA events, outside any profiler.
+
+    python -m herbert_rs_b200.ops.microbench decode-gemm --rows 8 --layers 12
+    python -m herbert_rs_b200.ops.microbench prefill-gemm --rows 2048
+    python -m herbert_rs_b200.ops.microbench decode-attention --seqs 8 --context 2050 --splits 4
+    python -m herbert_rs_b200.ops.microbench prefill-attention --seqs 1 --len 2048
+
+Shapes default to the Qwen3-8B layer (hidden 4096, 32 query / 8 key-value heads of 128,
+intermediate 12288).  Every launch of a timed loop reads other weights or another layer's cache
+than the one before (several copies, more than L2 holds together), decode kernels are timed
+inside a captured CUDA graph as the engine runs them, and the figure printed is the mean over the
+launches between two events after three untimed repetitions.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from .. import ops
+
+
+def _timed(fn, reps: int, per: int, graph: bool) -> float:
+    """Mean microseconds per launch of fn() (which makes `per` launches)."""
+    fn()
+    torch.cuda.synchronize()
+    run = fn
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        run = g.replay
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    return e0.elapsed_time(e1) * 1e3 / reps / per
+
+
+def _shapes(a):
+    q, kv = a.heads * a.head_dim, a.kv_heads * a.head_dim
+    return [("q/k/v", q + 2 * kv, a.hidden, ops.EPI_STORE), ("o", a.hidden, q, ops.EPI_RESIDUAL),
+            ("gate/up", 2 * a.intermediate, a.hidden, ops.EPI_SWIGLU), ("down", a.hidden, a.intermediate, ops.EPI_RESIDUAL)]
+
+
+def _gemm(a, kernels, graph):
+    M = a.rows
+    for name, N, K, epi in _shapes(a):
+        ws = [torch.randn(N, K, device="cuda").bfloat16() for _ in range(a.layers)]
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        c = (torch.zeros(M, N, device="cuda") if epi == ops.EPI_RESIDUAL
+             else torch.empty(M, N // 2 if epi == ops.EPI_SWIGLU else N, device="cuda", dtype=torch.bfloat16))
+        line = f"{name:8s} N={N:6d} K={K:6d} rows={M:5d}"
+        for kname in kernels:
+            fn = getattr(ops, kname)
+            us = _timed(lambda: [fn(x, w, c, epi) for w in ws], a.reps, a.layers, graph)
+            line += f"   {kname} {us:7.1f} us {N * K * 2 / us / 1e3:6.0f} GB/s {2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s"
+        print(line, flush=True)
+        del ws
+
+
+def decode_gemm(a):
+    _gemm(a, [k for k in ("gemm_skinny", "gemm_stream", "gemm_tcgen05") if k != "gemm_skinny" or a.rows <= 64], True)
+
+
+def prefill_gemm(a):
+    _gemm(a, ["gemm_tcgen05"], False)
+
+
+def decode_attention(a):
+    from ..parts.rope import rope_tables
+    B, nh, nkv, hd, page = a.seqs, a.heads, a.kv_heads, a.head_dim, 64
+    if hd != 128:
+        raise SystemExit("decode-attention times the fused kernel: head size 128")
+    P = -(-a.context // page)
+    kc = [torch.randn(B * P, nkv, page, hd, device="cuda").bfloat16() for _ in range(a.layers)]
+    vc = [torch.randn(B * P, nkv, page, hd, device="cuda").bfloat16() for _ in range(a.layers)]
+    table = torch.arange(B * P, dtype=torch.int32, device="cuda").view(B, P).contiguous()
+    seq_len = torch.full((B,), a.context, dtype=torch.int32, device="cuda")
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda").bfloat16()
+    out = torch.empty(B, nh * hd, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(hd, device="cuda")
+    cos, sin = (t.cuda() for t in rope_tables(hd, 1e6, max(4096, a.context + 1)))
+    splits = a.splits or ops.decode_splits(B, nkv, P)
+    scratch = torch.empty(ops.attention_decode_scratch_floats(B, nh, hd, splits), device="cuda")
+    us = _timed(lambda: [ops.attention_decode_fused(qkv, out, kc[i], vc[i], w, w, 1e-6, cos, sin, True, seq_len, table, scratch,
+                                                    nh, nkv, page, splits, hd ** -0.5, 0) for i in range(a.layers)],
+                a.reps, a.layers, True)
+    byts = B * a.context * nkv * hd * 2 * 2
+    print(f"fused decode attention: {B} sequences of {a.context}, {splits} splits ({splits * B * nkv} CTAs): {us:7.2f} us  {byts / us / 1e3:6.0f} GB/s")
+
+
+def prefill_attention(a):
+    B, T, nh, nkv, hd = a.seqs, a.len, a.heads, a.kv_heads, a.head_dim
+    P = -(-T // 64)
+    q = torch.randn(B * T, (nh + 2 * nkv) * hd, device="cuda").bfloat16()
+    k = torch.randn(B * P, nkv, 64, hd, device="cuda").bfloat16()
+    v = torch.randn(B * P, nkv, 64, hd, device="cuda").bfloat16()
+    table = torch.arange(B * P, dtype=torch.int32, device="cuda").view(B, P).contiguous()
+    starts = torch.arange(0, B * T + 1, T, dtype=torch.int32, device="cuda")
+    pos0 = torch.zeros(B, dtype=torch.int32, device="cuda")
+    out = torch.empty(B * T, nh * hd, device="cuda", dtype=torch.bfloat16)
+    us = _timed(lambda: ops.attention_prefill_tc(q, q.stride(0), out, k, v, starts, pos0, table, B, T, nh, nkv, hd, 64, hd ** -0.5, None),
+                a.reps, 1, False)
+    flops = 4.0 * B * nh * hd * T * (T + 1) / 2
+    print(f"tcgen05 prefill attention: {B} prompts of {T}: {us:8.1f} us  {flops / us / 1e6:6.0f} TFLOP/s on the causal half")
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(prog="python -m herbert_rs_b200.ops.microbench", description=__doc__.split("\n\n")[0])
+    ap.add_argument("what", choices=["decode-gemm", "prefill-gemm", "decode-attention", "prefill-attention"])
+    ap.add_argument("--rows", type=int, default=8, help="activation rows of the products")
+    ap.add_argument("--layers", type=int, default=12, help="copies of the weights / caches cycled through")
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--seqs", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2050)
+    ap.add_argument("--len", type=int, default=2048)
+    ap.add_argument("--splits", type=int, default=0, help="key ranges per (sequence, kv head); 0: as the engine chooses")
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--intermediate", type=int, default=12288)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device")
+    {"decode-gemm": decode_gemm, "prefill-gemm": prefill_gemm, "decode-attention": decode_attention,
+     "prefill-attention": prefill_attention}[a.what](a)
+
+
+if __name__ == "__main__":
+    main()

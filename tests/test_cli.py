@@ -52,3 +52,14 @@ def test_cli_generates_what_the_library_call_generates(model_dirs, tmp_path):
     assert os.path.getsize(tmp_path / "l.f32") == 2 * 384 * 4
     p = subprocess.run(cmd[:4] + ["--backend", "tpu", "--prompt-ids", "1"], capture_output=True, text=True, timeout=600)
     assert p.returncode == 1 and "unknown backend" in p.stderr
+
+
+def test_microbench_says_what_it_needs_without_a_gpu():
+    import torch
+    from herbert_rs_b200.ops import microbench
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(SystemExit, match="CUDA device"):
+        microbench.main(["decode-gemm", "--rows", "8"])
+    with pytest.raises(SystemExit):
+        microbench.main(["no-such-kernel"])
