@@ -292,6 +292,14 @@ def check_kernel_errors() -> None:
         code = int(flag.item())
         if code != 0:
             flag.zero_()
+            # a kernel that gave up may have left arrival counters mid-count: start them afresh
+            for table in (_decode_counters, ):
+                if key in table:
+                    table[key].zero_()
+            if _tcgen05_ws.get(key) is not None:
+                _tcgen05_ws[key][1].zero_()
+            if key in _stream_bufs:
+                _stream_bufs[key][1].zero_()
             raise BackendError(f"a kernel on {key} gave up waiting on a barrier (code {code}); its output is not valid")
 
 
