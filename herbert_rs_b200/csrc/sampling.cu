@@ -192,10 +192,11 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature, int top_k,
-              float top_p, const float* __restrict__ uniforms, int* __restrict__ out) {
+              float top_p, const float* __restrict__ uniforms, int* __restrict__ out, const int* __restrict__ only_rows) {
   __shared__ SampleShared sh;
   pdl_wait();
   pdl_launch();
+  if (only_rows != nullptr && only_rows[blockIdx.x] == 0) return;      // the list kernel has chosen for this row
   const int tid = threadIdx.x;
   const float* row = logits + (size_t)blockIdx.x * ld;
 
@@ -346,14 +347,427 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, float tempera
   if (tid == 0) out[blockIdx.x] = sh.result >= 0 ? sh.result : max(sh.last_survivor, 0);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same choice when top_k is small against a large vocabulary (the usual case: 40 of 151,936).
+// The kernel above walks the whole row a dozen times with one CTA; here the row is read twice:
+//   pass 1  histogram of the keys' top 12 bits (sign, exponent, 3 bits of the fraction: an eighth
+//           of an octave per bin) -> the bin b that holds the top_k-th largest value;
+//   pass 2  every element whose top 12 bits are >= b goes into a list in shared memory (value /
+//           temperature and index, in any order); that list holds all top_k survivors and ties.
+// Everything else (the exact top_k threshold, maximum, softmax mass, the nucleus threshold and the
+// draw in index order) then runs over the list with the arithmetic of the kernel above.  A row with
+// more candidates than the list holds (flat logits) is left to the kernel above.  Without top_k
+// (top_p alone) the list takes as many whole bins from the top as it holds, pass 2 also sums the
+// row's softmax mass, and a row whose nucleus reaches below the list is left to the kernel above.
+// Scans done by one warp instead of one thread (a thread's serial walk over hundreds of bins in
+// shared memory costs tens of microseconds).  Bins are walked from the highest down.
+//   count form: the bin b with  sum(hist[b+1..]) < want <= sum(hist[b..]);  returns b and the sum above it.
+__device__ __forceinline__ void warp_find_count_bin(const unsigned int* hist, int nbins, int want, int lane, int* bin_out, int* above_out) {
+  const int per = nbins / 32;                       // nbins is a multiple of 32
+  const int hi = nbins - 1 - lane * per;            // this lane's bins: hi, hi-1, ..., hi-per+1
+  int mine = 0;
+  for (int j = 0; j < per; ++j) mine += (int)hist[hi - j];
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const int excl = incl - mine;                      // count in all bins above this lane's
+  const unsigned int owners = __ballot_sync(0xffffffffu, excl < want && incl >= want);
+  const int owner = owners ? __ffs(owners) - 1 : 31; // nobody: fewer elements than wanted, the lowest bin
+  if (lane == owner) {
+    int cum = excl, b = hi;
+    for (int j = 0; j < per; ++j, --b) {
+      if (cum + (int)hist[b] >= want || j == per - 1) break;
+      cum += (int)hist[b];
+    }
+    *bin_out = b;
+    *above_out = cum;
+  }
+}
+//   mass form (nucleus): among bins with entries, the highest b with  above + sum(mass[b..]) >= target;
+//   if rounding leaves the total below the target, the lowest bin with entries.  Returns b and the mass above it.
+__device__ __forceinline__ void warp_find_mass_bin(const unsigned int* hist, const float* mass, float above, float target, int lane,
+                                                   int* bin_out, float* above_out) {
+  const int hi = 255 - lane * 8;
+  float mine = 0.0f;
+  for (int j = 0; j < 8; ++j) mine += mass[hi - j];
+  float incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const float excl = above + (incl - mine);
+  // walk this lane's bins exactly as a single thread would, starting from the mass above them
+  int found_b = -1, lowest = -1;
+  float cum = excl, found_cum = 0.0f;
+  for (int j = 0; j < 8; ++j) {
+    const int b = hi - j;
+    if (hist[b] == 0) continue;
+    lowest = b;
+    if (found_b < 0 && cum + mass[b] >= target) {
+      found_b = b;
+      found_cum = cum;
+    }
+    cum += mass[b];
+  }
+  const unsigned int finders = __ballot_sync(0xffffffffu, found_b >= 0);
+  const unsigned int havers = __ballot_sync(0xffffffffu, lowest >= 0);
+  if (finders) {
+    if (lane == __ffs(finders) - 1) {
+      *bin_out = found_b;
+      *above_out = found_cum;
+    }
+  } else if (havers) {
+    const int owner = 31 - __clz(havers);            // the lane with the lowest bins that has entries
+    if (lane == owner) {
+      *bin_out = lowest;
+      *above_out = cum - mass[lowest];
+    }
+  }
+}
+
+#define SAMPLE_LIST 2048
+#define SAMPLE_BINS 4096       // 12 bits
+
+struct SampleListShared {
+  float val[SAMPLE_LIST];
+  int idx[SAMPLE_LIST];
+  unsigned int hist[SAMPLE_BINS];  // pass 1: 12-bit bins; then its first 256 entries serve the radix passes;
+                                   // at the end the whole array holds the survivors (values, then indices)
+  unsigned long long mass64[256];  // masses as integers (x 2^40): sums that do not depend on the order of the adds
+  unsigned long long acc64;
+  float mass[256];
+  float red[32];
+  float scan[SAMPLE_THREADS];
+  unsigned int prefix;
+  int remaining;
+  float mass_above;
+  int chosen_thread;
+  int result;
+  int bin, n, above;
+};
+
+__device__ __forceinline__ unsigned long long mass_fixed(float e) { return __float2ull_rn(e * 0x1p40f); }
+
+// Sum of the threads' integers over the block; every thread gets it.
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* acc) {
+  __syncthreads();
+  if (threadIdx.x == 0) *acc = 0ull;
+  __syncthreads();
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0 && v != 0ull) atomicAdd(acc, v);
+  __syncthreads();
+  return *acc;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature, int top_k,
+                   float top_p, const float* __restrict__ uniforms, int* __restrict__ out, int* __restrict__ overflow) {
+  __shared__ SampleListShared sh;
+  pdl_wait();
+  pdl_launch();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* row = logits + (size_t)blockIdx.x * ld;
+  const bool vec = (ld & 3) == 0 && (((uintptr_t)logits) & 15) == 0;
+  const int nvec = vec ? vocab >> 2 : 0;                    // float4 groups; the rest one by one
+
+  // ---- pass 1: histogram of the keys' top 12 bits, and the row's maximum ----------------------------
+  for (int i = tid; i < SAMPLE_BINS; i += SAMPLE_THREADS) sh.hist[i] = 0;
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int v0 = tid; v0 < nvec; v0 += 2 * SAMPLE_THREADS) {
+    float4 x[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (v0 + u * SAMPLE_THREADS < nvec) x[u] = reinterpret_cast<const float4*>(row)[v0 + u * SAMPLE_THREADS];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (v0 + u * SAMPLE_THREADS < nvec) {
+        const float sv[4] = {x[u].x / temperature, x[u].y / temperature, x[u].z / temperature, x[u].w / temperature};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          mx = fmaxf(mx, sv[j]);
+          atomicAdd(&sh.hist[order_key(sv[j]) >> 20], 1u);
+        }
+      }
+  }
+  for (int i = 4 * nvec + tid; i < vocab; i += SAMPLE_THREADS) {
+    const float sv = row[i] / temperature;
+    mx = fmaxf(mx, sv);
+    atomicAdd(&sh.hist[order_key(sv) >> 20], 1u);
+  }
+  mx = block_max(mx, sh.red);                       // its barriers also close the histogram
+  if (warp == 0) {
+    if (top_k > 0) {
+      // the bin of the top_k-th largest value: the list takes that bin and every bin above it
+      warp_find_count_bin(sh.hist, SAMPLE_BINS, top_k, lane, &sh.bin, &sh.above);
+      __syncwarp();
+      if (lane == 0) sh.n = sh.above + (int)sh.hist[sh.bin];
+    } else {
+      // no top_k: as many whole bins from the top as the list holds
+      warp_find_count_bin(sh.hist, SAMPLE_BINS, SAMPLE_LIST + 1, lane, &sh.bin, &sh.above);
+      __syncwarp();
+      if (lane == 0) {
+        sh.bin += 1;
+        sh.n = sh.above;
+      }
+    }
+  }
+  __syncthreads();
+  const unsigned int bin = (unsigned int)sh.bin;
+  const int n = sh.n;
+  if (n > SAMPLE_LIST || n == 0) {                // the list cannot hold the candidates: the general kernel takes the row
+    if (tid == 0) {
+      overflow[blockIdx.x] = 1;
+      out[blockIdx.x] = 0;
+    }
+    return;
+  }
+  if (tid == 0) overflow[blockIdx.x] = 0;
+
+  // ---- pass 2: the candidates into the list, in any order; without top_k also the row's softmax mass
+  if (tid == 0) sh.remaining = 0;                  // the list's fill count
+  __syncthreads();
+  const bool whole_mass = top_k <= 0;
+  float row_mass = 0.0f;                           // per thread over a fixed set of elements in a fixed order
+  for (int v0 = tid; v0 < nvec; v0 += 2 * SAMPLE_THREADS) {
+    float4 x[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (v0 + u * SAMPLE_THREADS < nvec) x[u] = reinterpret_cast<const float4*>(row)[v0 + u * SAMPLE_THREADS];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (v0 + u * SAMPLE_THREADS < nvec) {
+        const float sv[4] = {x[u].x / temperature, x[u].y / temperature, x[u].z / temperature, x[u].w / temperature};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (whole_mass) row_mass += expf(sv[j] - mx);
+          if ((order_key(sv[j]) >> 20) >= bin) {
+            const int pos = atomicAdd(&sh.remaining, 1);     // < n <= SAMPLE_LIST: the histogram counted the same elements
+            sh.val[pos] = sv[j];
+            sh.idx[pos] = 4 * (v0 + u * SAMPLE_THREADS) + j;
+          }
+        }
+      }
+  }
+  for (int i = 4 * nvec + tid; i < vocab; i += SAMPLE_THREADS) {
+    const float sv = row[i] / temperature;
+    if (whole_mass) row_mass += expf(sv - mx);
+    if ((order_key(sv) >> 20) >= bin) {
+      const int pos = atomicAdd(&sh.remaining, 1);
+      sh.val[pos] = sv;
+      sh.idx[pos] = i;
+    }
+  }
+  __syncthreads();
+
+  // ---- A: key of the top_k-th largest value, exactly (radix descent over the list) -----------------
+  unsigned int kth_key = 0;
+  if (top_k > 0 && top_k < n) {
+    if (tid == 0) {
+      sh.prefix = 0;
+      sh.remaining = top_k;
+    }
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (tid < 256) sh.hist[tid] = 0;
+      __syncthreads();
+      const unsigned int prefix = sh.prefix;
+      const unsigned int himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = tid; i < n; i += SAMPLE_THREADS) {
+        const unsigned int key = order_key(sh.val[i]);
+        if ((key & himask) == prefix) atomicAdd(&sh.hist[(key >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (warp == 0) {
+        const int want = sh.remaining;
+        __syncwarp();
+        warp_find_count_bin(sh.hist, 256, want, lane, &sh.bin, &sh.above);
+        __syncwarp();
+        if (lane == 0) {
+          sh.remaining = want - sh.above;
+          sh.prefix = prefix | ((unsigned int)sh.bin << shift);
+        }
+      }
+      __syncthreads();
+    }
+    kth_key = sh.prefix;
+  }
+
+  // ---- B: softmax mass of the survivors (the list is in no fixed order: integer sums) ----------------
+  unsigned long long part = 0ull;
+  for (int i = tid; i < n; i += SAMPLE_THREADS)
+    if (order_key(sh.val[i]) >= kth_key) part += mass_fixed(expf(sh.val[i] - mx));
+  const float list_mass = (float)block_sum_u64(part, &sh.acc64) * 0x1p-40f;
+  float sum_e = list_mass;
+  if (whole_mass) {
+    sum_e = block_sum(row_mass, sh.red);
+    if (list_mass < top_p * sum_e) {               // the nucleus reaches below the list: the general kernel takes the row
+      if (tid == 0) {
+        overflow[blockIdx.x] = 1;
+        out[blockIdx.x] = 0;
+      }
+      return;
+    }
+  }
+
+  // ---- C: nucleus threshold key ------------------------------------------------------------------
+  unsigned int final_key = kth_key;
+  if (top_p < 1.0f) {
+    const float target = top_p * sum_e;
+    if (tid == 0) {
+      sh.prefix = 0;
+      sh.mass_above = 0.0f;
+    }
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (tid < 256) {
+        sh.mass64[tid] = 0ull;
+        sh.hist[tid] = 0;
+      }
+      __syncthreads();
+      const unsigned int prefix = sh.prefix;
+      const unsigned int himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = tid; i < n; i += SAMPLE_THREADS) {
+        const float sval = sh.val[i];
+        const unsigned int key = order_key(sval);
+        if (key >= kth_key && (key & himask) == prefix) {
+          atomicAdd(&sh.mass64[(key >> shift) & 255u], mass_fixed(expf(sval - mx)));
+          atomicAdd(&sh.hist[(key >> shift) & 255u], 1u);
+        }
+      }
+      __syncthreads();
+      if (tid < 256) sh.mass[tid] = (float)sh.mass64[tid] * 0x1p-40f;
+      __syncthreads();
+      if (warp == 0) {
+        const float above = sh.mass_above;
+        __syncwarp();
+        warp_find_mass_bin(sh.hist, sh.mass, above, target, lane, &sh.bin, &sh.mass_above);
+        __syncwarp();
+        if (lane == 0) sh.prefix = prefix | ((unsigned int)sh.bin << shift);
+      }
+      __syncthreads();
+    }
+    if (sh.prefix > final_key) final_key = sh.prefix;
+  }
+
+  // ---- the survivors, put in index order -----------------------------------------------------------
+  float* sval = reinterpret_cast<float*>(sh.hist);
+  int* sidx = reinterpret_cast<int*>(sh.hist + SAMPLE_LIST);
+  if (tid == 0) sh.remaining = 0;
+  __syncthreads();
+  for (int i = tid; i < n; i += SAMPLE_THREADS)
+    if (order_key(sh.val[i]) >= final_key) {
+      const int pos = atomicAdd(&sh.remaining, 1);
+      sval[pos] = sh.val[i];
+      sidx[pos] = sh.idx[i];
+    }
+  __syncthreads();
+  const int ns = sh.remaining;
+  {
+    // rank of a survivor = survivors with a smaller index; every thread holds its (at most two)
+    // survivors in registers over the barrier and stores them at their ranks
+    float my_val[SAMPLE_LIST / SAMPLE_THREADS];
+    int my_idx[SAMPLE_LIST / SAMPLE_THREADS], my_rank[SAMPLE_LIST / SAMPLE_THREADS];
+#pragma unroll
+    for (int e = 0; e < SAMPLE_LIST / SAMPLE_THREADS; ++e) {
+      const int i = tid + e * SAMPLE_THREADS;
+      my_rank[e] = -1;
+      if (i < ns) {
+        my_val[e] = sval[i];
+        my_idx[e] = sidx[i];
+        int r = 0;
+        for (int j = 0; j < ns; ++j) r += sidx[j] < my_idx[e] ? 1 : 0;
+        my_rank[e] = r;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < SAMPLE_LIST / SAMPLE_THREADS; ++e)
+      if (my_rank[e] >= 0) {
+        sval[my_rank[e]] = my_val[e];
+        sidx[my_rank[e]] = my_idx[e];
+      }
+    __syncthreads();
+  }
+
+  // ---- D/E: draw in index order over contiguous segments of the survivors ----------------------------
+  const int seg = (ns + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  const int beg = min(ns, tid * seg), end = min(ns, beg + seg);
+  float segmass = 0.0f;
+  for (int i = beg; i < end; ++i) segmass += expf(sval[i] - mx);
+  if (tid == 0) {
+    sh.chosen_thread = 0x7fffffff;
+    sh.result = -1;
+  }
+  // inclusive scan of the segments' masses over the block, as a fixed tree: within a warp, then over the warps
+  float run = segmass;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, run, o);
+    if (lane >= o) run += t;
+  }
+  if (lane == 31) sh.red[warp] = run;
+  __syncthreads();
+  if (warp == 0) {
+    float w = sh.red[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += t;
+    }
+    sh.red[lane] = w;                                // inclusive over the warps
+  }
+  __syncthreads();
+  sh.scan[tid] = run + (warp > 0 ? sh.red[warp - 1] : 0.0f);
+  __syncthreads();
+  const float total = sh.scan[SAMPLE_THREADS - 1];
+  const float target = uniforms[blockIdx.x] * total;
+  const float incl = sh.scan[tid];
+  const float excl = tid == 0 ? 0.0f : sh.scan[tid - 1];
+  if (segmass > 0.0f && target < incl) atomicMin(&sh.chosen_thread, tid);
+  __syncthreads();
+  if (sh.chosen_thread == tid) {
+    float c = excl;
+    int pick = sidx[end - 1];
+    for (int i = beg; i < end; ++i) {
+      c += expf(sval[i] - mx);
+      if (target < c) {
+        pick = sidx[i];
+        break;
+      }
+    }
+    sh.result = pick;
+  }
+  __syncthreads();
+  if (tid == 0) out[blockIdx.x] = sh.result >= 0 ? sh.result : (ns > 0 ? sidx[ns - 1] : 0);
+}
+
+// overflow (optional): n_rows ints of scratch; with it, a small top_k against a large vocabulary
+// takes the two-pass list kernel, and the general kernel only runs for rows the list could not hold.
 extern "C" int hb_sample(const float* logits, int ld, int n_rows, int vocab, float temperature, int top_k,
-                         float top_p, const float* uniforms, int* out, void* stream) {
+                         float top_p, const float* uniforms, int* out, int* overflow, void* stream) {
   HB_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "sample: bad sizes");
   HB_REQUIRE(temperature > 0.0f, "sample: temperature must be > 0 (0 is greedy: use argmax)");
   HB_REQUIRE(top_k >= 0, "sample: top_k must be >= 0");
   HB_REQUIRE(top_p > 0.0f, "sample: top_p must be > 0");
+  const bool small_k = top_k > 0 && top_k <= SAMPLE_LIST / 4, nucleus_only = top_k == 0 && top_p < 1.0f;
+  if (overflow != nullptr && (small_k || nucleus_only) && vocab >= 4 * SAMPLE_LIST) {
+    hb_launch(sample_topk_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, ld, vocab, temperature,
+              top_k, top_p, uniforms, out, overflow);
+    HB_CHECK_LAUNCH("sample_topk");
+    // the general kernel returns at once for every row that is done (all of them, unless logits are flat)
+    hb_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, ld, vocab, temperature, top_k,
+              top_p, uniforms, out, (const int*)overflow);
+    HB_CHECK_LAUNCH("sample");
+    return 0;
+  }
   hb_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, ld, vocab, temperature, top_k,
-                                                                    top_p, uniforms, out);
+            top_p, uniforms, out, (const int*)nullptr);
   HB_CHECK_LAUNCH("sample");
   return 0;
 }

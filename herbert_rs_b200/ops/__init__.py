@@ -59,7 +59,7 @@ _SIGS = {
                                     c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_gemm_skinny_norm_parts": [c_int, c_int],
-    "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p],
+    "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 _fns: dict = {}
 
@@ -81,7 +81,7 @@ def _fn(name: str):
 
 
 # kernels each launcher starts (for honest launch counts)
-_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_attention_decode_tc_bf16": 2, "hb_argmax": 2}
+_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_attention_decode_tc_bf16": 2, "hb_argmax": 2, "hb_sample": 2}
 _launches = 0
 
 
@@ -199,10 +199,19 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
          sc.data_ptr(), sc.numel(), _stream())
 
 
+_sample_flags: dict = {}
+
+
 def sample(logits, temperature, top_k, top_p, uniforms, out) -> None:
+    """One token per row under temperature / top-k / top-p with the row's uniform.  A small top_k
+    against a large vocabulary takes a kernel that reads the row twice and works on a list of
+    candidates in shared memory; rows it cannot hold fall to the general kernel in the same call."""
     _check(logits, torch.float32, "logits"); _check(uniforms, torch.float32, "uniforms"); _check(out, torch.int32, "out")
+    key = str(logits.device)
+    if key not in _sample_flags or _sample_flags[key].numel() < logits.shape[0]:
+        _sample_flags[key] = torch.zeros(max(1024, logits.shape[0]), dtype=torch.int32, device=logits.device)
     _run("hb_sample", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], float(temperature),
-         int(top_k), float(top_p), uniforms.data_ptr(), out.data_ptr(), _stream())
+         int(top_k), float(top_p), uniforms.data_ptr(), out.data_ptr(), _sample_flags[key].data_ptr(), _stream())
 
 
 def gemm_skinny(a, w, c, epilogue=EPI_STORE) -> None:

@@ -274,6 +274,53 @@ def test_sample_kernel_against_its_host_twin_and_the_reference_distribution(t, k
     assert np.abs(np.bincount(got, minlength=V) / R - want).max() < 3.0 / R + 1e-5
 
 
+@pytest.mark.parametrize("t,k,p,listed", [(0.7, 40, 0.9, True), (1.0, 5, 1.0, True), (0.4, 1000, 0.95, None),
+                                          (0.25, 0, 0.9, True), (0.3, 0, 0.999, True), (1.0, 0, 0.95, False)])
+def test_sample_with_a_small_top_k_against_a_large_vocabulary(t, k, p, listed):
+    """The two-pass kernel that works on a list of candidates: same survivors, intervals and
+    distribution as the host twin; ties at the top_k-th value all survive; a row of flat logits (more
+    candidates than the list holds) falls to the general kernel in the same call.  With top_p alone
+    the list serves a peaked row and the general kernel a row whose nucleus is wider than the list;
+    `listed` says which of the two is expected to have chosen (None: the general kernel alone)."""
+    rng = np.random.default_rng(9)
+    V, R = 40000, 2048
+    logits = (rng.standard_normal(V) * 2.5).astype(np.float32)
+    us = ((np.arange(R) + 0.5) / R).astype(np.float32)
+    rows = dev(torch.from_numpy(logits)).expand(R, V).contiguous()
+    out = torch.full((R,), -7, dtype=torch.int32, device="cuda")
+    ops.sample(rows, t, k, p, dev(torch.from_numpy(us)), out)
+    got = out.cpu().numpy()
+    if listed is not None:
+        assert (ops._sample_flags[str(rows.device)][:R].cpu().numpy() == (0 if listed else 1)).all()
+    params = SamplingParams(t, k, p)
+    keep, e = host_survivors(logits, params)
+    assert keep[got].all()
+    c = np.cumsum(e.astype(np.float64)); c /= c[-1]
+    lo = np.concatenate([[0.0], c[:-1]])
+    assert (us >= lo[got] - 1e-5).all() and (us <= c[got] + 1e-5).all()
+    twin = np.array([host_sample(logits, params, float(u)) for u in us[::64]])
+    assert (twin == got[::64]).mean() > 0.99
+    want = sample_distribution(logits, t, k, p)
+    assert np.abs(np.bincount(got, minlength=V) / R - want).max() < 3.0 / R + 1e-5
+    # mixed rows: row 0 flat (all values within an eighth of an octave: 40,000 candidates, more than
+    # the list holds), row 1 as above, row 2 with four equal values across the top_k edge (all survive)
+    flat = (1.0 + 0.1 * rng.random(V)).astype(np.float32)
+    tied = logits.copy()
+    order = np.argsort(-tied)
+    if k > 0:
+        tied[order[k - 1:k + 3]] = tied[order[k - 1]]
+    three = dev(torch.from_numpy(np.stack([flat, logits, tied])))
+    for u in (0.37, 0.999):
+        out3 = torch.full((3,), -7, dtype=torch.int32, device="cuda")
+        ops.sample(three, t, k, p, dev(torch.full((3,), u)), out3)
+        g3 = out3.cpu().numpy()
+        for row, g in zip((flat, logits, tied), g3):
+            assert host_survivors(row, params)[0][g]
+            assert g == host_sample(row, params, u)
+    if p == 1.0:
+        assert host_survivors(tied, params)[0].sum() == k + 3
+
+
 def test_sample_refuses_bad_options():
     x = dev(torch.zeros(1, 8)); u = dev(torch.zeros(1)); o = torch.empty(1, dtype=torch.int32, device="cuda")
     with pytest.raises(BackendError, match="temperature must be > 0"):
