@@ -350,8 +350,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, float tempera
 // ---------------------------------------------------------------------------------------------
 // The same choice when top_k is small against a large vocabulary (the usual case: 40 of 151,936).
 // The kernel above walks the whole row a dozen times with one CTA; here the row is read twice:
-//   pass 1  histogram of the keys' top 12 bits (sign, exponent, 3 bits of the fraction: an eighth
-//           of an octave per bin) -> the bin b that holds the top_k-th largest value;
+//   pass 1  histogram of the top 12 bits of the raw logits' keys (sign, exponent, 3 bits of the
+//           fraction: an eighth of an octave per bin) -> the bin b that holds the top_k-th largest value;
 //   pass 2  every element whose top 12 bits are >= b goes into a list in shared memory (value /
 //           temperature and index, in any order); that list holds all top_k survivors and ties.
 // Everything else (the exact top_k threshold, maximum, softmax mass, the nucleus threshold and the
@@ -464,7 +464,7 @@ __device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v
   return *acc;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+__global__ void __launch_bounds__(SAMPLE_THREADS, 1)
 sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float temperature, int top_k,
                    float top_p, const float* __restrict__ uniforms, int* __restrict__ out, int* __restrict__ overflow) {
   __shared__ SampleListShared sh;
@@ -478,6 +478,8 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
   // ---- pass 1: histogram of the keys' top 12 bits, and the row's maximum ----------------------------
   for (int i = tid; i < SAMPLE_BINS; i += SAMPLE_THREADS) sh.hist[i] = 0;
   __syncthreads();
+  // Bins and the maximum are taken on the raw logits: dividing by the temperature (> 0) keeps the
+  // order, so the bin of the top_k-th raw value bounds the same candidates, and max(x / t) = max(x) / t.
   float mx = -INFINITY;
   for (int v0 = tid; v0 < nvec; v0 += 2 * SAMPLE_THREADS) {
     float4 x[2];
@@ -487,19 +489,19 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
 #pragma unroll
     for (int u = 0; u < 2; ++u)
       if (v0 + u * SAMPLE_THREADS < nvec) {
-        const float sv[4] = {x[u].x / temperature, x[u].y / temperature, x[u].z / temperature, x[u].w / temperature};
+        const float xv[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          mx = fmaxf(mx, sv[j]);
-          atomicAdd(&sh.hist[order_key(sv[j]) >> 20], 1u);
+          mx = fmaxf(mx, xv[j]);
+          atomicAdd(&sh.hist[order_key(xv[j]) >> 20], 1u);
         }
       }
   }
   for (int i = 4 * nvec + tid; i < vocab; i += SAMPLE_THREADS) {
-    const float sv = row[i] / temperature;
-    mx = fmaxf(mx, sv);
-    atomicAdd(&sh.hist[order_key(sv) >> 20], 1u);
+    mx = fmaxf(mx, row[i]);
+    atomicAdd(&sh.hist[order_key(row[i]) >> 20], 1u);
   }
+  mx = mx / temperature;
   mx = block_max(mx, sh.red);                       // its barriers also close the histogram
   if (warp == 0) {
     if (top_k > 0) {
@@ -542,24 +544,24 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
 #pragma unroll
     for (int u = 0; u < 2; ++u)
       if (v0 + u * SAMPLE_THREADS < nvec) {
-        const float sv[4] = {x[u].x / temperature, x[u].y / temperature, x[u].z / temperature, x[u].w / temperature};
+        const float xv[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          if (whole_mass) row_mass += expf(sv[j] - mx);
-          if ((order_key(sv[j]) >> 20) >= bin) {
+          if (whole_mass) row_mass += expf(xv[j] / temperature - mx);
+          if ((order_key(xv[j]) >> 20) >= bin) {
             const int pos = atomicAdd(&sh.remaining, 1);     // < n <= SAMPLE_LIST: the histogram counted the same elements
-            sh.val[pos] = sv[j];
+            sh.val[pos] = xv[j] / temperature;
             sh.idx[pos] = 4 * (v0 + u * SAMPLE_THREADS) + j;
           }
         }
       }
   }
   for (int i = 4 * nvec + tid; i < vocab; i += SAMPLE_THREADS) {
-    const float sv = row[i] / temperature;
-    if (whole_mass) row_mass += expf(sv - mx);
-    if ((order_key(sv) >> 20) >= bin) {
+    const float xv = row[i];
+    if (whole_mass) row_mass += expf(xv / temperature - mx);
+    if ((order_key(xv) >> 20) >= bin) {
       const int pos = atomicAdd(&sh.remaining, 1);
-      sh.val[pos] = sv;
+      sh.val[pos] = xv / temperature;
       sh.idx[pos] = i;
     }
   }

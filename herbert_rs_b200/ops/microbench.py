@@ -4,6 +4,7 @@
     python -m herbert_rs_b200.ops.microbench prefill-gemm --rows 2048
     python -m herbert_rs_b200.ops.microbench decode-attention --seqs 8 --context 2050 --splits 4
     python -m herbert_rs_b200.ops.microbench prefill-attention --seqs 1 --len 2048
+    python -m herbert_rs_b200.ops.microbench sampling --seqs 8 --vocab 151936
 
 Shapes default to the Qwen3-8B layer (hidden 4096, 32 query / 8 key-value heads of 128,
 intermediate 12288).  Every launch of a timed loop reads other weights or another layer's cache
@@ -113,9 +114,22 @@ def prefill_attention(a):
     print(f"tcgen05 prefill attention: {B} prompts of {T}: {us:8.1f} us  {flops / us / 1e6:6.0f} TFLOP/s on the causal half")
 
 
+def sampling(a):
+    """argmax and the sampler's settings on rows of normal logits (standard deviation --spread)."""
+    B, V = a.seqs, a.vocab
+    logits = [torch.randn(B, V, device="cuda") * a.spread for _ in range(a.layers)]
+    u = torch.rand(B, device="cuda")
+    out = torch.empty(B, dtype=torch.int32, device="cuda")
+    line = f"{B} rows of {V}: argmax {_timed(lambda: [ops.argmax(x, out) for x in logits], a.reps, a.layers, True):6.1f} us"
+    for t, k, p in ((0.7, 40, 0.9), (1.0, 0, 0.95), (0.2, 0, 0.95), (1.0, 0, 1.0)):
+        us = _timed(lambda: [ops.sample(x, t, k, p, u, out) for x in logits], a.reps, a.layers, True)
+        line += f";  t {t} k {k} p {p} {us:7.1f} us"
+    print(line)
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="python -m herbert_rs_b200.ops.microbench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["decode-gemm", "prefill-gemm", "decode-attention", "prefill-attention"])
+    ap.add_argument("what", choices=["decode-gemm", "prefill-gemm", "decode-attention", "prefill-attention", "sampling"])
     ap.add_argument("--rows", type=int, default=8, help="activation rows of the products")
     ap.add_argument("--layers", type=int, default=12, help="copies of the weights / caches cycled through")
     ap.add_argument("--reps", type=int, default=10)
@@ -128,11 +142,13 @@ def main(argv=None) -> None:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--spread", type=float, default=3.0, help="standard deviation of the logits of `sampling`")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device")
     {"decode-gemm": decode_gemm, "prefill-gemm": prefill_gemm, "decode-attention": decode_attention,
-     "prefill-attention": prefill_attention}[a.what](a)
+     "prefill-attention": prefill_attention, "sampling": sampling}[a.what](a)
 
 
 if __name__ == "__main__":
