@@ -20,6 +20,9 @@ __device__ __forceinline__ unsigned int order_key(float v) {
   unsigned int u = __float_as_uint(v);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
+__device__ __forceinline__ float key_value(unsigned int k) {       // the inverse of order_key
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
 
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(SAMPLE_THREADS)
@@ -167,6 +170,78 @@ extern "C" int hb_argmax(const float* logits, int ld, int n_rows, int vocab, int
 }
 
 // ---------------------------------------------------------------------------------------------
+// Scans done by one warp instead of one thread (a thread's serial walk over hundreds of bins in
+// shared memory costs tens of microseconds).  Bins are walked from the highest down.
+//   count form: the bin b with  sum(hist[b+1..]) < want <= sum(hist[b..]);  returns b and the sum above it.
+__device__ __forceinline__ void warp_find_count_bin(const unsigned int* hist, int nbins, int want, int lane, int* bin_out, int* above_out) {
+  const int per = nbins / 32;                       // nbins is a multiple of 32
+  const int hi = nbins - 1 - lane * per;            // this lane's bins: hi, hi-1, ..., hi-per+1
+  int mine = 0;
+  for (int j = 0; j < per; ++j) mine += (int)hist[hi - j];
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const int excl = incl - mine;                      // count in all bins above this lane's
+  const unsigned int owners = __ballot_sync(0xffffffffu, excl < want && incl >= want);
+  const int owner = owners ? __ffs(owners) - 1 : 31; // nobody: fewer elements than wanted, the lowest bin
+  if (lane == owner) {
+    int cum = excl, b = hi;
+    for (int j = 0; j < per; ++j, --b) {
+      if (cum + (int)hist[b] >= want || j == per - 1) break;
+      cum += (int)hist[b];
+    }
+    *bin_out = b;
+    *above_out = cum;
+  }
+}
+//   mass form (nucleus): among bins with entries, the highest b with  above + sum(mass[b..]) >= target;
+//   if rounding leaves the total below the target, the lowest bin with entries.  Returns b and the mass above it.
+__device__ __forceinline__ void warp_find_mass_bin(const unsigned int* hist, const float* mass, int nbins, float above, float target,
+                                                   int lane, int* bin_out, float* above_out) {
+  const int per = nbins / 32;                       // nbins is a multiple of 32
+  const int hi = nbins - 1 - lane * per;
+  float mine = 0.0f;
+  for (int j = 0; j < per; ++j) mine += mass[hi - j];
+  float incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const float excl = above + (incl - mine);
+  // walk this lane's bins exactly as a single thread would, starting from the mass above them
+  int found_b = -1, lowest = -1;
+  float cum = excl, found_cum = 0.0f;
+  for (int j = 0; j < per; ++j) {
+    const int b = hi - j;
+    if (hist[b] == 0) continue;
+    lowest = b;
+    if (found_b < 0 && cum + mass[b] >= target) {
+      found_b = b;
+      found_cum = cum;
+    }
+    cum += mass[b];
+  }
+  const unsigned int finders = __ballot_sync(0xffffffffu, found_b >= 0);
+  const unsigned int havers = __ballot_sync(0xffffffffu, lowest >= 0);
+  if (finders) {
+    if (lane == __ffs(finders) - 1) {
+      *bin_out = found_b;
+      *above_out = found_cum;
+    }
+  } else if (havers) {
+    const int owner = 31 - __clz(havers);            // the lane with the lowest bins that has entries
+    if (lane == owner) {
+      *bin_out = lowest;
+      *above_out = cum - mass[lowest];
+    }
+  }
+}
+
+
 struct SampleShared {
   unsigned int hist[256];
   float mass[256];
@@ -178,6 +253,11 @@ struct SampleShared {
   int chosen_thread;
   int result;
   int last_survivor;
+  int last_of_warp[32];
+  int bin;
+  float target;
+  unsigned int hist12[4096];   // the nucleus search's first level: 12 bits
+  float mass12[4096];
 };
 
 __device__ __forceinline__ float block_max(float v, float* red) {
@@ -214,7 +294,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, float tempera
       const unsigned int prefix = sh.prefix;
       const unsigned int himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
       for (int i = tid; i < vocab; i += blockDim.x) {
-        const unsigned int key = order_key(row[i] / temperature);
+        const unsigned int key = order_key(row[i]);
         if ((key & himask) == prefix) atomicAdd(&sh.hist[(key >> shift) & 255u], 1u);
       }
       __syncthreads();
@@ -229,122 +309,232 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, float tempera
       }
       __syncthreads();
     }
-    kth_key = sh.prefix;
+    // the descent ran on the raw logits (dividing by a positive temperature keeps the order): the
+    // threshold among the scaled values is the scaled top_k-th raw value, ties included
+    kth_key = order_key(key_value(sh.prefix) / temperature);
   }
 
-  // ---- B: maximum and softmax mass of the survivors ---------------------------------------------
+  // ---- B: maximum (the nucleus search sums the survivors' softmax mass itself) -------------------------
   float mx = -INFINITY;
-  for (int i = tid; i < vocab; i += blockDim.x) mx = fmaxf(mx, row[i] / temperature);
-  mx = block_max(mx, sh.red);
-  float part = 0.0f;
-  for (int i = tid; i < vocab; i += blockDim.x) {
-    const float s = row[i] / temperature;
-    if (order_key(s) >= kth_key) part += expf(s - mx);
+  {
+    const bool vec4 = (ld & 3) == 0 && (((uintptr_t)logits) & 15) == 0;
+    const int nvec = vec4 ? vocab >> 2 : 0;
+    for (int v0 = tid; v0 < nvec; v0 += 2 * SAMPLE_THREADS) {
+      const float4 a = reinterpret_cast<const float4*>(row)[v0];
+      const float4 b = v0 + SAMPLE_THREADS < nvec ? reinterpret_cast<const float4*>(row)[v0 + SAMPLE_THREADS] : a;
+      mx = fmaxf(fmaxf(fmaxf(mx, a.x), fmaxf(a.y, a.z)), fmaxf(fmaxf(a.w, b.x), fmaxf(fmaxf(b.y, b.z), b.w)));
+    }
+    for (int i = 4 * nvec + tid; i < vocab; i += SAMPLE_THREADS) mx = fmaxf(mx, row[i]);
   }
-  const float sum_e = block_sum(part, sh.red);
+  mx = block_max(mx, sh.red) / temperature;          // max(x / t) = max(x) / t
 
-  // ---- C: nucleus threshold key ------------------------------------------------------------------
+  // ---- C: nucleus threshold key: radix descent over 12, 8, 8 and 4 bits of the keys ------------------
+  // The first level meets every surviving element; with 4,096 bins the lanes of a warp seldom add
+  // to the same bin at once (float atomics in shared memory take turns), the later levels meet only
+  // the elements of one bin.
   unsigned int final_key = kth_key;
   if (top_p < 1.0f) {
-    const float target = top_p * sum_e;
+    const int lane_c = tid & 31;
+    const bool vec4 = (ld & 3) == 0 && (((uintptr_t)logits) & 15) == 0;
+    const int nvec = vec4 ? vocab >> 2 : 0;
     if (tid == 0) {
       sh.prefix = 0;
       sh.mass_above = 0.0f;
     }
-    for (int pass = 0; pass < 4; ++pass) {
-      const int shift = 24 - 8 * pass;
-      for (int i = tid; i < 256; i += blockDim.x) {
-        sh.mass[i] = 0.0f;
-        sh.hist[i] = 0;
+    for (int level = 0; level < 4; ++level) {
+      const int bits = level == 0 ? 12 : (level == 3 ? 4 : 8);
+      const int shift = level == 0 ? 20 : (level == 1 ? 12 : (level == 2 ? 4 : 0));
+      unsigned int* hist = level == 0 ? sh.hist12 : sh.hist;
+      float* mass = level == 0 ? sh.mass12 : sh.mass;
+      const int nbins = level == 0 ? 4096 : 256;
+      for (int i = tid; i < nbins; i += SAMPLE_THREADS) {
+        mass[i] = 0.0f;
+        hist[i] = 0;
       }
       __syncthreads();
       const unsigned int prefix = sh.prefix;
-      const unsigned int himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-      for (int i = tid; i < vocab; i += blockDim.x) {
-        const float s = row[i] / temperature;
-        const unsigned int key = order_key(s);
+      const unsigned int himask = level == 0 ? 0u : (0xffffffffu << (shift + bits));
+      const unsigned int binmask = (1u << bits) - 1u;
+      auto count = [&](float x) {
+        const float sv = x / temperature;
+        const unsigned int key = order_key(sv);
         if (key >= kth_key && (key & himask) == prefix) {
-          atomicAdd(&sh.mass[(key >> shift) & 255u], expf(s - mx));
-          atomicAdd(&sh.hist[(key >> shift) & 255u], 1u);
+          atomicAdd(&mass[(key >> shift) & binmask], expf(sv - mx));
+          atomicAdd(&hist[(key >> shift) & binmask], 1u);
+        }
+      };
+      for (int v0 = tid; v0 < nvec; v0 += 2 * SAMPLE_THREADS) {
+        const float4 a = reinterpret_cast<const float4*>(row)[v0];
+        const bool two = v0 + SAMPLE_THREADS < nvec;
+        const float4 b = two ? reinterpret_cast<const float4*>(row)[v0 + SAMPLE_THREADS] : a;
+        count(a.x); count(a.y); count(a.z); count(a.w);
+        if (two) {
+          count(b.x); count(b.y); count(b.z); count(b.w);
         }
       }
+      for (int i = 4 * nvec + tid; i < vocab; i += SAMPLE_THREADS) count(row[i]);
       __syncthreads();
-      if (tid == 0) {
-        float cum = sh.mass_above;
-        int b = 255, lowest = 255;
-        bool found = false;
-        for (; b >= 0; --b) {
-          if (sh.hist[b] == 0) continue;
-          lowest = b;
-          if (cum + sh.mass[b] >= target) {
-            found = true;
-            break;
-          }
-          cum += sh.mass[b];
+      if (tid < 32) {
+        if (level == 0) {
+          // the survivors' whole mass is the sum of the first level's bins, added in a fixed order
+          float total = 0.0f;
+          for (int i = lane_c; i < nbins; i += 32) total += mass[i];
+          total = warp_sum(total);
+          if (lane_c == 0) sh.target = top_p * total;
+          __syncwarp();
         }
-        if (!found) {  // rounding left the total just below the target: keep everything
-          b = lowest;
-          cum -= sh.mass[b];
-        }
-        sh.mass_above = cum;
-        sh.prefix = prefix | ((unsigned int)b << shift);
+        const float above = sh.mass_above, target = sh.target;
+        __syncwarp();
+        warp_find_mass_bin(hist, mass, nbins, above, target, lane_c, &sh.bin, &sh.mass_above);
+        __syncwarp();
+        if (lane_c == 0) sh.prefix = prefix | ((unsigned int)sh.bin << shift);
       }
       __syncthreads();
     }
     if (sh.prefix > final_key) final_key = sh.prefix;
   }
 
-  // ---- D/E: draw in index order over contiguous segments ----------------------------------------
-  const int seg = (vocab + blockDim.x - 1) / blockDim.x;
-  const int beg = tid * seg, end = min(vocab, beg + seg);
-  float segmass = 0.0f;
+  // ---- D/E: draw in index order.  Every warp owns a contiguous run of the row and reads it 128
+  // consecutive elements at a time; the warps' masses are scanned; the run that holds the target is
+  // cut into 32 sub-runs, one per warp, whose masses are scanned in turn; the warp of the sub-run
+  // that holds the target finds the element with warp scans over the values it kept in registers.
+  const int warp = tid >> 5, lane = tid & 31;        // the block has SAMPLE_THREADS threads: 32 warps
+  const int run = ((vocab + 31) / 32 + 127) & ~127;
+  const int beg = min(vocab, warp * run), end = min(vocab, beg + run);
+  const bool vec = (ld & 3) == 0 && (((uintptr_t)logits) & 15) == 0;
+  float lane_mass = 0.0f;
   int last = -1;
-  for (int i = beg; i < end; ++i) {
-    const float s = row[i] / temperature;
-    if (order_key(s) >= final_key) {
-      segmass += expf(s - mx);
-      last = i;
+  for (int i0 = beg + 4 * lane; i0 < end; i0 += 256) {
+    float x[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = i0 + 128 * u;
+      if (vec && i + 3 < end) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        x[u][0] = v.x; x[u][1] = v.y; x[u][2] = v.z; x[u][3] = v.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[u][j] = i + j < end ? row[i + j] : 0.0f;
+      }
     }
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = i0 + 128 * u + j;
+        const float sv = x[u][j] / temperature;
+        if (i < end && order_key(sv) >= final_key) {
+          lane_mass += expf(sv - mx);
+          last = i;
+        }
+      }
   }
-  sh.scan[tid] = segmass;
+  lane_mass = warp_sum(lane_mass);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
   if (tid == 0) {
-    sh.chosen_thread = 0x7fffffff;
     sh.result = -1;
     sh.last_survivor = -1;
   }
   __syncthreads();
-  if (tid == 0) {  // serial inclusive scan: 1024 adds, in a fixed order
-    float c = 0.0f;
-    for (int i = 0; i < (int)blockDim.x; ++i) {
-      c += sh.scan[i];
-      sh.scan[i] = c;
-    }
+  if (lane == 0) {
+    sh.scan[warp] = lane_mass;
+    sh.last_of_warp[warp] = last;
+    if (last >= 0) atomicMax(&sh.last_survivor, last);
   }
-  if (last >= 0) atomicMax(&sh.last_survivor, last);
   __syncthreads();
-  const float total = sh.scan[blockDim.x - 1];
-  const float target = uniforms[blockIdx.x] * total;
-  const float incl = sh.scan[tid];
-  const float excl = tid == 0 ? 0.0f : sh.scan[tid - 1];
-  if (segmass > 0.0f && target < incl) atomicMin(&sh.chosen_thread, tid);
+  // inclusive scan of 32 masses by warp 0, a fixed tree; the first part whose running sum passes the
+  // target is chosen (0x7fffffff: none, rounding); sh.mass[w] = mass before part w
+  auto choose_part = [&](float before, bool first) {
+    float w = sh.scan[lane];
+    const float own = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += t;
+    }
+    if (first && lane == 31) sh.mass_above = uniforms[blockIdx.x] * w;      // the target: uniform x total mass
+    __syncwarp();
+    const float target = sh.mass_above;
+    const unsigned int hit = __ballot_sync(0xffffffffu, own > 0.0f && target < before + w);
+    if (lane == 0) sh.chosen_thread = hit ? __ffs(hit) - 1 : 0x7fffffff;
+    sh.mass[lane] = before + (w - own);
+  };
+  if (warp == 0) choose_part(0.0f, true);
   __syncthreads();
-  if (sh.chosen_thread == tid) {
-    float c = excl;
-    int pick = last;
-    for (int i = beg; i < end; ++i) {
-      const float s = row[i] / temperature;
-      if (order_key(s) >= final_key) {
-        c += expf(s - mx);
-        if (target < c) {
-          pick = i;
-          break;
+  const int chosen_run = sh.chosen_thread;
+  const float target = sh.mass_above;
+  const float before_run = chosen_run != 0x7fffffff ? sh.mass[chosen_run] : 0.0f;
+  __syncthreads();                                   // everyone has read them before they are written again
+  if (chosen_run != 0x7fffffff) {
+    constexpr int GROUPS = 8;                        // 32 warps x 8 groups x 32 elements: runs up to 8,192 elements
+    const int rb = min(vocab, chosen_run * run), re = min(vocab, rb + run);
+    const int sub = ((re - rb + 31) / 32 + 31) & ~31;
+    if (sub <= 32 * GROUPS) {
+      const int sb = min(re, rb + warp * sub), se = min(re, sb + sub);
+      float e[GROUPS];
+      float m = 0.0f;
+#pragma unroll
+      for (int gi = 0; gi < GROUPS; ++gi) {
+        const int i = sb + gi * 32 + lane;
+        e[gi] = 0.0f;
+        if (i < se) {
+          const float sv = row[i] / temperature;
+          if (order_key(sv) >= final_key) e[gi] = expf(sv - mx);
         }
+        m += e[gi];
       }
+      m = warp_sum(m);
+      if (lane == 0) sh.scan[warp] = m;
+      __syncthreads();
+      if (warp == 0) choose_part(before_run, false);
+      __syncthreads();
+      if (sh.chosen_thread == warp) {
+        float c = sh.mass[warp];
+        int pick = -1;
+#pragma unroll
+        for (int gi = 0; gi < GROUPS; ++gi) {
+          float incl = e[gi];
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+          }
+          const unsigned int hit = __ballot_sync(0xffffffffu, e[gi] > 0.0f && target < c + incl);
+          if (hit && pick < 0) pick = sb + gi * 32 + __ffs(hit) - 1;
+          c += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) sh.result = pick;
+      }
+    } else if (warp == chosen_run) {
+      // a run too long for the registers: this warp walks it, 32 elements at a time
+      float c = before_run;
+      int pick = -1;
+      for (int i0 = rb; i0 < re && pick < 0; i0 += 32) {
+        const int i = i0 + lane;
+        float e = 0.0f;
+        if (i < re) {
+          const float sv = row[i] / temperature;
+          if (order_key(sv) >= final_key) e = expf(sv - mx);
+        }
+        float incl = e;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        const unsigned int hit = __ballot_sync(0xffffffffu, e > 0.0f && target < c + incl);
+        if (hit) pick = i0 + __ffs(hit) - 1;
+        c += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) sh.result = pick;
     }
-    sh.result = pick;
   }
   __syncthreads();
-  if (tid == 0) out[blockIdx.x] = sh.result >= 0 ? sh.result : max(sh.last_survivor, 0);
+  // rounding may leave the target just beyond the sums that were formed again: the last survivor of the chosen run, or of the row
+  if (tid == 0)
+    out[blockIdx.x] = sh.result >= 0 ? sh.result
+                                     : (chosen_run != 0x7fffffff ? sh.last_of_warp[chosen_run] : max(sh.last_survivor, 0));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -359,76 +549,6 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, float tempera
 // more candidates than the list holds (flat logits) is left to the kernel above.  Without top_k
 // (top_p alone) the list takes as many whole bins from the top as it holds, pass 2 also sums the
 // row's softmax mass, and a row whose nucleus reaches below the list is left to the kernel above.
-// Scans done by one warp instead of one thread (a thread's serial walk over hundreds of bins in
-// shared memory costs tens of microseconds).  Bins are walked from the highest down.
-//   count form: the bin b with  sum(hist[b+1..]) < want <= sum(hist[b..]);  returns b and the sum above it.
-__device__ __forceinline__ void warp_find_count_bin(const unsigned int* hist, int nbins, int want, int lane, int* bin_out, int* above_out) {
-  const int per = nbins / 32;                       // nbins is a multiple of 32
-  const int hi = nbins - 1 - lane * per;            // this lane's bins: hi, hi-1, ..., hi-per+1
-  int mine = 0;
-  for (int j = 0; j < per; ++j) mine += (int)hist[hi - j];
-  int incl = mine;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  const int excl = incl - mine;                      // count in all bins above this lane's
-  const unsigned int owners = __ballot_sync(0xffffffffu, excl < want && incl >= want);
-  const int owner = owners ? __ffs(owners) - 1 : 31; // nobody: fewer elements than wanted, the lowest bin
-  if (lane == owner) {
-    int cum = excl, b = hi;
-    for (int j = 0; j < per; ++j, --b) {
-      if (cum + (int)hist[b] >= want || j == per - 1) break;
-      cum += (int)hist[b];
-    }
-    *bin_out = b;
-    *above_out = cum;
-  }
-}
-//   mass form (nucleus): among bins with entries, the highest b with  above + sum(mass[b..]) >= target;
-//   if rounding leaves the total below the target, the lowest bin with entries.  Returns b and the mass above it.
-__device__ __forceinline__ void warp_find_mass_bin(const unsigned int* hist, const float* mass, float above, float target, int lane,
-                                                   int* bin_out, float* above_out) {
-  const int hi = 255 - lane * 8;
-  float mine = 0.0f;
-  for (int j = 0; j < 8; ++j) mine += mass[hi - j];
-  float incl = mine;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const float t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  const float excl = above + (incl - mine);
-  // walk this lane's bins exactly as a single thread would, starting from the mass above them
-  int found_b = -1, lowest = -1;
-  float cum = excl, found_cum = 0.0f;
-  for (int j = 0; j < 8; ++j) {
-    const int b = hi - j;
-    if (hist[b] == 0) continue;
-    lowest = b;
-    if (found_b < 0 && cum + mass[b] >= target) {
-      found_b = b;
-      found_cum = cum;
-    }
-    cum += mass[b];
-  }
-  const unsigned int finders = __ballot_sync(0xffffffffu, found_b >= 0);
-  const unsigned int havers = __ballot_sync(0xffffffffu, lowest >= 0);
-  if (finders) {
-    if (lane == __ffs(finders) - 1) {
-      *bin_out = found_b;
-      *above_out = found_cum;
-    }
-  } else if (havers) {
-    const int owner = 31 - __clz(havers);            // the lane with the lowest bins that has entries
-    if (lane == owner) {
-      *bin_out = lowest;
-      *above_out = cum - mass[lowest];
-    }
-  }
-}
-
 #define SAMPLE_LIST 2048
 #define SAMPLE_BINS 4096       // 12 bits
 
@@ -648,7 +768,7 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
       if (warp == 0) {
         const float above = sh.mass_above;
         __syncwarp();
-        warp_find_mass_bin(sh.hist, sh.mass, above, target, lane, &sh.bin, &sh.mass_above);
+        warp_find_mass_bin(sh.hist, sh.mass, 256, above, target, lane, &sh.bin, &sh.mass_above);
         __syncwarp();
         if (lane == 0) sh.prefix = prefix | ((unsigned int)sh.bin << shift);
       }
