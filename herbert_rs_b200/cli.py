@@ -51,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                     help="Make random weights from --config and SEED instead of loading --model")
     ap.add_argument("--config", help="config.json for --random-weights")
+    ap.add_argument("--prefill-chunk-size", type=int, default=None,
+                    help="Prefill chunk size (split long prefills into chunks of N tokens)")
     ap.add_argument("--max-batch", type=int, default=None, help="Most sequences generated together")
     ap.add_argument("--max-context", type=int, default=None, help="Most positions per sequence (default: what the prompts and --max-tokens need)")
     ap.add_argument("--logits-out", help="Write the logits at each prompt's last token to this file (float32, [prompts, vocab])")
@@ -99,7 +101,8 @@ def main(argv: Optional[List[str]] = None) -> int:
         result = hb.generate(
             engine, prompts,
             hb.GenerationOptions(max_tokens=args.max_tokens, stop_token_ids=args.stop_token_id,
-                                 ignore_eos=args.ignore_eos, repeat_check=not args.no_repeat_check, max_batch=width),
+                                 ignore_eos=args.ignore_eos, repeat_check=not args.no_repeat_check, max_batch=width,
+                                 prefill_chunk_size=args.prefill_chunk_size),
             hb.SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, seed=args.seed))
         if tmp is not None:
             tmp.cleanup()

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 from ..errors import CacheError, RequestError
 from ..sampling import SamplingParams, uniform_for
@@ -45,6 +45,7 @@ class GenerationOptions:
     ignore_eos: bool = False
     repeat_check: bool = False
     max_batch: Optional[int] = None   # most sequences of one batch; None: as many as there are slots
+    prefill_chunk_size: Optional[int] = None  # prompts enter in pieces of at most this many tokens (crates/cli/src/main.rs:110-112)
 
 
 @dataclass
@@ -82,13 +83,36 @@ def plan_batches(n_requests: int, max_batch: int) -> List[List[int]]:
     return [list(range(i, min(i + max_batch, n_requests))) for i in range(0, n_requests, max_batch)]
 
 
+def plan_prefill_pieces(lengths: Sequence[int], chunk: Optional[int]) -> List[List[Tuple[int, int, int]]]:
+    """The steps in which prompts of these lengths enter the cache when no sequence may bring more
+    than `chunk` tokens to a step: a list of steps, each a list of (request, begin, end).  Every
+    request's last piece lies in the last step (there its first token is chosen and all go on
+    together), so a shorter prompt starts later; pieces of a request are consecutive steps."""
+    if chunk is None or chunk <= 0 or max(lengths) <= chunk:
+        return [[(i, 0, n) for i, n in enumerate(lengths)]]
+    pieces = [-(-n // chunk) for n in lengths]
+    n_steps = max(pieces)
+    steps: List[List[Tuple[int, int, int]]] = [[] for _ in range(n_steps)]
+    for i, n in enumerate(lengths):
+        first = n_steps - pieces[i]
+        # the first piece takes the remainder, so that the last one is as long as the others' last
+        head = n - (pieces[i] - 1) * chunk
+        begin = 0
+        for j in range(pieces[i]):
+            end = begin + (head if j == 0 else chunk)
+            steps[first + j].append((i, begin, end))
+            begin = end
+    return steps
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
              sampling: Optional[SamplingParams] = None, stop_token_ids: Optional[Sequence[int]] = None
              ) -> GenerationResult:
     """Generate for every prompt; results keep the order of the requests.
 
     `engine` needs: alloc_slot(), free_slot(slot), step_and_choose(entries, params, uniforms) -> ids,
-    and optionally `default_stop_token_ids` and `max_slots`.
+    step(entries, None) when prompts enter in pieces, and optionally `default_stop_token_ids` and
+    `max_slots`.
     finish_reason is one of: "stop_token", "max_tokens", "repetition", "capacity".
     """
     options = options or GenerationOptions()
@@ -128,10 +152,14 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
         try:
             for i in batch_ids:
                 slots[i] = engine.alloc_slot()
-            # all prompts in one step
+            # all prompts in one step, or in pieces whose last ones meet in one step
             t0 = time.perf_counter()
             uni = [uniform_for(seed, i, 0) for i in batch_ids]
-            toks = engine.step_and_choose([(slots[i], prompts[i]) for i in batch_ids], sampling, uni)
+            steps = plan_prefill_pieces([len(prompts[i]) for i in batch_ids], options.prefill_chunk_size)
+            for pieces in steps[:-1]:
+                engine.step([(slots[batch_ids[j]], prompts[batch_ids[j]][b:e]) for j, b, e in pieces], None)
+            toks = engine.step_and_choose([(slots[batch_ids[j]], prompts[batch_ids[j]][b:e]) for j, b, e in steps[-1]],
+                                          sampling, uni)
             stats.prefill_seconds += time.perf_counter() - t0
             stats.prompt_tokens += sum(len(prompts[i]) for i in batch_ids)
             active = []

@@ -2,7 +2,7 @@
 import pytest
 
 import herbert_rs_b200 as hb
-from herbert_rs_b200.engine.generate import detect_repetition_loop, generate, plan_batches
+from herbert_rs_b200.engine.generate import detect_repetition_loop, generate, plan_batches, plan_prefill_pieces
 from herbert_rs_b200.errors import CacheError, RequestError
 
 
@@ -27,6 +27,12 @@ class FakeEngine:
         assert s not in self.free
         self.free.append(s)
         self.free.sort()
+
+    def step(self, entries, want):
+        assert want is None
+        for s, t in entries:
+            self.lengths[s] += len(t)
+        self.steps.append([(s, list(t)) for s, t in entries])
 
     def step_and_choose(self, entries, params, uniforms):
         for s, t in entries:
@@ -128,3 +134,35 @@ def test_repetition_detector():
             return [7 for _ in entries]
     r = generate(Looping(), [[1]], hb.GenerationOptions(max_tokens=100, repeat_check=True), hb.SamplingParams(temperature=0.0))
     assert r.finish_reasons == ["repetition"] and len(r.tokens[0]) == 18
+
+
+@pytest.mark.parametrize("lengths,chunk", [([9, 1, 30, 4, 17], 5), ([10, 10], 5), ([3, 2], 8), ([33], 32), ([7, 64, 1], 1)])
+def test_prompts_in_pieces_meet_in_the_last_step(lengths, chunk):
+    steps = plan_prefill_pieces(lengths, chunk)
+    assert sorted(i for i, _, _ in steps[-1]) == list(range(len(lengths)))      # everyone's last piece
+    seen = {i: 0 for i in range(len(lengths))}
+    active_since = {}
+    for j, pieces in enumerate(steps):
+        assert len({i for i, _, _ in pieces}) == len(pieces)                     # a request once per step
+        for i, b, e in pieces:
+            assert b == seen[i] and 0 < e - b <= max(chunk, 1) and e <= lengths[i]   # in order, no gap, no piece too long
+            seen[i] = e
+            active_since.setdefault(i, j)
+        for i, first in active_since.items():
+            assert any(k == i for k, _, _ in pieces)                             # once begun, in every step to the end
+    assert seen == {i: n for i, n in enumerate(lengths)}
+    assert len(steps) == max(-(-n // chunk) for n in lengths)
+
+
+def test_generation_with_a_prefill_chunk_size_steps_the_pieces_then_decodes():
+    e = FakeEngine()
+    r = generate(e, [[1, 2, 3, 4, 5, 6, 7], [10], [20, 21, 22]],
+                 hb.GenerationOptions(max_tokens=2, prefill_chunk_size=3), hb.SamplingParams(temperature=0.0))
+    assert e.steps[0] == [(0, [1])]                                  # the remainder first
+    assert e.steps[1] == [(0, [2, 3, 4])]
+    assert e.steps[2] == [(0, [5, 6, 7]), (1, [10]), (2, [20, 21, 22])]
+    assert e.steps[3] == [(0, [8]), (1, [11]), (2, [23])]
+    assert r.tokens == [[8, 9], [11, 12], [23, 24]] and r.stats.prompt_tokens == 11
+    whole = generate(FakeEngine(), [[1, 2, 3, 4, 5, 6, 7], [10], [20, 21, 22]],
+                     hb.GenerationOptions(max_tokens=2), hb.SamplingParams(temperature=0.0))
+    assert whole.tokens == r.tokens

@@ -222,6 +222,30 @@ def test_greedy_generation_through_the_entry_point(model_dirs, plain, dtype):
     assert eng.cache.slots.free_count == eng.cache.num_slots
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_generation_with_prompts_in_pieces(model_dirs, plain, dtype):
+    """--prefill-chunk-size: prompts enter the cache five tokens at a time, shorter ones later, and
+    the tokens are those of whole prompts (float32: identical; bfloat16: the plain model's best)."""
+    eng = engine_for(model_dirs["A"], dtype)
+    rng = np.random.default_rng(25)
+    prompts = [random_ids(rng, 256, n) for n in (23, 2, 11, 5)]
+    opt = dict(max_tokens=6, ignore_eos=True)
+    whole = hb.generate(eng, prompts, hb.GenerationOptions(**opt), hb.SamplingParams(temperature=0.0))
+    cut = hb.generate(eng, prompts, hb.GenerationOptions(prefill_chunk_size=5, **opt), hb.SamplingParams(temperature=0.0))
+    margin = {"float32": 1e-4, "bfloat16": 4e-2}[dtype]
+    for p, got in zip(prompts, cut.tokens):
+        ids = list(p)
+        for tok in got:
+            ref = plain["A"].logits(ids)[-1].numpy()
+            assert ref.max() - ref[tok] <= margin
+            ids.append(tok)
+    if dtype == "float32":
+        assert cut.tokens == whole.tokens
+    assert cut.stats.prompt_tokens == whole.stats.prompt_tokens == 41
+    eng.cache.check()
+    assert eng.cache.slots.free_count == eng.cache.num_slots
+
+
 def test_sampled_generation_is_reproducible_and_batch_independent(model_dirs):
     eng = engine_for(model_dirs["B"], "float32")
     rng = np.random.default_rng(16)
