@@ -321,6 +321,29 @@ def test_sample_with_a_small_top_k_against_a_large_vocabulary(t, k, p, listed):
         assert host_survivors(tied, params)[0].sum() == k + 3
 
 
+@pytest.mark.parametrize("V,t,k,p", [(300001, 1.0, 0, 1.0), (300001, 0.5, 0, 0.8), (300001, 0.8, 600, 1.0),
+                                     (4097, 1.0, 0, 1.0), (33, 1.3, 0, 0.7), (8192, 1.0, 0, 0.9)])
+def test_sample_general_kernel_at_other_vocabulary_sizes(V, t, k, p):
+    """The general kernel's draw in two levels: a vocabulary whose runs are too long for the
+    registers (one warp walks the chosen run) and is no multiple of 4, one that leaves most warps
+    an empty run, and a power of two; survivors and intervals as the host twin has them."""
+    rng = np.random.default_rng(V + k)
+    R = 256
+    logits = (rng.standard_normal(V) * 2.0).astype(np.float32)
+    us = ((np.arange(R) + 0.5) / R).astype(np.float32)
+    rows = dev(torch.from_numpy(logits)).expand(R, V).contiguous()
+    out = torch.full((R,), -7, dtype=torch.int32, device="cuda")
+    ops.sample(rows, t, k, p, dev(torch.from_numpy(us)), out)
+    got = out.cpu().numpy()
+    params = SamplingParams(t, k, p)
+    keep, e = host_survivors(logits, params)
+    assert keep[got].all()
+    c = np.cumsum(e.astype(np.float64)); c /= c[-1]
+    lo = np.concatenate([[0.0], c[:-1]])
+    assert (us >= lo[got] - 1e-4).all() and (us <= c[got] + 1e-4).all()
+    assert (np.diff(got[np.argsort(us, kind="stable")]) >= 0).all()      # a larger uniform never draws an earlier token
+
+
 def test_sample_refuses_bad_options():
     x = dev(torch.zeros(1, 8)); u = dev(torch.zeros(1)); o = torch.empty(1, dtype=torch.int32, device="cuda")
     with pytest.raises(BackendError, match="temperature must be > 0"):
