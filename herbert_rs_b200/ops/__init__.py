@@ -419,18 +419,21 @@ def _stream_uncut(M: int, N: int, K: int) -> bool:
 
 
 def _decode_gemm(a, w):
-    """Which kernel multiplies at most 64 activation rows.  Measured at Qwen3-8B shapes: the
-    mma.sync kernel wins up to 16 rows and on matrices of few rows (o, down: 32 tiles of 128 rows
-    cannot fill the GPU without cutting K deep); from 17 rows on its activation reads through L1
-    dominate and the TMA/tcgen05 kernel is 1.3-3x faster on matrices of at least 48 row tiles;
-    from 33 rows on the widest matrices (gate/up) go fastest through the prefill kernel, whose 96
-    tiles of 256 weight rows stream at 4.6 TB/s (44 against 57 us)."""
+    """Which kernel multiplies at most 64 activation rows.  Measured at Qwen3-8B shapes (microseconds
+    at 17 / 32 / 64 rows; skinny, streaming tcgen05, prefill kernel with tiles of 128 weight rows):
+    q/k/v 19 / 21 / 31, 22 / 22 / 27, 18 / 18 / 18; o 12 / 12 / 18, 26 / 29 / 41, 20 / 21 / 21;
+    gate/up 58 / 65 / 93, 44 / 47 / 55, 38 / 38 / 39; down 28 / 29 / 42, 53 / 59 / 76, 34 / 33 / 34.
+    Up to 16 rows the mma.sync kernel streams the weights at the memory's rate; beyond that every CTA
+    of 16 weight rows reads the whole activation matrix again and the prefill kernel wins wherever
+    the matrix has enough rows to fill the GPU with tiles, or enough columns to be cut into runs."""
     if DECODE_GEMM == "stream":
         return gemm_stream
-    if DECODE_GEMM == "auto" and a.shape[0] > 32 and 16384 <= w.shape[0] < 65536 and _tcgen05_ok(a, w):
+    M, N, K = a.shape[0], w.shape[0], a.shape[1]
+    if DECODE_GEMM == "auto" and M > 16 and _tcgen05_ok(a, w) and N < 65536 and \
+            (N >= 6144 or (M > 32 and N * K >= 32 * 1024 * 1024)):
         return gemm_tcgen05
-    if DECODE_GEMM == "auto" and a.shape[0] > 16 and (w.shape[0] >= 6144 or _stream_uncut(a.shape[0], w.shape[0], a.shape[1])):
-        return gemm_stream
+    if DECODE_GEMM == "auto" and M > 16 and (N >= 65536 or _stream_uncut(M, N, K)):
+        return gemm_stream            # the head; matrices so small that the streaming kernel need not cut K
     return gemm_skinny
 
 

@@ -53,15 +53,17 @@ def _shapes(a):
 
 def _gemm(a, kernels, graph):
     M = a.rows
-    for name, N, K, epi in _shapes(a):
-        ws = [torch.randn(N, K, device="cuda").bfloat16() for _ in range(a.layers)]
+    shapes = _shapes(a) + ([("head", a.vocab, a.hidden, ops.EPI_STORE_F32)] if a.head else [])
+    for name, N, K, epi in shapes:
+        copies = 2 if name == "head" else a.layers          # two heads are already ten times L2
+        ws = [torch.randn(N, K, device="cuda").bfloat16() for _ in range(copies)]
         x = torch.randn(M, K, device="cuda").bfloat16()
-        c = (torch.zeros(M, N, device="cuda") if epi == ops.EPI_RESIDUAL
+        c = (torch.zeros(M, N, device="cuda") if epi in (ops.EPI_RESIDUAL, ops.EPI_STORE_F32)
              else torch.empty(M, N // 2 if epi == ops.EPI_SWIGLU else N, device="cuda", dtype=torch.bfloat16))
         line = f"{name:8s} N={N:6d} K={K:6d} rows={M:5d}"
         for kname in kernels:
             fn = getattr(ops, kname)
-            us = _timed(lambda: [fn(x, w, c, epi) for w in ws], a.reps, a.layers, graph)
+            us = _timed(lambda: [fn(x, w, c, epi) for w in ws], a.reps, copies, graph)
             line += f"   {kname} {us:7.1f} us {N * K * 2 / us / 1e3:6.0f} GB/s {2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s"
         print(line, flush=True)
         del ws
@@ -143,6 +145,7 @@ def main(argv=None) -> None:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--head", action="store_true", help="decode-gemm / prefill-gemm: also the output head (vocab x hidden)")
     ap.add_argument("--spread", type=float, default=3.0, help="standard deviation of the logits of `sampling`")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
