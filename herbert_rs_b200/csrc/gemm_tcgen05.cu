@@ -489,6 +489,23 @@ static int tg_dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, in
   HB_FAIL(2, "gemm_tcgen05: unknown epilogue %d", epi);
 }
 
+// Output columns per tile.  Tiles of 256 weight rows feed the tensor cores best; when there are too
+// few of them to keep half the SMs busy (decode batches, short prompts, matrices of few rows),
+// tiles of 128 give twice the tiles to spread and, where tiles are shared, pieces of half the size.
+// Measured at the 8B sizes: 64 rows q/k/v 27.6 -> 18.1 us, down 52.3 -> 33.9; 256 rows o 41.8 ->
+// 26.8, down 70 -> 47; 512 rows o 41 -> 30, down 85 -> 67; with more tiles the wide ones win
+// (512 rows gate/up 89 against 108).
+static int tg_tile_cols(int M, int N) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  if (N <= 128) return 128;
+  return ceil_div(M, TG_BM) * ceil_div(N, 256) * 2 > sms ? 256 : 128;
+}
+
 // Gives the products a workspace for tiles shared between CTAs: `floats` must hold
 // hb_gemm_tcgen05_workspace_floats(ctas) floats and `counters` ctas ints, zero, for ctas >= the
 // number of SMs.  Without it (null) every tile is computed by one CTA.  Calls that use the same
@@ -511,10 +528,7 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   HB_REQUIRE(epi != HB_EPI_SWIGLU || N % 16 == 0, "gemm_tcgen05: SwiGLU columns come in groups of 16, N=%d", N);
   HB_REQUIRE(error_flag != nullptr, "gemm_tcgen05: an error flag is required");
   CUtensorMap ma, mw;
-  // Up to 64 rows (a decode batch) the product is a stream of weights: tiles of 128 weight rows give
-  // twice the tiles to spread over the SMs and pieces of half the size where tiles are shared
-  // (64 rows: q/k/v 27.6 -> 18.1 us, down 52.3 -> 33.9 us).
-  const int BN = (N > 128 && M > 64) ? 256 : 128;
+  const int BN = tg_tile_cols(M, N);
   int rc = make_map(&ma, A, M, K, lda, TG_BM);
   if (rc) return rc;
   rc = make_map(&mw, W, N, K, ldw, BN);
@@ -526,13 +540,13 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
 }
 
 // Tiles of output columns, i.e. rows of out_sumsq, of a product with N output columns.
-extern "C" int hb_gemm_tcgen05_norm_parts(int N) { return ceil_div(N, N > 128 ? 256 : 128); }
+extern "C" int hb_gemm_tcgen05_norm_parts(int M, int N) { return ceil_div(N, tg_tile_cols(M, N)); }
 
 // The same product with a shared norm on either side (any M):
 //   in_sumsq != null: A holds x * w of a norm over K; results are multiplied by 1 / rms of the rows,
 //     rms^2 = sum_i in_sumsq[i * in_stride + row] / K + in_eps, i < in_parts;
 //   out_w != null (epi HB_EPI_RESIDUAL): besides C += ..., out_xw = C * out_w (bfloat16) and
-//     out_sumsq[hb_gemm_tcgen05_norm_parts(N)][out_stride] = partial sums of C^2 (out_stride >= M).
+//     out_sumsq[hb_gemm_tcgen05_norm_parts(M, N)][out_stride] = partial sums of C^2 (out_stride >= M).
 extern "C" int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M,
                                          int N, int K, int epi, const float* in_sumsq, int in_parts, int in_stride,
                                          float in_eps, const float* out_w, void* out_xw, int out_ld,
@@ -547,7 +561,7 @@ extern "C" int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, 
              "gemm_tcgen05_norm: the next norm's input is written by the residual epilogue and needs both outputs, row stride >= M");
   HB_REQUIRE(out_w == nullptr || (((uintptr_t)out_w & 15) == 0), "gemm_tcgen05_norm: the norm weight must be 16-byte aligned");
   CUtensorMap ma, mw;
-  const int BN = N > 128 ? 256 : 128;
+  const int BN = tg_tile_cols(M, N);
   int rc = make_map(&ma, A, M, K, lda, TG_BM);
   if (rc) return rc;
   rc = make_map(&mw, W, N, K, ldw, BN);

@@ -39,7 +39,7 @@ _SIGS = {
     "hb_finish_norm": [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
     "hb_gemm_tcgen05_norm_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                   c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
-    "hb_gemm_tcgen05_norm_parts": [c_int],
+    "hb_gemm_tcgen05_norm_parts": [c_int, c_int],
     "hb_gemm_tcgen05_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
@@ -364,7 +364,7 @@ def gemm_tcgen05_norm(a, w, c, epilogue=EPI_STORE, next_norm=None, scratch=None)
         _check(nw, torch.float32, "next norm weight")
         if epilogue != EPI_RESIDUAL or nw.numel() != N:
             raise BackendError("gemm_tcgen05_norm: the next norm needs the residual epilogue and a weight per output column")
-        parts = int(_fn("hb_gemm_tcgen05_norm_parts")(N))
+        parts = int(_fn("hb_gemm_tcgen05_norm_parts")(M, N))
         out = PendingNorm(scratch((M, N), torch.bfloat16), scratch((parts, (M + 3) // 4 * 4), torch.float32), parts, eps)
     _tcgen05_workspace(c.device)
     _run("hb_gemm_tcgen05_norm_bf16", x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0),
