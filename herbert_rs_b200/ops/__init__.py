@@ -246,9 +246,9 @@ class PendingNorm:
 
 def shared_norm_ok(n_rows: int, dtype, dim: int) -> bool:
     """Whether products of `n_rows` activation rows can carry a norm over `dim` between them: the
-    kernels for at most 16 rows and the tensor-memory kernel for more than 64 can."""
-    return (SHARED_NORM and dtype == torch.bfloat16 and dim % 8 == 0
-            and (n_rows <= SHARED_NORM_MAX_ROWS or n_rows > SKINNY_MAX_ROWS))
+    mma.sync kernel can for at most 16 rows, the tensor-memory kernel for any number; between 17
+    and 64 rows a product that goes through another kernel leaves the norm to a kernel of its own."""
+    return SHARED_NORM and dtype == torch.bfloat16 and dim % 8 == 0
 
 
 def finish_norm(p: PendingNorm, out: torch.Tensor) -> None:
@@ -464,7 +464,8 @@ def gemm(a, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPI_STORE, next_no
             and shared_norm_ok(x.shape[0], x.dtype, w.shape[0] if next_norm is not None else 8):
         if x.shape[0] <= SHARED_NORM_MAX_ROWS and _skinny_ok(x, w):
             return gemm_skinny_norm(a, w, c, epilogue, next_norm, scratch)
-        if x.shape[0] > SKINNY_MAX_ROWS and _tcgen05_ok(x, w) and (next_norm is None or next_norm[0].data_ptr() % 16 == 0):
+        if (x.shape[0] > SKINNY_MAX_ROWS or (_skinny_ok(x, w) and _decode_gemm(x, w) is gemm_tcgen05)) \
+                and _tcgen05_ok(x, w) and (next_norm is None or next_norm[0].data_ptr() % 16 == 0):
             return gemm_tcgen05_norm(a, w, c, epilogue, next_norm, scratch)
     a = _plain_input(a, scratch)
     if _skinny_ok(a, w):
@@ -482,7 +483,8 @@ def gemm_swiglu(a, wgu: torch.Tensor, out: torch.Tensor, interleave: int, scratc
         if interleave == 8 and _skinny_ok(a.xw, wgu) and a.xw.shape[0] <= SHARED_NORM_MAX_ROWS:
             gemm_skinny_norm(a, wgu, out, EPI_SWIGLU)
             return
-        if interleave == 8 and a.xw.shape[0] > SKINNY_MAX_ROWS and _tcgen05_ok(a.xw, wgu):
+        if interleave == 8 and _tcgen05_ok(a.xw, wgu) and \
+                (a.xw.shape[0] > SKINNY_MAX_ROWS or (_skinny_ok(a.xw, wgu) and _decode_gemm(a.xw, wgu) is gemm_tcgen05)):
             gemm_tcgen05_norm(a, wgu, out, EPI_SWIGLU)
             return
         a = _plain_input(a, scratch)

@@ -70,7 +70,7 @@ def _gemm(a, kernels, graph):
 
 
 def decode_gemm(a):
-    _gemm(a, [k for k in ("gemm_skinny", "gemm_stream", "gemm_tcgen05") if k != "gemm_skinny" or a.rows <= 64], True)
+    _gemm(a, [k for k in ("gemm_skinny", "gemm_stream", "gemm_tcgen05") if k == "gemm_tcgen05" or a.rows <= 64], True)
 
 
 def prefill_gemm(a):

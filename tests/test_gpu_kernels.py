@@ -378,12 +378,14 @@ def test_gemm_skinny_every_epilogue(M, N, K):
         close(out, gate / (1 + torch.exp(-gate)) * up, torch.bfloat16)
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 65, 200, 333])
-@pytest.mark.parametrize("H,N2,eps", [(96, 64, 1e-5), (304, 16 * 1024, 1e-6), (1000, 48, 3e-3)])
+@pytest.mark.parametrize("M,H,N2,eps", [(M, H, N2, eps) for M in (1, 5, 8, 13, 16, 65, 200, 333)
+                                        for H, N2, eps in ((96, 64, 1e-5), (304, 16 * 1024, 1e-6), (1000, 48, 3e-3))]
+                         + [(17, 6144, 6144, 1e-6), (40, 6160, 6144, 1e-5), (64, 6144, 16 * 1024, 1e-6)])
 def test_products_with_a_norm_shared_between_them(M, H, N2, eps):
     """First product: x += a w1^T, and it begins RMSNorm(x; nw, eps).  Second product: finishes the
     norm and multiplies with w2 (store, SwiGLU and residual epilogues).  Up to 16 rows the decode
-    kernel does it, beyond 64 the tensor-memory kernel.  Reference: the norm as a
+    kernel does it, beyond 64 the tensor-memory kernel, and between them the tensor-memory kernel
+    where it is the one that multiplies such a matrix (6,144 weight rows and more).  Reference: the norm as a
     step of its own in double precision, rounded to bfloat16 where the engine's plain path rounds."""
     torch.manual_seed(31)
     K1 = 72
