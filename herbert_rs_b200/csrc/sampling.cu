@@ -869,8 +869,8 @@ sample_topk_kernel(const float* __restrict__ logits, int ld, int vocab, float te
   if (tid == 0) out[blockIdx.x] = sh.result >= 0 ? sh.result : (ns > 0 ? sidx[ns - 1] : 0);
 }
 
-// overflow (optional): n_rows ints of scratch; with it, a small top_k against a large vocabulary
-// takes the two-pass list kernel, and the general kernel only runs for rows the list could not hold.
+// overflow (optional): n_rows ints of scratch; with it, a small top_k (or top_p alone) against a large
+// vocabulary takes the two-pass list kernel, and the general kernel only runs for rows the list could not hold.
 extern "C" int hb_sample(const float* logits, int ld, int n_rows, int vocab, float temperature, int top_k,
                          float top_p, const float* uniforms, int* out, int* overflow, void* stream) {
   HB_REQUIRE(n_rows > 0 && vocab > 0 && ld >= vocab, "sample: bad sizes");
