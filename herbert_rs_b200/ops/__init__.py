@@ -404,36 +404,25 @@ def _tcgen05_ok(a, w) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-_stream_plan_fn = None
-
-
-def _stream_uncut(M: int, N: int, K: int) -> bool:
-    """True if the streaming tcgen05 kernel would run this product without cutting K (enough tiles
-    of 128 weight rows to fill the GPU), the case in which it has no reduction to pay for."""
-    global _stream_plan_fn
-    if _stream_plan_fn is None:
-        _stream_plan_fn = _libmod.load().hb_gemm_stream_scratch_floats
-        _stream_plan_fn.argtypes = [c_int, c_int, c_int]
-        _stream_plan_fn.restype = ctypes.c_longlong
-    return _stream_plan_fn(M, N, K) == 0
-
-
 def _decode_gemm(a, w):
-    """Which kernel multiplies at most 64 activation rows.  Measured at Qwen3-8B shapes (microseconds
-    at 17 / 32 / 64 rows; skinny, streaming tcgen05, prefill kernel with tiles of 128 weight rows):
-    q/k/v 19 / 21 / 31, 22 / 22 / 27, 18 / 18 / 18; o 12 / 12 / 18, 26 / 29 / 41, 20 / 21 / 21;
-    gate/up 58 / 65 / 93, 44 / 47 / 55, 38 / 38 / 39; down 28 / 29 / 42, 53 / 59 / 76, 34 / 33 / 34.
+    """Which kernel multiplies at most 64 activation rows.  Measured (microseconds at 17 / 32 / 64
+    rows; mma.sync kernel, streaming tcgen05 kernel, prefill kernel with tiles of 128 weight rows) at
+    Qwen3-8B shapes: q/k/v 19 / 21 / 31, 22 / 22 / 27, 18 / 18 / 18; o 12 / 12 / 18, 26 / 29 / 41,
+    20 / 21 / 21; gate/up 58 / 65 / 93, 44 / 47 / 55, 38 / 38 / 40; down 28 / 29 / 42, 53 / 59 / 76,
+    34 / 33 / 34; at 32B shapes the prefill kernel wins all four from 32 rows on (down 60 against 103
+    and 97), at 0.6B shapes (at most 6 M elements) the mma.sync kernel wins all four.
     Up to 16 rows the mma.sync kernel streams the weights at the memory's rate; beyond that every CTA
-    of 16 weight rows reads the whole activation matrix again and the prefill kernel wins wherever
-    the matrix has enough rows to fill the GPU with tiles, or enough columns to be cut into runs."""
+    of 16 weight rows reads the whole activation matrix again, and the prefill kernel wins wherever
+    the matrix is large enough to pay for its start and end.  The streaming kernel keeps the head."""
     if DECODE_GEMM == "stream":
         return gemm_stream
     M, N, K = a.shape[0], w.shape[0], a.shape[1]
-    if DECODE_GEMM == "auto" and M > 16 and _tcgen05_ok(a, w) and N < 65536 and \
-            (N >= 6144 or (M > 32 and N * K >= 32 * 1024 * 1024)):
-        return gemm_tcgen05
-    if DECODE_GEMM == "auto" and M > 16 and (N >= 65536 or _stream_uncut(M, N, K)):
-        return gemm_stream            # the head; matrices so small that the streaming kernel need not cut K
+    if DECODE_GEMM == "auto" and M > 16:
+        elements = N * K
+        if N >= 65536:
+            return gemm_stream
+        if _tcgen05_ok(a, w) and elements >= 20 * 1024 * 1024 and (M > 32 or N >= 6144 or elements >= 64 * 1024 * 1024):
+            return gemm_tcgen05
     return gemm_skinny
 
 

@@ -388,9 +388,9 @@ def test_products_with_a_norm_shared_between_them(M, H, N2, eps):
     where it is the one that multiplies such a matrix (6,144 weight rows and more).  Reference: the norm as a
     step of its own in double precision, rounded to bfloat16 where the engine's plain path rounds."""
     torch.manual_seed(31)
-    K1 = 72
+    K1 = 4096 if 16 < M <= 64 else 72       # between 17 and 64 rows only a large matrix goes through the tensor-memory kernel
     a = torch.randn(M, K1).to(torch.bfloat16)
-    w1 = (torch.randn(H, K1) * 0.3).to(torch.bfloat16)
+    w1 = (torch.randn(H, K1) * 0.3 * (72 / K1) ** 0.5).to(torch.bfloat16)
     x0 = torch.randn(M, H) * 3.0
     x0[0] *= 40.0                                             # rows of very different size: one factor per row
     nw = 1.0 + 0.1 * torch.randn(H)
