@@ -38,3 +38,21 @@ def test_every_cutting_at_production_widths(wide, dtype):
         assert_close(g, ref, dtype, "wide batched")
     from herbert_rs_b200 import ops
     ops.check_kernel_errors()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_decode_batch_of_forty_at_production_widths(wide, dtype):
+    """Between 17 and 64 sequences the decode step's large products go through the tensor-memory
+    kernel (tiles of 128 weight rows, shared norms), the small one through the mma.sync kernel:
+    forty unequal prompts in one step, then one token each, against the plain implementation."""
+    d, plain = wide
+    rng = np.random.default_rng(4)
+    lens = [int(n) for n in rng.integers(1, 14, 40)]
+    reqs = [random_ids(rng, 20040, n + 5) for n in lens]
+    eng = engine_for(d, dtype, max_tokens=48 * 64, max_slots=48)
+    got = replay_batches(eng, reqs, lens, [list(range(40))])
+    for i in (0, 7, 19, 39):
+        ref = plain.logits(reqs[i], torch.float32).double().numpy()
+        assert_close(got[i], ref, dtype, f"request {i} of forty")
+    from herbert_rs_b200 import ops
+    ops.check_kernel_errors()
