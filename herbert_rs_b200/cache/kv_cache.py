@@ -169,9 +169,14 @@ class SequenceCache:
 
     # -- pages -----------------------------------------------------------------------------
     def pages_needed(self, slot: int, n_new: int) -> int:
-        have = len(self._pages[slot][0]) if self.kv_needs else 0
+        """Pages that `n_new` more positions of `slot` take from the fullest-used pool: the most any
+        key/value group needs (groups differ once a window has given pages back)."""
         want = -(-(self.lengths[slot] + n_new) // self.page_size)
-        return max(0, want - have)
+        return max((max(0, want - len(self._pages[slot][g])) for g in range(len(self.kv_needs))), default=0)
+
+    def free_pages(self) -> int:
+        """Pages free in the group with the fewest free pages."""
+        return min((p.free_count for p in self.pools), default=self.num_pages)
 
     def reserve(self, requests: Sequence[tuple]) -> None:
         """Make room for n_new more positions per (slot, n_new); all or nothing."""

@@ -53,6 +53,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--config", help="config.json for --random-weights")
     ap.add_argument("--prefill-chunk-size", type=int, default=None,
                     help="Prefill chunk size (split long prefills into chunks of N tokens)")
+    ap.add_argument("--round-weights-to-bf16", action="store_true",
+                    help="Round every float tensor (norm weights too) to bfloat16 while loading, as the reference does")
     ap.add_argument("--max-batch", type=int, default=None, help="Most sequences generated together")
     ap.add_argument("--max-context", type=int, default=None, help="Most positions per sequence (default: what the prompts and --max-tokens need)")
     ap.add_argument("--logits-out", help="Write the logits at each prompt's last token to this file (float32, [prompts, vocab])")
@@ -89,9 +91,10 @@ def main(argv: Optional[List[str]] = None) -> int:
         if args.max_context is not None:
             per_seq = min(per_seq, args.max_context)
         width = min(len(prompts), args.max_batch or len(prompts))
-        pages = -(-per_seq // 64) * width
-        engine = hb.Engine.from_folder(model_dir, dtype=backend.dtype, max_tokens=pages * 64, max_slots=width,
-                                       max_seq_len=args.max_context)
+        ps = hb.Engine.default_page_size()
+        engine = hb.Engine.from_folder(model_dir, dtype=backend.dtype, max_tokens=hb.Engine.pages_for(per_seq, width) * ps,
+                                       max_slots=width, max_seq_len=args.max_context,
+                                       round_weights_to_bf16=args.round_weights_to_bf16)
         if args.logits_out:
             slots = [engine.alloc_slot() for _ in prompts[:width]]
             logits = engine.step(list(zip(slots, prompts[:width])), "last").cpu().numpy()

@@ -112,7 +112,12 @@ class ModelSpec:
     embed_name: str = "model.embed_tokens.weight"
     final_norm_name: str = "model.norm.weight"
     head_name: str = "lm_head.weight"
-    extra: dict = field(default_factory=dict)
+    # How many numbers place a token: 1 for a position in a sequence.  An encoding that needs
+    # more (rows and columns of an image, say) raises this; the step then carries that many position
+    # rows per token, which the caller may give per sequence (Engine.step(..., positions=...)) and
+    # which default to the token's index in its sequence in every component.
+    position_components: int = 1
+    extra: dict = field(default_factory=dict)     # free for an architecture's own model class
 
 
 def identity_schedule(n: int) -> tuple:

@@ -6,7 +6,8 @@ disturb exists.  Everything the kernels need is a handful of int32 arrays, built
 written into one pinned buffer and copied to the device with one transfer:
 
   token_ids[T]   the ids                   tok_seq[T]   index of the token's sequence in this step
-  tok_pos[T]     position in its sequence  seq_slot[B]  cache slot of each sequence
+  positions[C,T] position in its sequence  seq_slot[B]  cache slot of each sequence
+                 (C components; tok_pos = component 0)
   seq_start[B+1] first row of each sequence seq_pos0[B] cached length before this step
   seq_len[B]     length after this step    want_rows[R] rows whose logits are asked for
   pages[g][B,P]  physical page of each logical page, per key/value group
@@ -14,7 +15,10 @@ written into one pinned buffer and copied to the device with one transfer:
 
 The reference's step has one sequence and takes its position from the cache length
 (crates/backends/backend_common/src/generic_model.rs:530; linear_ops.rs:374: start_pos + t);
-the same rule gives tok_pos here, per sequence.
+the same rule gives tok_pos here, per sequence.  A model whose position encoding takes several
+numbers per token (`ModelSpec.position_components`) gets as many rows; each defaults to the same
+rule and can be given by the caller instead.  Component 0 is always the index in the sequence: it
+is what the cache and the causal mask go by.
 """
 
 from __future__ import annotations
@@ -39,14 +43,15 @@ class StepLayout:
     R: int
     G: int
     P: int
+    C: int = 1
     offsets: dict = field(default_factory=dict)
     total: int = 0
 
     @staticmethod
-    def make(T: int, B: int, R: int, G: int, P: int) -> "StepLayout":
-        lay = StepLayout(T, B, R, G, P)
+    def make(T: int, B: int, R: int, G: int, P: int, C: int = 1) -> "StepLayout":
+        lay = StepLayout(T, B, R, G, P, C)
         o = 0
-        for name, n in (("token_ids", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B + 1),
+        for name, n in (("token_ids", T), ("tok_seq", T), ("tok_pos", C * _align(T)), ("seq_slot", B), ("seq_start", B + 1),
                         ("seq_pos0", B), ("seq_len", B), ("want_rows", max(R, 1)), ("uniforms", B)):
             lay.offsets[name] = o
             o += _align(n)
@@ -62,7 +67,7 @@ class StepBatch:
 
     def __init__(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], pos0: Sequence[int],
                  want: Sequence[Sequence[int]], num_kv_groups: int, pages_width: Optional[int] = None,
-                 page_size: int = 64):
+                 page_size: int = 64, position_components: int = 1, positions: Optional[Sequence] = None):
         self.slots = list(slots)
         self.q_lens = [len(t) for t in tokens]
         self.pos0 = list(pos0)
@@ -83,8 +88,11 @@ class StepBatch:
                 rows.append(int(starts[b]) + int(i))
         self.want_rows_host = rows
         self.n_want = len(rows)
-        self.layout = StepLayout.make(self.n_tokens, self.n_seqs, self.n_want, num_kv_groups, self.pages_width)
+        self.n_components = int(position_components)
+        self.layout = StepLayout.make(self.n_tokens, self.n_seqs, self.n_want, num_kv_groups, self.pages_width,
+                                      self.n_components)
         self._tokens = tokens
+        self._positions = positions      # per sequence: [len, C] (or [len] when C == 1), or None
         self.host: Optional[np.ndarray] = None
         self.dev: Optional[torch.Tensor] = None
         self.pages: List[torch.Tensor] = []
@@ -100,7 +108,14 @@ class StepBatch:
         buf[o["tok_seq"]:o["tok_seq"] + T] = seq_idx
         pos0 = np.asarray(self.pos0, dtype=np.int32)
         within = np.arange(T, dtype=np.int32) - np.repeat(self.seq_start_host[:-1], reps)
-        buf[o["tok_pos"]:o["tok_pos"] + T] = pos0[seq_idx] + within
+        own = pos0[seq_idx] + within
+        row = _align(T)
+        for c in range(self.n_components):
+            at = o["tok_pos"] + c * row
+            buf[at:at + T] = own
+            if c > 0 and self._positions is not None:
+                given = np.concatenate([np.asarray(p, dtype=np.int64).reshape(len(p), -1)[:, c] for p in self._positions])
+                buf[at:at + T] = given
         buf[o["seq_slot"]:o["seq_slot"] + B] = np.asarray(self.slots, dtype=np.int32)
         buf[o["seq_start"]:o["seq_start"] + B + 1] = self.seq_start_host
         buf[o["seq_pos0"]:o["seq_pos0"] + B] = pos0
@@ -120,7 +135,9 @@ class StepBatch:
         self.dev = dev
         self.token_ids = dev[o["token_ids"]:o["token_ids"] + T]
         self.tok_seq = dev[o["tok_seq"]:o["tok_seq"] + T]
-        self.tok_pos = dev[o["tok_pos"]:o["tok_pos"] + T]
+        row = _align(T)
+        self.positions = dev[o["tok_pos"]:o["tok_pos"] + self.n_components * row].view(self.n_components, row)[:, :T]
+        self.tok_pos = self.positions[0]
         self.seq_slot = dev[o["seq_slot"]:o["seq_slot"] + B]
         self.seq_start = dev[o["seq_start"]:o["seq_start"] + B + 1]
         self.seq_pos0 = dev[o["seq_pos0"]:o["seq_pos0"] + B]

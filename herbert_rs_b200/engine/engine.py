@@ -68,10 +68,31 @@ class Engine:
     @classmethod
     def from_folder(cls, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", max_tokens: int = 4096,
                     max_slots: Optional[int] = None, max_seq_len: Optional[int] = None, device="cuda",
-                    page_size: int = 64, use_graphs: bool = True) -> "Engine":
+                    page_size: Optional[int] = None, use_graphs: bool = True,
+                    round_weights_to_bf16: bool = False) -> "Engine":
+        """An engine over the model folder.  `max_tokens` sizes the cache: the most positions that
+        live sequences hold at any time, each sequence's count rounded up to whole pages
+        (`pages_for`).  `round_weights_to_bf16` rounds every float tensor to bfloat16 while loading,
+        norm weights included, as the reference does with a checkpoint stored in 32-bit."""
         from ..weights import load_model
-        model = load_model(model_dir, device=device, dtype=_dtype(dtype), page_size=page_size)
+        model = load_model(model_dir, device=device, dtype=_dtype(dtype), page_size=page_size,
+                           round_weights_to_bf16=round_weights_to_bf16)
         return cls(model, max_tokens, max_slots, max_seq_len, use_graphs)
+
+    @staticmethod
+    def default_page_size() -> int:
+        from .runtime import DEFAULT_PAGE_SIZE
+        return DEFAULT_PAGE_SIZE
+
+    @classmethod
+    def pages_for(cls, tokens_per_sequence: int, sequences: int = 1, page_size: Optional[int] = None) -> int:
+        """Cache pages that `sequences` sequences of `tokens_per_sequence` positions hold."""
+        ps = page_size or cls.default_page_size()
+        return -(-int(tokens_per_sequence) // ps) * int(sequences)
+
+    @property
+    def page_size(self) -> int:
+        return self.rt.page_size
 
     @property
     def vocab_size(self) -> int:
@@ -106,7 +127,8 @@ class Engine:
 
     # -- the step ----------------------------------------------------------------------------
     def _prepare(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Want,
-                 uniforms: Optional[np.ndarray] = None, pages_width: Optional[int] = None) -> StepBatch:
+                 uniforms: Optional[np.ndarray] = None, pages_width: Optional[int] = None,
+                 positions: Optional[Sequence] = None) -> StepBatch:
         if len(entries) == 0:
             raise RequestError("a step needs at least one sequence")
         slots = [int(s) for s, _ in entries]
@@ -131,13 +153,22 @@ class Engine:
             for w, t in zip(want_l, tokens):
                 if any(not (0 <= i < len(t)) for i in w):
                     raise RequestError(f"a wanted place is outside the {len(t)} tokens its sequence brings")
+        C = self.model.spec.position_components
+        if positions is not None:
+            if len(positions) != len(tokens):
+                raise RequestError("positions must be given for every sequence of the step")
+            for p, t in zip(positions, tokens):
+                shape = np.asarray(p).shape
+                if shape not in ((len(t), C),) and not (C == 1 and shape == (len(t),)):
+                    raise RequestError(f"positions of a sequence of {len(t)} tokens must have shape [{len(t)}, {C}], got {list(shape)}")
         self.cache.reserve([(s, len(t)) for s, t in zip(slots, tokens)])
         pos0 = [self.cache.lengths[s] for s in slots]
         if pages_width is None and self.use_graphs and all(len(t) == 1 for t in tokens):
             # a few widths only, so that a captured decode step is reused while sequences grow
             need = -(-(max(pos0) + 1) // self.rt.page_size)
             pages_width = min(max(4, 1 << (need - 1).bit_length()), max(self.cache.max_pages_per_seq, need))
-        batch = StepBatch(slots, tokens, pos0, want_l, self.cache.num_kv_groups, pages_width, self.rt.page_size)
+        batch = StepBatch(slots, tokens, pos0, want_l, self.cache.num_kv_groups, pages_width, self.rt.page_size,
+                          C, positions)
         n = batch.layout.total
         if n > self._host.numel():
             size = 1 << (n - 1).bit_length()
@@ -159,7 +190,7 @@ class Engine:
         step buffer anew, bump positions and lengths in place, write the new tokens (and page rows,
         when a sequence enters a new page) and upload.  None if this is not such a step."""
         st = self._decode_again
-        if st is None or self._host_owner is not st[1]:
+        if st is None or self._host_owner is not st[1] or st[1]._positions is not None:
             return None
         slots, batch, lens_after = st
         if len(entries) != len(slots):
@@ -181,8 +212,11 @@ class Engine:
         B, o, host = len(slots), batch.layout.offsets, self._host.numpy()
         self._copied.synchronize()
         host[o["token_ids"]:o["token_ids"] + B] = toks
-        for name in ("tok_pos", "seq_pos0", "seq_len"):
+        for name in ("seq_pos0", "seq_len"):
             host[o[name]:o[name] + B] += 1
+        row = (B + 3) // 4 * 4
+        for c in range(batch.n_components):
+            host[o["tok_pos"] + c * row:o["tok_pos"] + c * row + B] += 1
         if uniforms is not None:
             host[o["uniforms"]:o["uniforms"] + B] = np.asarray(uniforms, dtype=np.float32).view(np.int32)
         if new_page:
@@ -235,11 +269,16 @@ class Engine:
         for s, n in zip(batch.slots, batch.q_lens):
             self.cache.advance(s, n)
 
-    def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Want = "last") -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Want = "last",
+             positions: Optional[Sequence] = None) -> Optional[torch.Tensor]:
         """Run the given tokens; return logits [wanted, vocab] (float32, on the device), in the order
         of the entries and of their wanted places.  The tensor is the engine's own buffer: it is
-        overwritten by the next step, so copy what must last."""
-        batch = self._prepare(entries, want)
+        overwritten by the next step, so copy what must last.
+
+        `positions` (only for models whose `position_components` exceeds 1): per sequence an integer
+        array [tokens, components]; component 0 is ignored (it is always the index in the sequence),
+        the others replace the default, which is that index again."""
+        batch = self._prepare(entries, want, positions=positions)
         logits = self._forward(batch)
         self._finish(batch)
         return logits

@@ -50,8 +50,14 @@ class Workspace:
         return self.buf[start:start + n * es].view(dtype).view(tuple(shape))
 
 
+# Positions per cache page unless a caller asks otherwise: the tile of keys that the attention
+# kernels fetch at a time.
+DEFAULT_PAGE_SIZE = 64
+
+
 class Runtime:
-    def __init__(self, device, dtype: torch.dtype, page_size: int = 64):
+    def __init__(self, device, dtype: torch.dtype, page_size: int | None = None):
+        page_size = DEFAULT_PAGE_SIZE if page_size is None else int(page_size)
         if dtype not in (torch.float32, torch.bfloat16):
             raise BackendError(f"compute dtype must be float32 or bfloat16, got {dtype}")
         self.device = torch.device(device)

@@ -60,6 +60,9 @@ _SIGS = {
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_gemm_skinny_norm_parts": [c_int, c_int],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
+    "hb_rng_normal": [c_int, c_void_p, ctypes.c_longlong, ctypes.c_ulonglong, c_float, c_float, c_void_p],
+    "hb_fill": [c_int, c_void_p, ctypes.c_longlong, c_float, c_void_p],
+    "hb_cast": [c_int, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int, c_void_p],
 }
 _fns: dict = {}
 
@@ -129,6 +132,44 @@ def is_available() -> bool:
 
 
 # ---------------------------------------------------------------------------------------------
+def rng_normal(out: torch.Tensor, key: int, mean: float, std: float) -> None:
+    """out.flat[i] = mean + std * normal(key, i): the same bits as `weights.counter_rng.normal`."""
+    _check(out, None, "out")
+    if not out.is_contiguous():
+        raise BackendError("rng_normal: out must be contiguous")
+    _run("hb_rng_normal", dtype_code(out.dtype), out.data_ptr(), out.numel(), int(key) & ((1 << 64) - 1),
+         float(mean), float(std), _stream())
+
+
+def fill(out: torch.Tensor, value: float) -> None:
+    """Every element of a contiguous float32, bfloat16 or int32 tensor becomes `value`."""
+    _check(out, None, "out")
+    if not out.is_contiguous():
+        raise BackendError("fill: out must be contiguous")
+    code = 2 if out.dtype == torch.int32 else dtype_code(out.dtype)
+    _run("hb_fill", code, out.data_ptr(), out.numel(), float(value), _stream())
+
+
+_CAST_SRC = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def cast(src: torch.Tensor, dtype: torch.dtype, round_bf16: bool = False) -> torch.Tensor:
+    """`src` (float32, bfloat16 or float16, contiguous, on the device) as a new tensor of `dtype`
+    (float32 or bfloat16; float32 -> bfloat16 rounds to nearest even).  With `round_bf16` the
+    values pass through bfloat16 whatever `dtype` is.  Returns `src` itself when nothing changes."""
+    _check(src, None, "src")
+    if src.dtype not in _CAST_SRC:
+        raise BackendError(f"cast: cannot read {src.dtype}")
+    if src.dtype == dtype and (not round_bf16 or dtype == torch.bfloat16):
+        return src
+    if not src.is_contiguous():
+        raise BackendError("cast: src must be contiguous")
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    _run("hb_cast", _CAST_SRC[src.dtype], src.data_ptr(), dtype_code(dtype), out.data_ptr(), src.numel(),
+         1 if round_bf16 else 0, _stream())
+    return out
+
+
 def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, :] = float(table[ids[t], :]); out is the float residual stream [T, H]."""
     _check(table, None, "table"); _check(ids, torch.int32, "ids"); _check(out, torch.float32, "out")

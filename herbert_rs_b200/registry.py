@@ -20,39 +20,67 @@ from typing import Callable, Dict
 from .errors import ConfigError
 
 _ARCHITECTURES: Dict[str, type] = {}
+_MODEL_CLASSES: Dict[str, type] = {}
 _MODEL_TYPES: Dict[str, str] = {}
+_DEFAULT_ARCHITECTURE: list = []
 _PARTS: Dict[str, Dict[str, Callable]] = {
     "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {},
 }
 
 
-def register_architecture(name: str, config_cls: type, model_types: tuple = ()) -> None:
-    """Register `config_cls` (with `from_dict(dict)` and `model_spec()`) under an architecture name."""
+def register_architecture(name: str, config_cls: type, model_types: tuple = (), model_cls: type = None,
+                          default: bool = False) -> None:
+    """Register `config_cls` (with `from_dict(dict)` and `model_spec()`) under an architecture name.
+
+    `model_cls(spec, rt)` is the class built from the spec (the generic decoder when None): an
+    architecture whose top level differs (scaled embeddings, a cap on the logits, a second head)
+    brings its own.  `default=True` makes this the architecture of a config.json that names neither
+    `architectures` nor `model_type` (the reference defaults `model_type` to "qwen3",
+    crates/core/src/config.rs:184-185, 261-263)."""
     _ARCHITECTURES[name] = config_cls
+    if model_cls is not None:
+        _MODEL_CLASSES[name] = model_cls
+    else:
+        _MODEL_CLASSES.pop(name, None)
     for mt in model_types:
         _MODEL_TYPES[mt] = name
+    if default:
+        _DEFAULT_ARCHITECTURE[:] = [name]
 
 
 def architectures() -> list:
     return sorted(_ARCHITECTURES)
 
 
-def config_class_for(config_json: dict) -> type:
-    """Choose the configuration class from config.json's `architectures`, else `model_type`."""
+def architecture_for(config_json: dict) -> str:
+    """The registered architecture name chosen by config.json's `architectures`, else `model_type`,
+    else the registered default."""
     archs = config_json.get("architectures")
     names = [a for a in archs if isinstance(a, str)] if isinstance(archs, list) else []
     for a in names:
         if a in _ARCHITECTURES:
-            return _ARCHITECTURES[a]
+            return a
     mt = config_json.get("model_type")
     if not names and isinstance(mt, str) and mt in _MODEL_TYPES:
-        return _ARCHITECTURES[_MODEL_TYPES[mt]]
-    if not names and mt is None and "qwen3" in _MODEL_TYPES:
-        # the reference's default model_type (crates/core/src/config.rs:184-185, 261-263)
-        return _ARCHITECTURES[_MODEL_TYPES["qwen3"]]
+        return _MODEL_TYPES[mt]
+    if not names and mt is None and _DEFAULT_ARCHITECTURE and _DEFAULT_ARCHITECTURE[0] in _ARCHITECTURES:
+        return _DEFAULT_ARCHITECTURE[0]
     asked = names[0] if names else mt
     raise ConfigError(
         f"unsupported architecture: {asked!r}. Registered: {', '.join(architectures()) or '(none)'}")
+
+
+def config_class_for(config_json: dict) -> type:
+    return _ARCHITECTURES[architecture_for(config_json)]
+
+
+def model_class_for(config_json: dict) -> type:
+    """The model class of config.json's architecture (the generic decoder unless it brought its own)."""
+    name = architecture_for(config_json)
+    if name in _MODEL_CLASSES:
+        return _MODEL_CLASSES[name]
+    from .models.decoder import DecoderModel
+    return DecoderModel
 
 
 def config_from_json(config_json: dict):

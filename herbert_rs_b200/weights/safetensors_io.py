@@ -110,35 +110,46 @@ class SafeTensorsFile:
         self._f.close()
 
 
-def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: dict | None = None) -> None:
-    """Write tensors (sorted by name) to one safetensors file."""
+def _raw_bytes(t: torch.Tensor) -> bytes:
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().tobytes()
+    if t.dtype == torch.bool:
+        return t.to(torch.uint8).numpy().tobytes()
+    return t.numpy().tobytes()
+
+
+def save_stream(entries, path: str, metadata: dict | None = None) -> None:
+    """Write one safetensors file from `entries`: (name, dtype, shape, make) with `make()` returning
+    the tensor.  Tensors are made and written one at a time, sorted by name, so a model larger
+    than the host's free memory can still be written."""
     header: dict = {}
     if metadata:
         header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
+    entries = sorted(entries, key=lambda e: e[0])
     offset = 0
-    order = sorted(tensors)
-    blobs = []
-    for name in order:
-        t = tensors[name].detach().cpu().contiguous()
-        if t.dtype not in _TORCH_TO_NAME:
-            raise SafeTensorsError(f"cannot store dtype {t.dtype} for '{name}'")
-        if t.dtype == torch.bfloat16:
-            raw = t.view(torch.int16).numpy().tobytes()
-        elif t.dtype == torch.bool:
-            raw = t.to(torch.uint8).numpy().tobytes()
-        else:
-            raw = t.numpy().tobytes()
-        header[name] = {"dtype": _TORCH_TO_NAME[t.dtype], "shape": list(t.shape),
-                        "data_offsets": [offset, offset + len(raw)]}
-        offset += len(raw)
-        blobs.append(raw)
+    for name, dtype, shape, _ in entries:
+        if dtype not in _TORCH_TO_NAME:
+            raise SafeTensorsError(f"cannot store dtype {dtype} for '{name}'")
+        key = _TORCH_TO_NAME[dtype]
+        n = int(np.prod(shape, dtype=np.int64)) * _DTYPES[key][2] if len(shape) else _DTYPES[key][2]
+        header[name] = {"dtype": key, "shape": [int(d) for d in shape], "data_offsets": [offset, offset + n]}
+        offset += n
     text = json.dumps(header, separators=(",", ":")).encode("utf-8")
     text += b" " * ((8 - len(text) % 8) % 8)
     with open(path, "wb") as f:
         f.write(struct.pack("<Q", len(text)))
         f.write(text)
-        for raw in blobs:
-            f.write(raw)
+        for name, dtype, shape, make in entries:
+            t = make()
+            if t.dtype != dtype or tuple(t.shape) != tuple(shape):
+                raise SafeTensorsError(f"'{name}' was announced as {dtype} {list(shape)} and made as {t.dtype} {list(t.shape)}")
+            f.write(_raw_bytes(t))
+
+
+def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: dict | None = None) -> None:
+    """Write tensors (sorted by name) to one safetensors file."""
+    save_stream([(n, t.dtype, tuple(t.shape), (lambda t=t: t)) for n, t in tensors.items()], path, metadata)
 
 
 class ModelFiles:

@@ -40,3 +40,20 @@ def model_dirs(tmp_path_factory):
         hb.write_random_model(cfg, str(d), seed={"A": 11, "B": 22, "C": 33, "D": 44}.get(name, 5))
         out[name] = str(d)
     return out
+
+
+def pytest_terminal_summary(terminalreporter):
+    """How close the bfloat16 comparisons came to their bounds (the bound's constants rest on this)."""
+    try:
+        import gpu_util
+    except Exception:
+        return
+    rec = gpu_util.RECORDS
+    if not rec:
+        return
+    for kind in ("model", "scale"):
+        r = [(e / b if b > 0 else float("inf"), w) for w, e, b, k in rec if k == kind]
+        if r:
+            worst = max(r)
+            terminalreporter.write_line(
+                f"bfloat16 comparisons ({kind}-derived bound): {len(r)}, largest error/bound {worst[0]:.3f} ({worst[1]})")

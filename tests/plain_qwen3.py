@@ -186,17 +186,20 @@ def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], i: int, cfg: dict
 
 
 def logits_all_positions(w: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int], dtype=torch.float64,
-                         store=_same) -> torch.Tensor:
+                         store=_same, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
     """Logits at every position of one whole sequence: embed -> layers -> final norm -> head
     (generic_model.rs:131-319; the head is the embedding table when tied, loader_common.rs:1851-1860).
     `store` is applied wherever an engine would keep an activation between two kernels (norm
     outputs, projections, rotated q/k, attention output, the gated product); with `bf16_storage`
-    the result shows how much of a bfloat16 engine's error is the storage format's own."""
+    the result shows how much of a bfloat16 engine's error is the storage format's own.
+    `rows`: only these positions go through the final norm and the head (a large vocabulary)."""
     T = len(ids)
     cos, sin = rope_tables(cfg["rot"], cfg["theta"], T, dtype)
     x = embedding(w["model.embed_tokens.weight"], ids, dtype)
     for i in range(cfg["L"]):
         x = decoder_layer(x, w, i, cfg, cos, sin, store)
+    if rows is not None:
+        x = x[list(rows)]
     n = store(rms_norm(x, w["model.norm.weight"], cfg["eps"]))
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     return linear(n, head)
@@ -207,8 +210,8 @@ class PlainModel:
         self.cfg = read_config(f"{model_dir}/config.json")
         self.w = read_safetensors(f"{model_dir}/model.safetensors")
 
-    def logits(self, ids: Sequence[int], dtype=torch.float64, store=_same) -> torch.Tensor:
-        return logits_all_positions(self.w, self.cfg, ids, dtype, store)
+    def logits(self, ids: Sequence[int], dtype=torch.float64, store=_same, rows=None) -> torch.Tensor:
+        return logits_all_positions(self.w, self.cfg, ids, dtype, store, rows)
 
     def greedy(self, prompt: Sequence[int], n: int, dtype=torch.float64) -> List[int]:
         """n greedy tokens, recomputing the whole sequence each time; first maximum wins

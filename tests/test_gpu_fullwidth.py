@@ -31,11 +31,11 @@ def test_every_cutting_at_production_widths(wide, dtype):
     refs = [plain.logits(r, torch.float32).double().numpy() for r in reqs]     # float32 plain: float64 at this width is slow
     eng = engine_for(d, dtype, max_tokens=1024, max_slots=4)
     for r, ref in zip(reqs, refs):
-        assert_close(replay_whole(eng, r), ref, dtype, "wide whole")
-    assert_close(replay_tail_one_by_one(eng, reqs[0], 32), refs[0], dtype, "wide one by one")
+        assert_close(replay_whole(eng, r), ref, dtype, "wide whole", plain=plain, ids=r, arith=torch.float32)
+    assert_close(replay_tail_one_by_one(eng, reqs[0], 32), refs[0], dtype, "wide one by one", plain=plain, ids=reqs[0], arith=torch.float32)
     got = replay_batches(eng, reqs, [100, 9, 3], [[0, 1, 2]])
-    for g, ref in zip(got, refs):
-        assert_close(g, ref, dtype, "wide batched")
+    for g, ref, r in zip(got, refs, reqs):
+        assert_close(g, ref, dtype, "wide batched", plain=plain, ids=r, arith=torch.float32)
     from herbert_rs_b200 import ops
     ops.check_kernel_errors()
 
@@ -53,6 +53,6 @@ def test_a_decode_batch_of_forty_at_production_widths(wide, dtype):
     got = replay_batches(eng, reqs, lens, [list(range(40))])
     for i in (0, 7, 19, 39):
         ref = plain.logits(reqs[i], torch.float32).double().numpy()
-        assert_close(got[i], ref, dtype, f"request {i} of forty")
+        assert_close(got[i], ref, dtype, f"request {i} of forty", plain=plain, ids=reqs[i], arith=torch.float32)
     from herbert_rs_b200 import ops
     ops.check_kernel_errors()

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import herbert_rs_b200 as hb
-from gpu_util import (DTYPES, TOL, assert_close, engine_for, random_ids, replay_batches, replay_tail_one_by_one,
+from gpu_util import (DTYPES, assert_close, bound_for, bf16_own_error, engine_for, random_ids, replay_batches, replay_tail_one_by_one,
                       replay_whole, sensitivity_bound, to_np)
 from plain_qwen3 import PlainModel
 
@@ -47,7 +47,7 @@ def test_each_request_alone_and_whole(model_dirs, plain, name, dtype):
     V, P = plain[name].cfg["V"], plain[name].cfg["P"]
     for n in [1, 2, 13, 64, 65, min(P, 200)] + ([300] if name == "D" else []):
         ids = random_ids(rng, V, n)
-        assert_close(replay_whole(eng, ids), plain[name].logits(ids).numpy(), dtype, f"{name} whole n={n}")
+        assert_close(replay_whole(eng, ids), plain[name].logits(ids).numpy(), dtype, f"{name} whole n={n}", plain=plain[name], ids=ids)
     eng.cache.check()
 
 
@@ -60,8 +60,8 @@ def test_last_32_tokens_one_by_one(model_dirs, plain, name, dtype):
         ids = random_ids(rng, plain[name].cfg["V"], n)
         ref = plain[name].logits(ids).numpy()
         got = replay_tail_one_by_one(eng, ids, 32)
-        assert_close(got, ref, dtype, f"{name} tail n={n}")
-        assert_close(got, replay_whole(eng, ids), dtype, f"{name} tail vs whole n={n}")
+        assert_close(got, ref, dtype, f"{name} tail n={n}", plain=plain[name], ids=ids)
+        assert_close(got, replay_whole(eng, ids), dtype, f"{name} tail vs whole n={n}", plain=plain[name], ids=ids)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -78,12 +78,12 @@ def test_unequal_batches_one_after_another(model_dirs, sharp_dir, plain, name, d
     got = replay_batches(eng, reqs, prompts, [[0, 1, 2, 3], [4, 5, 6], [7, 8]])
     for i, ids in enumerate(reqs):
         bound = sensitivity_bound(pm, ids, dtype) if name == "Bsharp" else None
-        assert_close(got[i], pm.logits(ids).numpy(), dtype, f"{name} batched request {i} (len {lens[i]})", bound)
+        assert_close(got[i], pm.logits(ids).numpy(), dtype, f"{name} batched request {i} (len {lens[i]})", bound, plain=pm, ids=ids)
     assert eng.cache.slots.free_count == 4 and all(p.free_count == 5 for p in eng.cache.pools)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_batch_composition_does_not_change_logits(model_dirs, dtype):
+def test_batch_composition_does_not_change_logits(model_dirs, plain, dtype):
     eng = engine_for(model_dirs["B"], dtype)
     rng = np.random.default_rng(8)
     reqs = [random_ids(rng, 384, n) for n in (50, 3, 17)]
@@ -91,8 +91,8 @@ def test_batch_composition_does_not_change_logits(model_dirs, dtype):
     together = replay_batches(eng, reqs, [len(r) for r in reqs], [[0, 1, 2]])
     # float32: one kernel for every size, the same sums per row.  bfloat16: a step of few rows and
     # a step of many rows take different product kernels, so rounding (and only rounding) differs.
-    for a, b in zip(alone, together):
-        assert np.abs(a - b).max() <= (1e-6 if dtype == "float32" else TOL[dtype])
+    for a, b, ids in zip(alone, together, reqs):
+        assert np.abs(a - b).max() <= (1e-6 if dtype == "float32" else bound_for(plain["B"], ids, dtype, a))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -102,7 +102,7 @@ def test_long_decoding(model_dirs, plain, name, dtype):
     eng = engine_for(model_dirs[name], dtype)
     ids = random_ids(np.random.default_rng(9), plain[name].cfg["V"], n)
     got = replay_tail_one_by_one(eng, ids, n - 3)
-    assert_close(got, plain[name].logits(ids).numpy(), dtype, f"{name} long decode")
+    assert_close(got, plain[name].logits(ids).numpy(), dtype, f"{name} long decode", plain=plain[name], ids=ids)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -111,12 +111,12 @@ def test_first_tokens_of_a_sequence(model_dirs, plain, name, dtype):
     eng = engine_for(model_dirs[name], dtype)
     ids = random_ids(np.random.default_rng(10), plain[name].cfg["V"], 4)
     ref = plain[name].logits(ids).numpy()
-    assert_close(replay_tail_one_by_one(eng, ids, 3), ref, dtype, f"{name} first tokens")
+    assert_close(replay_tail_one_by_one(eng, ids, 3), ref, dtype, f"{name} first tokens", plain=plain[name], ids=ids)
     s = eng.alloc_slot()
     first = to_np(eng.step([(s, ids[:1])], "last"))
-    assert_close(first, ref[:1], dtype, "the very first token")
+    assert_close(first, ref[:1], dtype, "the very first token", plain=plain[name], ids=ids, rows=[0])
     assert eng.step([(s, ids[1:2])], None) is None            # nothing wanted: nothing returned
-    assert_close(to_np(eng.step([(s, ids[2:4])], [[1]])), ref[3:4], dtype, "after a silent step")
+    assert_close(to_np(eng.step([(s, ids[2:4])], [[1]])), ref[3:4], dtype, "after a silent step", plain=plain[name], ids=ids, rows=[3])
     eng.free_slot(s)
 
 
@@ -129,7 +129,7 @@ def test_prompt_cut_into_pieces(model_dirs, plain, dtype):
     for a, b in [(0, 7), (7, 64), (64, 65), (65, 140), (140, 150)]:
         rows.append(to_np(eng.step([(s, ids[a:b])], "all")))
     eng.free_slot(s)
-    assert_close(np.concatenate(rows, 0), plain["C"].logits(ids).numpy(), dtype, "prompt in pieces")
+    assert_close(np.concatenate(rows, 0), plain["C"].logits(ids).numpy(), dtype, "prompt in pieces", plain=plain["C"], ids=ids)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -142,7 +142,7 @@ def test_truncate_and_refeed(model_dirs, plain, dtype):
     other = ids[:70] + random_ids(np.random.default_rng(13), 256, 20)
     got = to_np(eng.step([(s, other[70:])], "all"))
     eng.free_slot(s)
-    assert_close(got, plain["A"].logits(other).numpy()[70:], dtype, "after truncate")
+    assert_close(got, plain["A"].logits(other).numpy()[70:], dtype, "after truncate", plain=plain["A"], ids=other, rows=range(70, 90))
 
 
 def test_requests_are_validated_before_anything_runs(model_dirs):
@@ -189,14 +189,16 @@ def test_trace_run_program(model_dirs, plain, tmp_path, dtype):
     ra, rb = plain["A"].logits(a).numpy(), plain["A"].logits(b).numpy()
     rc = plain["A"].logits(c + [9]).numpy()
     g0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(3, 256)
-    assert_close(g0.astype(np.float64), np.stack([ra[0], ra[29], rb[4]]), dtype, "trace step 0")
+    assert_close(g0[:2].astype(np.float64), np.stack([ra[0], ra[29]]), dtype, "trace step 0", plain=plain["A"], ids=a, rows=[0, 29])
+    assert_close(g0[2:].astype(np.float64), rb[4:5], dtype, "trace step 0, second request", plain=plain["A"], ids=b, rows=[4])
     g1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(2, 256)
-    assert_close(g1.astype(np.float64), np.stack([ra[30], rb[5]]), dtype, "trace step 1")
+    assert_close(g1[:1].astype(np.float64), ra[30:31], dtype, "trace step 1", plain=plain["A"], ids=a, rows=[30])
+    assert_close(g1[1:].astype(np.float64), rb[5:6], dtype, "trace step 1, second request", plain=plain["A"], ids=b, rows=[5])
     g10 = np.fromfile(out / "10.f32", dtype="<f4").reshape(1, 256)
-    assert_close(g10.astype(np.float64), ra[39:40], dtype, "trace step 10")
+    assert_close(g10.astype(np.float64), ra[39:40], dtype, "trace step 10", plain=plain["A"], ids=a, rows=[39])
     assert not (out / "11.f32").exists()
     g12 = np.fromfile(out / "12.f32", dtype="<f4").reshape(1, 256)
-    assert_close(g12.astype(np.float64), rc[70:71], dtype, "trace step 12")
+    assert_close(g12.astype(np.float64), rc[70:71], dtype, "trace step 12", plain=plain["A"], ids=c + [9], rows=[70])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -207,13 +209,14 @@ def test_greedy_generation_through_the_entry_point(model_dirs, plain, dtype):
     res = hb.generate(eng, prompts, hb.GenerationOptions(max_tokens=12, ignore_eos=True, max_batch=3),
                       hb.SamplingParams(temperature=0.0))
     assert res.stats.batches == 2 and all(len(t) == 12 for t in res.tokens)
-    margin = {"float32": 1e-4, "bfloat16": 4e-2}[dtype]
     same = 0
     for p, got in zip(prompts, res.tokens):
         ids = list(p)
         for tok in got:
             ref = plain["B"].logits(ids)[-1].numpy()
-            assert ref.max() - ref[tok] <= margin       # the plain model's best token, or one tied with it within rounding
+            # the plain model's best token, or one tied with it within twice the logits' own bound
+            margin = 1e-4 if dtype == "float32" else 2 * bound_for(plain["B"], ids, dtype, ref, rows=[len(ids) - 1])
+            assert ref.max() - ref[tok] <= margin
             same += int(tok == int(ref.argmax()))
             ids.append(tok)
     if dtype == "float32":
@@ -232,11 +235,11 @@ def test_generation_with_prompts_in_pieces(model_dirs, plain, dtype):
     opt = dict(max_tokens=6, ignore_eos=True)
     whole = hb.generate(eng, prompts, hb.GenerationOptions(**opt), hb.SamplingParams(temperature=0.0))
     cut = hb.generate(eng, prompts, hb.GenerationOptions(prefill_chunk_size=5, **opt), hb.SamplingParams(temperature=0.0))
-    margin = {"float32": 1e-4, "bfloat16": 4e-2}[dtype]
     for p, got in zip(prompts, cut.tokens):
         ids = list(p)
         for tok in got:
             ref = plain["A"].logits(ids)[-1].numpy()
+            margin = 1e-4 if dtype == "float32" else 2 * bound_for(plain["A"], ids, dtype, ref, rows=[len(ids) - 1])
             assert ref.max() - ref[tok] <= margin
             ids.append(tok)
     if dtype == "float32":
@@ -274,7 +277,7 @@ def test_captured_decode_steps_equal_eager_ones(model_dirs, plain, dtype):
     assert eager.graph_replays == 0 and graphed.graph_replays > 200
     for x, y, ids in zip(a, b, reqs):
         assert np.abs(x - y).max() <= 1e-6          # same kernels, same arithmetic
-        assert_close(y, plain["C"].logits(ids).numpy(), dtype, "graphed decode")
+        assert_close(y, plain["C"].logits(ids).numpy(), dtype, "graphed decode", plain=plain["C"], ids=ids)
 
 
 @pytest.mark.parametrize("which,dtype", [("C", "float32"), ("D", "bfloat16")])
@@ -296,3 +299,40 @@ def test_decode_steps_that_update_the_step_buffer_in_place(model_dirs, plain, wh
     d = hb.generate(slow, prompts[:3], hb.GenerationOptions(max_tokens=40, stop_token_ids=[stop]), hb.SamplingParams(temperature=0.7, top_k=30, top_p=0.95, seed=5)).tokens
     assert c == d and len(c[0]) == 11
     fast.cache.check()
+
+
+@pytest.mark.parametrize("key", [0, 57])
+def test_the_bfloat16_bound_sees_one_dropped_key(model_dirs, plain, key):
+    """The derived bfloat16 bound is tight enough to show a fault of the cache: compared with a
+    reference that is wrong on purpose (head 3 of the first layer never sees key `key`), the engine's
+    logits at Tiny D are out of bounds, while against the right reference they are within."""
+    import plain_qwen3 as P
+    pm = plain["D"]
+    ids = random_ids(np.random.default_rng(1), 1000, 200)
+    eng = engine_for(model_dirs["D"], "bfloat16")
+    got = replay_whole(eng, ids)
+    ref = pm.logits(ids).numpy()
+    bound = bound_for(pm, ids, "bfloat16", ref)
+    assert np.abs(got - ref).max() <= bound
+    orig, calls, head = P.attention_scores, [0], 3
+
+    def faulty(q, k, v, scale, window):
+        out = orig(q, k, v, scale, window)
+        if calls[0] == 0:
+            T, kh = q.shape[0], head // (q.shape[1] // k.shape[1])
+            s = (q[:, head] @ k[:, kh].T) * scale
+            i = torch.arange(T)
+            mask = i[None, :] <= i[:, None]
+            mask[:, key] = False
+            mask[key, key] = True
+            out[:, head] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, kh]
+        calls[0] += 1
+        return out
+
+    P.attention_scores = faulty
+    try:
+        wrong = pm.logits(ids).numpy()
+    finally:
+        P.attention_scores = orig
+    over = np.abs(got - wrong).max(axis=-1) > bound
+    assert over.any() and not over[:key].any()        # rows before the dropped key cannot tell

@@ -52,12 +52,12 @@ def test_random_configurations_in_every_cutting(seed):
                 what = f"seed {seed} case {case} {cfg}"
                 eng = engine_for(d, dtype, max_tokens=64 * 24, max_slots=4)
                 i = int(rng.integers(0, 4))
-                assert_close(replay_whole(eng, reqs[i]), refs[i], dtype, "whole: " + what)
-                assert_close(replay_tail_one_by_one(eng, reqs[i], int(rng.integers(1, 40))), refs[i], dtype, "tail: " + what)
+                assert_close(replay_whole(eng, reqs[i]), refs[i], dtype, "whole: " + what, plain=pm, ids=reqs[i])
+                assert_close(replay_tail_one_by_one(eng, reqs[i], int(rng.integers(1, 40))), refs[i], dtype, "tail: " + what, plain=pm, ids=reqs[i])
                 prompt_lens = [int(rng.integers(1, len(r) + 1)) for r in reqs]
                 got = replay_batches(eng, reqs, prompt_lens, [[0, 1, 2], [3]] if rng.random() < 0.5 else [[0, 1, 2, 3]])
-                for g, ref in zip(got, refs):
-                    assert_close(g, ref, dtype, "batched: " + what)
+                for g, ref, r in zip(got, refs, reqs):
+                    assert_close(g, ref, dtype, "batched: " + what, plain=pm, ids=r)
                 hb.ops.check_kernel_errors()
         finally:
             shutil.rmtree(d, ignore_errors=True)

@@ -178,3 +178,32 @@ def test_our_writer_is_read_by_the_safetensors_package(tmp_path):
     save_file(t, str(tmp_path / "x.safetensors"))
     back = st.load_file(str(tmp_path / "x.safetensors"))
     assert torch.equal(back["a"], t["a"]) and torch.equal(back["b"], t["b"])
+
+
+def test_counter_rng_is_addressed_by_element_and_looks_normal():
+    from herbert_rs_b200.weights import counter_rng as R
+    key = R.tensor_key(3, "model.layers.0.mlp.down_proj.weight")
+    assert key != R.tensor_key(4, "model.layers.0.mlp.down_proj.weight") != R.tensor_key(3, "model.layers.1.mlp.down_proj.weight")
+    whole = R.normal(key, 300000, 0.0, 1.0)
+    assert torch.equal(whole[1234:1234 + 5000], R.normal(key, 5000, 0.0, 1.0, start=1234))     # any piece alone
+    assert torch.equal(R.normal(key, 1000, 1.0, 0.1, torch.bfloat16).float(),
+                       (1.0 + 0.1 * whole[:1000]).to(torch.bfloat16).float())
+    z = whole.double()
+    assert abs(z.mean()) < 0.01 and abs(z.std() - 1) < 0.01 and 2.9 < (z ** 4).mean() < 3.1
+    assert 0.0020 < (z.abs() > 3).double().mean() < 0.0034 and z.abs().max() < 6.0
+    other = R.normal(R.tensor_key(3, "x"), 300000, 0.0, 1.0).double()
+    assert abs((z * other).mean()) < 0.01                                                     # streams do not follow each other
+
+
+def test_a_tensor_of_a_random_model_depends_on_seed_and_name_only(tmp_path):
+    import herbert_rs_b200 as hb
+    from herbert_rs_b200.weights import ModelFiles
+    a, b = dict(TINY["A"]), dict(TINY["A"])
+    b["num_hidden_layers"] = 3                      # another tensor list: the shared names keep their bytes
+    hb.write_random_model(a, str(tmp_path / "a"), seed=9)
+    hb.write_random_model(b, str(tmp_path / "b"), seed=9)
+    fa, fb = ModelFiles(str(tmp_path / "a")), ModelFiles(str(tmp_path / "b"))
+    for n in fa.names():
+        assert torch.equal(fa.tensor(n).view(torch.int16), fb.tensor(n).view(torch.int16))
+    w = fa.tensor("model.layers.1.input_layernorm.weight").float()
+    assert abs(w.mean() - 1) < 0.05 and 0.05 < w.std() < 0.15
