@@ -122,6 +122,20 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def admit(self, pairs: Sequence[Tuple[int, int]]) -> List[bool]:
+        """For (slot, new positions) in order of priority: which of them fit into the next step
+        together.  One does not fit if it would pass the length limit, or if the pages it needs are
+        no longer free after the ones before it took theirs.  Nothing is reserved."""
+        free = self.cache.free_pages()
+        out = []
+        for slot, n in pairs:
+            need = self.cache.pages_needed(slot, n)
+            good = self.cache.length(slot) + n <= self.cache.max_seq_len and need <= free
+            if good:
+                free -= need
+            out.append(good)
+        return out
+
     def truncate(self, slot: int, n: int) -> None:
         self.cache.truncate(slot, n)
 

@@ -111,8 +111,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
     """Generate for every prompt; results keep the order of the requests.
 
     `engine` needs: alloc_slot(), free_slot(slot), step_and_choose(entries, params, uniforms) -> ids,
-    step(entries, None) when prompts enter in pieces, and optionally `default_stop_token_ids` and
-    `max_slots`.
+    step(entries, None) when prompts enter in pieces, and optionally `default_stop_token_ids`,
+    `max_slots` and `admit(pairs)` (for (slot, new positions) pairs in order of priority: which of
+    them fit into the next step together).  With `admit`, a batch takes only the prompts that fit
+    (the others wait for the next batch), and a sequence that runs out of room ends alone.
     finish_reason is one of: "stop_token", "max_tokens", "repetition", "capacity".
     """
     options = options or GenerationOptions()
@@ -146,20 +148,48 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
             return "repetition"
         return None
 
-    for batch_ids in plan_batches(len(prompts), max_batch):
-        stats.batches += 1
-        slots = {}
+    admit = getattr(engine, "admit", None)      # which of these (slot, new positions) fit the next step together
+
+    def fits(pairs: List[Tuple[int, int]]) -> List[bool]:
+        return list(admit(pairs)) if admit is not None else [True] * len(pairs)
+
+    pending = list(range(len(prompts)))
+    while pending:
+        # the next batch: requests in their order, as many as have slots and room for their prompts
+        batch_ids, slots = [], {}
         try:
-            for i in batch_ids:
+            cand = pending[:max_batch]
+            for i in cand:
                 slots[i] = engine.alloc_slot()
+            ok = fits([(slots[i], len(prompts[i])) for i in cand])
+            if not ok[0]:
+                # the first in line has the whole cache before it and still does not fit: it never will
+                reasons[cand[0]] = "capacity"
+                pending.remove(cand[0])
+                continue
+            for i, good in zip(cand, ok):
+                if good:
+                    batch_ids.append(i)
+                else:
+                    engine.free_slot(slots.pop(i))
+            # a request that did not fit waits for the next batch; the ones behind it keep their order
+            pending = [i for i in pending if i not in batch_ids]
+            stats.batches += 1
             # all prompts in one step, or in pieces whose last ones meet in one step
             t0 = time.perf_counter()
             uni = [uniform_for(seed, i, 0) for i in batch_ids]
             steps = plan_prefill_pieces([len(prompts[i]) for i in batch_ids], options.prefill_chunk_size)
-            for pieces in steps[:-1]:
-                engine.step([(slots[batch_ids[j]], prompts[batch_ids[j]][b:e]) for j, b, e in pieces], None)
-            toks = engine.step_and_choose([(slots[batch_ids[j]], prompts[batch_ids[j]][b:e]) for j, b, e in steps[-1]],
-                                          sampling, uni)
+            try:
+                for pieces in steps[:-1]:
+                    engine.step([(slots[batch_ids[j]], prompts[batch_ids[j]][b:e]) for j, b, e in pieces], None)
+                toks = engine.step_and_choose([(slots[batch_ids[j]], prompts[batch_ids[j]][b:e]) for j, b, e in steps[-1]],
+                                              sampling, uni)
+            except CacheError:
+                # an engine without `admit`, or one whose answer did not hold: this batch ends here,
+                # earlier batches keep their results and later ones still run
+                for i in batch_ids:
+                    reasons[i] = "capacity"
+                continue
             stats.prefill_seconds += time.perf_counter() - t0
             stats.prompt_tokens += sum(len(prompts[i]) for i in batch_ids)
             active = []
@@ -174,6 +204,18 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
             # then one token each, for the sequences that still run
             t0 = time.perf_counter()
             while active:
+                # only the sequences that have no room left end with "capacity" (a length limit reached,
+                # or no page left for the ones that need a new one); they give their pages back at once,
+                # and the others go on
+                ok = fits([(slots[i], 1) for i in active])
+                if not all(ok):
+                    for i, good in zip(active, ok):
+                        if not good:
+                            reasons[i] = "capacity"
+                            engine.free_slot(slots.pop(i))
+                    active = [i for i, good in zip(active, ok) if good]
+                    if not active:
+                        break
                 uni = [uniform_for(seed, i, len(out[i])) for i in active]
                 try:
                     toks = engine.step_and_choose([(slots[i], [out[i][-1]]) for i in active], sampling, uni)

@@ -9,7 +9,8 @@ from herbert_rs_b200.errors import CacheError, RequestError
 class FakeEngine:
     """Next token = (last token + 1) % 100; records every step; has `max_slots` slots."""
 
-    def __init__(self, max_slots=4, capacity=None):
+    def __init__(self, max_slots=4, capacity=None, pool=None, admits=True):
+        self.pool, self.admits = pool, admits
         self.max_slots = max_slots
         self.free = list(range(max_slots))
         self.steps = []
@@ -27,6 +28,19 @@ class FakeEngine:
         assert s not in self.free
         self.free.append(s)
         self.free.sort()
+        self.lengths[s] = 0
+
+    def admit(self, pairs):
+        """Per sequence a limit of `capacity` positions; all sequences together at most `pool` positions."""
+        used = sum(self.lengths[s] for s in range(self.max_slots) if s not in self.free)
+        out = []
+        for s, n in pairs:
+            good = (self.capacity is None or self.lengths[s] + n <= self.capacity) and \
+                   (self.pool is None or used + n <= self.pool)
+            if good:
+                used += n
+            out.append(good)
+        return out if self.admits else [True] * len(pairs)
 
     def step(self, entries, want):
         assert want is None
@@ -98,6 +112,43 @@ def test_running_out_of_cache_ends_with_capacity():
     e = FakeEngine(capacity=4)
     r = generate(e, [[1, 2]], hb.GenerationOptions(max_tokens=10), hb.SamplingParams(temperature=0.0))
     assert r.finish_reasons == ["capacity"] and r.tokens == [[3, 4, 5]]
+
+
+def test_only_the_sequence_that_runs_out_of_room_ends_with_capacity():
+    # a limit of 8 positions per sequence: the long prompt reaches it after two tokens, the short one goes on
+    e = FakeEngine(capacity=8)
+    r = generate(e, [[1, 2, 3, 4, 5, 6], [10]], hb.GenerationOptions(max_tokens=5), hb.SamplingParams(temperature=0.0))
+    assert r.finish_reasons == ["capacity", "max_tokens"]
+    assert r.tokens == [[7, 8, 9], [11, 12, 13, 14, 15]]
+    assert e.steps[3] == [(1, [13])]                 # the step after the long one left: the short one alone
+    assert e.free == [0, 1, 2, 3]
+    # the same without `admit`: the engine's error ends the whole batch (what an outside engine gets)
+    e = FakeEngine(capacity=8, admits=False)
+    r = generate(e, [[1, 2, 3, 4, 5, 6], [10]], hb.GenerationOptions(max_tokens=5), hb.SamplingParams(temperature=0.0))
+    assert r.finish_reasons == ["capacity", "capacity"] and e.free == [0, 1, 2, 3]
+
+
+def test_prompts_that_do_not_fit_together_wait_for_the_next_batch():
+    # 10 positions in all: prompts of 6 and 5 cannot start together; a prompt of 12 never fits
+    e = FakeEngine(pool=10)
+    r = generate(e, [[1, 2, 3, 4, 5, 6], [20, 21, 22, 23, 24], list(range(30, 42)), [50]],
+                 hb.GenerationOptions(max_tokens=2, ignore_eos=True), hb.SamplingParams(temperature=0.0))
+    assert r.tokens == [[7, 8], [25, 26], [], [51, 52]]
+    assert r.finish_reasons == ["max_tokens", "max_tokens", "capacity", "max_tokens"]
+    assert e.steps[0] == [(0, [1, 2, 3, 4, 5, 6]), (3, [50])]      # who fits goes along; order of results is the requests'
+    assert r.stats.batches == 2 and e.free == [0, 1, 2, 3]
+
+
+def test_a_prompt_step_that_overflows_keeps_the_earlier_batches():
+    class Tight(FakeEngine):
+        def step_and_choose(self, entries, params, uniforms):
+            if any(len(t) > 3 for _, t in entries):
+                raise CacheError("cache full")
+            return super().step_and_choose(entries, params, uniforms)
+    e = Tight(max_slots=1, admits=False)
+    r = generate(e, [[1, 2], [1, 2, 3, 4], [9]], hb.GenerationOptions(max_tokens=2), hb.SamplingParams(temperature=0.0))
+    assert r.tokens == [[3, 4], [], [10, 11]] and r.finish_reasons == ["max_tokens", "capacity", "max_tokens"]
+    assert e.free == [0]
 
 
 def test_uniforms_depend_on_request_and_step_not_on_batch():

@@ -19,9 +19,18 @@ def dev(t):
     return t.cuda()
 
 
-def close(got, ref, dtype, scale=1.0):
+def close(got, ref, dtype, scale=1.0, rowwise=False):
+    """|got - ref| <= tol * max(1, max|ref|); rowwise: <= tol * max|ref of that row| for every row, for
+    outputs whose rows differ in size and are far below 1 (attention over many keys)."""
     got, ref = got.detach().double().cpu(), ref.double().cpu()
-    tol = (2e-5 if dtype == torch.float32 else 1.2e-2) * scale * max(1.0, ref.abs().max().item())
+    rel = (2e-5 if dtype == torch.float32 else 1.2e-2) * scale
+    if rowwise:
+        err = (got - ref).abs().amax(dim=-1)
+        lim = rel * ref.abs().amax(dim=-1)
+        worst = int((err - lim).argmax())
+        assert (err <= lim).all(), f"row {worst}: max error {err[worst]:.3e} > {lim[worst]:.3e}"
+        return
+    tol = rel * max(1.0, ref.abs().max().item())
     err = (got - ref).abs().max().item()
     assert err <= tol, f"max error {err:.3e} > {tol:.3e}"
 
@@ -197,7 +206,7 @@ def test_attention_simt_prefill_and_decode_shapes(dtype, nh, nkv, hd, window):
         out = torch.empty(c["q"].shape, device="cuda", dtype=dtype)
         ops.attention_simt(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(c["tok_seq"]), dev(c["tok_pos"]),
                            dev(c["table"]), nh, nkv, hd, 16, c["scale"], window)
-        close(out, c["ref"], dtype)
+        close(out, c["ref"], dtype, rowwise=True)
 
 
 @pytest.mark.parametrize("dtype", DT)
@@ -212,7 +221,7 @@ def test_attention_finds_a_far_key_and_respects_the_windows_edge(dtype):
         out = torch.empty(c["q"].shape, device="cuda", dtype=dtype)
         ops.attention_simt(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(c["tok_seq"]), dev(c["tok_pos"]),
                            dev(c["table"]), nh, nkv, hd, 16, c["scale"], window)
-        close(out, c["ref"], dtype)
+        close(out, c["ref"], dtype, rowwise=True)
         b, _, h, kpos = sharp[0]
         target = c["vs"][b][kpos, h // 2]
         got = out[b].view(nh, hd)[h].float().cpu()
@@ -468,7 +477,7 @@ def test_attention_decode_kernel(nh, nkv, hd, window, nsplit):
     scratch = torch.full((ops.attention_decode_scratch_floats(len(lens), nh, hd, nsplit),), float("nan"), device="cuda")
     ops.attention_decode(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(torch.tensor(lens, dtype=torch.int32)),
                          dev(c["table"]), scratch, nh, nkv, hd, 64, nsplit, c["scale"], window)
-    close(out, c["ref"], torch.bfloat16)
+    close(out, c["ref"], torch.bfloat16, rowwise=True)
 
 
 @pytest.mark.parametrize("nh,nkv,window,nsplit,norm", [(8, 2, 0, 1, True), (8, 2, 0, 3, True), (4, 4, 100, 2, False),
@@ -531,7 +540,7 @@ def test_attention_decode_finds_a_far_key_and_the_windows_edge():
         scratch = torch.empty(ops.attention_decode_scratch_floats(2, nh, hd, nsplit), device="cuda")
         ops.attention_decode(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(torch.tensor(lens, dtype=torch.int32)),
                              dev(c["table"]), scratch, nh, nkv, hd, 64, nsplit, c["scale"], window)
-        close(out, c["ref"], torch.bfloat16)
+        close(out, c["ref"], torch.bfloat16, rowwise=True)
         b, _, h, kpos = sharp[0]
         target = c["vs"][b][kpos, h // (nh // nkv)]
         assert (((out[b].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit
@@ -641,7 +650,7 @@ def test_attention_prefill_kernel(nh, nkv, hd, window):
         pos0 = torch.tensor([n - q for n, q in zip(lens, qlens)], dtype=torch.int32)
         ops.attention_prefill(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
                               dev(c["table"]), len(lens), max(qlens), nh, nkv, hd, 64, c["scale"], window)
-        close(out, c["ref"], torch.bfloat16)
+        close(out, c["ref"], torch.bfloat16, rowwise=True)
 
 
 def test_attention_prefill_finds_a_far_key_and_the_windows_edge():
@@ -656,7 +665,7 @@ def test_attention_prefill_finds_a_far_key_and_the_windows_edge():
         pos0 = torch.tensor([600, 0], dtype=torch.int32)
         ops.attention_prefill(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
                               dev(c["table"]), 2, 500, nh, nkv, hd, 64, c["scale"], window)
-        close(out, c["ref"], torch.bfloat16)
+        close(out, c["ref"], torch.bfloat16, rowwise=True)
         b, qpos, h, kpos = sharp[0]
         row = (0 if b == 0 else 300) + qpos - int(pos0[b])
         target = c["vs"][b][kpos, h // (nh // nkv)]
@@ -713,14 +722,14 @@ def test_attention_prefill_tcgen05_kernel(nh, nkv, hd, window):
         ops.attention_prefill_tc(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
                                  dev(c["table"]), len(lens), max(qlens), nh, nkv, hd, 64, c["scale"], window)
         ops.check_kernel_errors()
-        close(out, c["ref"], torch.bfloat16)
+        close(out, c["ref"], torch.bfloat16, rowwise=True)
         # a longest prompt of 4,096 or more selects four threads per query row (head size 128); the
         # sequences here are shorter, so most query tiles are empty items that every warp must skip alike
         out.fill_(float("nan"))
         ops.attention_prefill_tc(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
                                  dev(c["table"]), len(lens), 4096, nh, nkv, hd, 64, c["scale"], window)
         ops.check_kernel_errors()
-        close(out, c["ref"], torch.bfloat16)
+        close(out, c["ref"], torch.bfloat16, rowwise=True)
 
 
 def test_attention_prefill_tcgen05_finds_a_far_key_and_the_windows_edge():
@@ -736,7 +745,7 @@ def test_attention_prefill_tcgen05_finds_a_far_key_and_the_windows_edge():
         ops.attention_prefill_tc(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(starts), dev(pos0),
                                  dev(c["table"]), 2, 500, nh, nkv, hd, 64, c["scale"], window)
         ops.check_kernel_errors()
-        close(out, c["ref"], torch.bfloat16)
+        close(out, c["ref"], torch.bfloat16, rowwise=True)
         b, qpos, h, kpos = sharp[0]
         row = (0 if b == 0 else 300) + qpos - int(pos0[b])
         target = c["vs"][b][kpos, h // (nh // nkv)]
@@ -755,7 +764,7 @@ def test_attention_decode_tcgen05_kernel(nh, nkv, window, nsplit):
     ops.attention_decode_tc(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(torch.tensor(lens, dtype=torch.int32)),
                             dev(c["table"]), scratch, nh, nkv, hd, 64, nsplit, c["scale"], window)
     ops.check_kernel_errors()
-    close(out, c["ref"], torch.bfloat16)
+    close(out, c["ref"], torch.bfloat16, rowwise=True)
 
 
 def test_attention_decode_tcgen05_finds_a_far_key_and_the_windows_edge():
@@ -771,7 +780,7 @@ def test_attention_decode_tcgen05_finds_a_far_key_and_the_windows_edge():
         ops.attention_decode_tc(dev(c["q"]), c["q"].shape[1], out, dev(c["k"]), dev(c["v"]), dev(torch.tensor(lens, dtype=torch.int32)),
                                 dev(c["table"]), scratch, nh, nkv, hd, 64, nsplit, c["scale"], window)
         ops.check_kernel_errors()
-        close(out, c["ref"], torch.bfloat16)
+        close(out, c["ref"], torch.bfloat16, rowwise=True)
         b, _, h, kpos = sharp[0]
         target = c["vs"][b][kpos, h // (nh // nkv)]
         assert (((out[b].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit

@@ -336,3 +336,32 @@ def test_the_bfloat16_bound_sees_one_dropped_key(model_dirs, plain, key):
         P.attention_scores = orig
     over = np.abs(got - wrong).max(axis=-1) > bound
     assert over.any() and not over[:key].any()        # rows before the dropped key cannot tell
+
+
+def test_a_full_cache_ends_only_the_sequence_that_needs_the_page(model_dirs):
+    """Three pages for two sequences: when no page is left, the one that needs a new page ends with
+    "capacity" and gives its pages back; the other goes on and generates what it generates alone.
+    A prompt that no empty cache could hold ends without a token and the next request still runs."""
+    rng = np.random.default_rng(31)
+    prompts = [random_ids(rng, 256, 100), random_ids(rng, 256, 10), random_ids(rng, 256, 120)]
+    opt = hb.GenerationOptions(max_tokens=20, ignore_eos=True)
+    sp = hb.SamplingParams(temperature=0.0)
+    eng = engine_for(model_dirs["A"], "float32", max_tokens=64 * 3, max_slots=2, max_seq_len=128)
+    res = hb.generate(eng, prompts, opt, sp)
+    alone = hb.generate(engine_for(model_dirs["A"], "float32", max_tokens=64 * 8, max_slots=1, max_seq_len=128), prompts, opt, sp)
+    # request 0: 100 + 20 positions, two pages: fits.  Request 1: a second page at position 64 is never needed.
+    assert res.finish_reasons[:2] == ["max_tokens", "max_tokens"] and res.tokens[:2] == alone.tokens[:2]
+    # request 2: 120 prompt tokens leave 8 positions under the limit of 128
+    assert res.finish_reasons[2] == "capacity" and res.tokens[2] == alone.tokens[2][:len(res.tokens[2])] and len(res.tokens[2]) == 9
+    eng.cache.check()
+    assert eng.cache.slots.free_count == 2 and eng.cache.free_pages() == 3
+    # pages, not the limit: two sequences of 60 tokens want a second page each after four tokens; one page is left
+    eng = engine_for(model_dirs["A"], "float32", max_tokens=64 * 3, max_slots=2)
+    two = [random_ids(rng, 256, 60), random_ids(rng, 256, 60)]
+    res = hb.generate(eng, two, opt, sp)
+    one = hb.generate(engine_for(model_dirs["A"], "float32", max_tokens=64 * 8, max_slots=1), two, opt, sp)
+    assert res.finish_reasons == ["max_tokens", "capacity"]
+    assert res.tokens[0] == one.tokens[0] and res.tokens[1] == one.tokens[1][:5]
+    eng.cache.check()
+    too_long = hb.generate(eng, [random_ids(rng, 256, 64 * 3 + 1), [5, 6]], opt, sp)
+    assert too_long.finish_reasons == ["capacity", "max_tokens"] and too_long.tokens[0] == [] and len(too_long.tokens[1]) == 20
