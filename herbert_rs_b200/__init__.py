@@ -19,6 +19,7 @@ from .engine.engine import Engine
 from .engine.generate import (GenerationOptions, GenerationResult, GenerationStats,
                               detect_repetition_loop, generate)
 from .engine.runtime import Runtime
+from .models.decoder import DecoderModel
 from .errors import (BackendError, CacheError, ConfigError, HerbertError, RequestError,
                      SafeTensorsError, WeightError)
 from .registry import (architectures, build_part, config_from_json, register_architecture,
@@ -30,7 +31,7 @@ __version__ = "0.1.0"
 
 __all__ = [
     "Engine", "generate", "GenerationOptions", "GenerationResult", "GenerationStats", "SamplingParams",
-    "Qwen3Config", "read_config_json", "Runtime", "load_model", "random_model", "write_random_model",
+    "Qwen3Config", "read_config_json", "Runtime", "DecoderModel", "load_model", "random_model", "write_random_model",
     "register_architecture", "register_part", "build_part", "config_from_json", "architectures",
     "BACKENDS", "available_backends_help", "resolve_backend", "detect_repetition_loop",
     "HerbertError", "ConfigError", "WeightError", "SafeTensorsError", "CacheError", "BackendError",

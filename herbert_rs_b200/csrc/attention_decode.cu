@@ -66,15 +66,14 @@ struct DecodeFuse {
 };
 
 // HDM: the largest head size this instantiation holds in registers (hd <= HDM, hd % 16 == 0).
-// EXACT: hd == HDM is known at compile time, so every size test and stride folds away.
-template <int HDM, bool EXACT>
+template <int HDM>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   pdl_wait();
   pdl_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int hd = EXACT ? HDM : a.hd, G = a.nh / a.nkv;
+  const int hd = a.hd, G = a.nh / a.nkv;
   const int row_bytes = hd * 2 + 16;                 // padded: conflict-free ldmatrix for any hd % 16 == 0
   const int tile_bytes = AD_TILE * row_bytes;
   const int chunks_per_row = hd >> 3;
@@ -643,38 +642,14 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
   }
 }
 
-// Second stage alone, for kernels that write the same (m, l, o) partials (m in natural-log units).
-int hb_attention_decode_combine(const float* part_o, const float* part_ml, void* out, int ldo, int n_seqs, int nh, int hd,
-                                int nsplit, cudaStream_t s) {
-  dim3 cgrid(nh, n_seqs);
-  hb_launch(attention_decode_combine_kernel, dim3(cgrid), dim3(hd >= 128 ? 128 : 64), 0, s, part_o, part_ml, (bf16*)out, ldo, nh, hd, nsplit);
-  HB_CHECK_LAUNCH("attention_decode_combine");
-  return 0;
-}
-
-static bool use_old_layout() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("HB_DECODE_HEADS_AS_M");     // tuning knob: 1 = the first kernel (query heads as the M side) also for head size 128
-    v = (e && e[0] == '1') ? 1 : 0;
-  }
-  return v == 1;
-}
-
 static int decode_smem_bytes(int hd, int stages) {
   const int pipeline = stages * 2 * AD_TILE * (hd * 2 + 16);
   const int merge = (2 * AD_WARPS * 16 + AD_WARPS * 16 * hd) * 4;
   return pipeline > merge ? pipeline : merge;
 }
 
-static int decode_stages(int hd) {
-  static int want_stages = 0;
-  if (want_stages == 0) {
-    const char* e = getenv("HB_DECODE_STAGES");      // tuning knob: 2 or 3 (default 3 where it fits twice per SM)
-    want_stages = (e && (e[0] == '2' || e[0] == '3')) ? e[0] - '0' : 3;
-  }
-  return decode_smem_bytes(hd, want_stages) > 110 * 1024 ? 2 : want_stages;
-}
+// Three stages of key/value tiles where two CTAs of that size still share an SM, else two.
+static int decode_stages(int hd) { return decode_smem_bytes(hd, 3) > 110 * 1024 ? 2 : 3; }
 
 extern "C" long long hb_attention_decode_scratch_floats(int n_seqs, int nh, int hd, int nsplit) {
   return (long long)n_seqs * nh * nsplit * (hd + 2);
@@ -706,10 +681,10 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
   dim3 grid(nsplit, nkv, n_seqs);
   cudaError_t e;
   if (hd <= 64) {
-    e = cudaFuncSetAttribute(attention_decode_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_kernel<64, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
-  } else if (hd == 128 && !use_old_layout()) {
+    hb_launch(attention_decode_kernel<64>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+  } else if (hd == 128) {
     if (nh / nkv <= 8) {
       e = cudaFuncSetAttribute(attention_decode_km_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -719,18 +694,14 @@ extern "C" int hb_attention_decode_bf16(const void* q, int ldq, void* out, int l
       if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
       hb_launch(attention_decode_km_kernel<2, false>, dim3(grid), dim3(AD_THREADS), smem, s, a, DecodeFuse{});
     }
-  } else if (hd == 128) {
-    e = cudaFuncSetAttribute(attention_decode_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_kernel<128, true>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   } else if (hd < 128) {
-    e = cudaFuncSetAttribute(attention_decode_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_kernel<128, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+    hb_launch(attention_decode_kernel<128>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   } else {
-    e = cudaFuncSetAttribute(attention_decode_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(attention_decode_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_kernel<256, false>, dim3(grid), dim3(AD_THREADS), smem, s, a);
+    hb_launch(attention_decode_kernel<256>, dim3(grid), dim3(AD_THREADS), smem, s, a);
   }
   HB_CHECK_LAUNCH("attention_decode");
   dim3 cgrid(nh, n_seqs);

@@ -19,7 +19,6 @@
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
-#define HB_EPI_SWIGLU 3
 #define SK_NORM_ROWS 16
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
@@ -248,20 +247,9 @@ static int skinny_launch(const bf16* A, int lda, const bf16* W, int ldw, void* C
 }
 
 // epi HB_EPI_SWIGLU: W holds 2I rows in groups of 16 (8 gate, 8 up); C is [M, I] bfloat16.
-static int skinny_rg_knob() {
-  static int rg_knob = -1;
-  if (rg_knob < 0) {
-    const char* e = getenv("HB_SKINNY_RG");        // tuning knob: 1 or 2 row groups per CTA; default by shape
-    rg_knob = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
-  }
-  return rg_knob;
-}
 // Two row groups per CTA halve the activation traffic; worth it once there are several tokens
 // and enough rows that the grid still fills the GPU.
-static bool skinny_two_groups(int M, int N) {
-  const int k = skinny_rg_knob();
-  return M <= 16 && (k ? k == 2 : (M > 1 && N >= 8192));
-}
+static bool skinny_two_groups(int M, int N) { return M <= 16 && M > 1 && N >= 8192; }
 
 extern "C" int hb_gemm_skinny_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
                                    int K, int epi, void* stream) {

@@ -25,7 +25,6 @@
 #define GS_THREADS 192
 #define GS_W_BYTES (GS_BM * TG_BK * 2)
 #define GS_MAX_NP 64
-#define HB_EPI_SWIGLU 3
 
 __device__ __forceinline__ void tc_ld16(unsigned taddr, float* r) {
   unsigned u[16];
@@ -238,12 +237,7 @@ static StreamPlan stream_plan(int M, int N, int K) {
   p.tiles = ceil_div(N, GS_BM);
   const int num_kb = ceil_div(K, TG_BK);
   const int slots = stream_sm_count() * 2;
-  static int max_slices = 0;
-  if (max_slices == 0) {
-    const char* e = getenv("HB_STREAM_MAX_SLICES");      // tuning knob
-    max_slices = e ? atoi(e) : 2;        // measured: more slices cost more in the ordered reduction than they gain
-    if (max_slices < 1) max_slices = 1;
-  }
+  const int max_slices = 2;        // measured: more slices cost more in the ordered reduction than they gain
   int s = slots / p.tiles;
   if (s > max_slices) s = max_slices;
   if (s > num_kb / 2) s = num_kb / 2;             // at least two k blocks per slice

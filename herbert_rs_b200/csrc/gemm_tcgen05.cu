@@ -23,7 +23,6 @@
 
 #define TG_BM 128
 #define TG_THREADS 192
-#define HB_EPI_SWIGLU 3
 
 template <int BN>
 struct TgSmem {

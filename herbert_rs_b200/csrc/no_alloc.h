@@ -14,6 +14,9 @@
 //    (n_seqs * nh * nsplit * (hd + 2) floats) is refused with a message, nothing is launched;
 //  * the first call on a device looks up the array's device address (cudaGetSymbolAddress) with
 //    that device current; make that first call outside any stream capture;
+//  * the array's address is looked up and kept per device under the device that is current at the
+//    call: the stream must belong to the current device, and first calls on a device that come
+//    from several host threads at once must be serialised by the caller (later calls only read);
 //  * no cudaMalloc, cudaFree or other allocating routine is called, here or in what it launches;
 //  * all calls share the one array, which keeps whatever the previous call left.  Nothing in it
 //    has to start at zero: the kernels write every partial result they later read.  Two calls

@@ -9,20 +9,20 @@ computes on the CPU and nothing falls back to a library model or attention routi
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
 
 from ..errors import BackendError
 from . import lib as _libmod
+from .options import KernelOptions
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64
-# Which kernel serves products of at most 64 activation rows: "stream" (TMA + tcgen05, K slices),
-# "skinny" (mma.sync with direct global loads), or "auto" (by shape, see _decode_gemm).
-DECODE_GEMM = os.environ.get("HB_DECODE_GEMM", "auto")
+# The one place where a choice between kernels can be changed (by a measurement script or a test
+# that assigns its fields); nothing reads the environment.
+options = KernelOptions()
 
 _SIGS = {
     "hb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -55,8 +55,6 @@ _SIGS = {
     "hb_attention_prefill_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
                                      c_void_p],
-    "hb_attention_decode_tc_bf16": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                                    c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "hb_argmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     "hb_gemm_skinny_norm_parts": [c_int, c_int],
     "hb_sample": [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -71,8 +69,6 @@ def _fn(name: str):
     f = _fns.get(name)
     if f is None:
         lib = _libmod.load()
-        if not _fns and "HB_PDL" in os.environ:
-            lib.hb_set_pdl(int(os.environ["HB_PDL"]))
         try:
             f = getattr(lib, name)
         except AttributeError:
@@ -84,7 +80,7 @@ def _fn(name: str):
 
 
 # kernels each launcher starts (for honest launch counts)
-_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_attention_decode_tc_bf16": 2, "hb_argmax": 2, "hb_sample": 2}
+_KERNELS_PER_CALL = {"hb_attention_decode_bf16": 2, "hb_argmax": 2, "hb_sample": 2}
 _launches = 0
 
 
@@ -113,6 +109,12 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise BackendError(f"unsupported activation dtype {dtype}: float32 or bfloat16")
 
 
+def device_key(device) -> str:
+    """One name per CUDA device ("cuda:0"), whether it was given with or without its index."""
+    d = torch.device(device)
+    return f"cuda:{d.index if d.index is not None else torch.cuda.current_device()}"
+
+
 def _ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
 
@@ -124,6 +126,12 @@ def _check(t: torch.Tensor, dtype, name: str) -> None:
         raise BackendError(f"{name} must be {dtype}, got {t.dtype}")
     if t.dim() > 0 and t.stride(-1) != 1:
         raise BackendError(f"{name} must be contiguous along its last axis")
+
+
+def set_pdl(mode: int) -> None:
+    """Programmatic dependent launch: 0 off (default: inside captured decode graphs it measured
+    slower), 1 every kernel, 2 only the launches that ask for it."""
+    _libmod.load().hb_set_pdl(int(mode))
 
 
 def is_available() -> bool:
@@ -232,7 +240,7 @@ ARGMAX_SCRATCH_ROWS = 4096
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = index of the first maximum of row r."""
     _check(logits, torch.float32, "logits"); _check(out, torch.int32, "out")
-    key = str(logits.device)
+    key = device_key(logits.device)
     if key not in _argmax_scratch:
         _argmax_scratch[key] = torch.empty(2 * 64 * ARGMAX_SCRATCH_ROWS, dtype=torch.int32, device=logits.device)
     sc = _argmax_scratch[key]
@@ -248,7 +256,7 @@ def sample(logits, temperature, top_k, top_p, uniforms, out) -> None:
     against a large vocabulary takes a kernel that reads the row twice and works on a list of
     candidates in shared memory; rows it cannot hold fall to the general kernel in the same call."""
     _check(logits, torch.float32, "logits"); _check(uniforms, torch.float32, "uniforms"); _check(out, torch.int32, "out")
-    key = str(logits.device)
+    key = device_key(logits.device)
     if key not in _sample_flags or _sample_flags[key].numel() < logits.shape[0]:
         _sample_flags[key] = torch.zeros(max(1024, logits.shape[0]), dtype=torch.int32, device=logits.device)
     _run("hb_sample", logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], float(temperature),
@@ -264,7 +272,6 @@ def gemm_skinny(a, w, c, epilogue=EPI_STORE) -> None:
 
 
 SHARED_NORM_MAX_ROWS = 16
-SHARED_NORM = os.environ.get("HB_SHARED_NORM", "1") != "0"     # 0: every norm is a kernel of its own
 
 
 class PendingNorm:
@@ -289,7 +296,7 @@ def shared_norm_ok(n_rows: int, dtype, dim: int) -> bool:
     """Whether products of `n_rows` activation rows can carry a norm over `dim` between them: the
     mma.sync kernel can for at most 16 rows, the tensor-memory kernel for any number; between 17
     and 64 rows a product that goes through another kernel leaves the norm to a kernel of its own."""
-    return SHARED_NORM and dtype == torch.bfloat16 and dim % 8 == 0
+    return options.shared_norm and dtype == torch.bfloat16 and dim % 8 == 0
 
 
 def finish_norm(p: PendingNorm, out: torch.Tensor) -> None:
@@ -329,7 +336,7 @@ _error_flags: dict = {}
 
 def _error_flag(device) -> torch.Tensor:
     """One int per device that kernels with bounded waits set when a wait runs out."""
-    key = str(device)
+    key = device_key(device)
     if key not in _error_flags:
         _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _error_flags[key]
@@ -353,17 +360,16 @@ def check_kernel_errors() -> None:
             raise BackendError(f"a kernel on {key} gave up waiting on a barrier (code {code}); its output is not valid")
 
 
-PREFILL_SPLIT_TILES = os.environ.get("HB_PREFILL_SPLIT_TILES", "1") != "0"   # 0: every output tile by one CTA
 _tcgen05_ws: dict = {}
 
 
 def _tcgen05_workspace(device) -> None:
     """Once per device: hand the prefill product the workspace in which CTAs that share an output
     tile leave their pieces (about 39 MB on 148 SMs)."""
-    key = str(device)
+    key = device_key(device)
     if key in _tcgen05_ws:
         return
-    if not PREFILL_SPLIT_TILES:
+    if not options.prefill_split_tiles:
         _tcgen05_ws[key] = None
         return
     sms = torch.cuda.get_device_properties(device).multi_processor_count
@@ -388,7 +394,6 @@ def gemm_tcgen05(a, w, c, epilogue=EPI_STORE) -> None:
 
 
 _stream_bufs: dict = {}
-STREAM_SCRATCH_FLOATS = 296 * 64 * 128     # most (tile, slice) pairs a call cuts K into, at 64 padded rows
 STREAM_COUNTERS = 8192
 
 
@@ -421,9 +426,10 @@ def gemm_tcgen05_norm(a, w, c, epilogue=EPI_STORE, next_norm=None, scratch=None)
 def _stream_buffers(device):
     """Per device: scratch for the K slices' partial tiles and the tiles' arrival counters (zero
     between launches).  Fixed addresses, so captured graphs can use them."""
-    key = str(device)
+    key = device_key(device)
     if key not in _stream_bufs:
-        _stream_bufs[key] = (torch.empty(STREAM_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+        # K is cut into slices only while (tiles x slices) fits two CTAs per SM: that many partial tiles of 64 x 128 floats
+        _stream_bufs[key] = (torch.empty(2 * sm_count(device) * 64 * 128, dtype=torch.float32, device=device),
                              torch.zeros(STREAM_COUNTERS, dtype=torch.int32, device=device))
     return _stream_bufs[key]
 
@@ -455,10 +461,10 @@ def _decode_gemm(a, w):
     Up to 16 rows the mma.sync kernel streams the weights at the memory's rate; beyond that every CTA
     of 16 weight rows reads the whole activation matrix again, and the prefill kernel wins wherever
     the matrix is large enough to pay for its start and end.  The streaming kernel keeps the head."""
-    if DECODE_GEMM == "stream":
+    if options.decode_gemm == "stream":
         return gemm_stream
     M, N, K = a.shape[0], w.shape[0], a.shape[1]
-    if DECODE_GEMM == "auto" and M > 16:
+    if options.decode_gemm == "auto" and M > 16:
         elements = N * K
         if N >= 65536:
             return gemm_stream
@@ -529,16 +535,27 @@ def gemm_swiglu(a, wgu: torch.Tensor, out: torch.Tensor, interleave: int, scratc
     swiglu(gu, out, interleave)
 
 
-DECODE_TARGET_CTAS = int(os.environ.get("HB_DECODE_CTAS", "296"))   # two resident CTAs on each of the 148 SMs: one wave
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once per device)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = device_key(dev)
+    if key not in _sm_counts:
+        _sm_counts[key] = int(torch.cuda.get_device_properties(dev).multi_processor_count)
+    return _sm_counts[key]
 
 
 def attention_decode_scratch_floats(n_seqs, num_heads, head_dim, nsplit) -> int:
     return n_seqs * num_heads * nsplit * (head_dim + 2)
 
 
-def decode_splits(n_seqs: int, num_kv_heads: int, max_tiles: int) -> int:
-    """How many key ranges each (sequence, kv head) is cut into, so that the grid fills the GPU."""
-    want = DECODE_TARGET_CTAS // max(1, n_seqs * num_kv_heads)      # rounded down: all CTAs resident at once
+def decode_splits(n_seqs: int, num_kv_heads: int, max_tiles: int, device=None) -> int:
+    """How many key ranges each (sequence, kv head) is cut into, so that the grid fills the GPU:
+    `options.decode_ctas_per_sm` CTAs on every SM, one wave."""
+    target = options.decode_ctas_per_sm * sm_count(device)
+    want = target // max(1, n_seqs * num_kv_heads)      # rounded down: all CTAs resident at once
     return max(1, min(want, max_tiles, 64))
 
 
@@ -554,14 +571,13 @@ def attention_decode(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch,
          n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit), float(scale), int(window or 0), _stream())
 
 
-DECODE_FUSED = os.environ.get("HB_DECODE_FUSED", "1") != "0"   # 0: norm/rotation/cache write, attention and combine as separate kernels
 _DECODE_COUNTERS = 65536
 _decode_counters: dict = {}
 
 
 def attention_decode_fused_ok(qkv, out, num_heads, num_kv_heads, head_dim, page_size, rotary_dim, n_seqs) -> bool:
     """Whether one launch can do norm, rotation, cache write, attention and combine for this step."""
-    return (DECODE_FUSED and DECODE_ATTENTION == "mma" and out.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
+    return (options.decode_fused and out.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16
             and head_dim == 128 and rotary_dim == head_dim and num_heads // num_kv_heads <= 16 and page_size % 64 == 0
             and qkv.stride(0) % 4 == 0 and qkv.data_ptr() % 8 == 0 and n_seqs * num_kv_heads <= _DECODE_COUNTERS)
 
@@ -574,7 +590,7 @@ def attention_decode_fused(qkv, out, k_cache, v_cache, q_weight, k_weight, eps, 
     n = out.shape[0]
     if scratch.numel() < attention_decode_scratch_floats(n, num_heads, 128, nsplit):
         raise BackendError("attention_decode_fused: scratch is too small")
-    key = str(out.device)
+    key = device_key(out.device)
     if key not in _decode_counters:
         _decode_counters[key] = torch.zeros(_DECODE_COUNTERS, dtype=torch.int32, device=out.device)
     _run("hb_attention_decode_fused_bf16", qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0),
@@ -611,44 +627,19 @@ _work_counters: dict = {}
 def _work_counter(device) -> torch.Tensor:
     """One int per device from which the CTAs of a persistent kernel take their next item of work
     (the launcher zeroes it on the stream before the kernel)."""
-    key = str(device)
+    key = device_key(device)
     if key not in _work_counters:
         _work_counters[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _work_counters[key]
 
 
-PREFILL_ATTENTION = os.environ.get("HB_PREFILL_ATTENTION", "tcgen05")   # or "mma": the mma.sync kernel for every size
-
-
 def _prefill_tc_ok(q, ldq, out, head_dim, page_size) -> bool:
-    return (PREFILL_ATTENTION == "tcgen05" and out.dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 64 == 0
+    return (options.prefill_attention == "tcgen05" and out.dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 64 == 0
             and ldq % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
 def _prefill_kernel_ok(out, head_dim, page_size) -> bool:
     return out.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and page_size % 64 == 0
-
-
-def attention_decode_tc(q, ldq, out, k_cache, v_cache, seq_len, seq_pages, scratch, num_heads, num_kv_heads,
-                        head_dim, page_size, nsplit, scale, window) -> None:
-    """The same on tcgen05 tensor cores (head size 128): keys as the M side, S^T and O^T in tensor memory."""
-    _check(out, torch.bfloat16, "out"); _check(scratch, torch.float32, "scratch")
-    n = out.shape[0]
-    if scratch.numel() < attention_decode_scratch_floats(n, num_heads, head_dim, nsplit):
-        raise BackendError("attention_decode_tc: scratch is too small")
-    _run("hb_attention_decode_tc_bf16", q.data_ptr(), int(ldq), q.shape[0], out.data_ptr(), out.stride(0),
-         k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[0], seq_len.data_ptr(), seq_pages.data_ptr(),
-         seq_pages.stride(0), scratch.data_ptr(), n, num_heads, num_kv_heads, head_dim, page_size, int(nsplit),
-         float(scale), int(window or 0), _error_flag(out.device).data_ptr(), _stream())
-
-
-DECODE_ATTENTION = os.environ.get("HB_DECODE_ATTENTION", "mma")    # "tcgen05": the tensor-memory kernel (head 128); measured slower, see profiles/
-DECODE_TC_TARGET_CTAS = int(os.environ.get("HB_DECODE_TC_CTAS", "148"))   # one CTA per SM (200 KB of shared memory each)
-
-
-def _decode_tc_ok(q, ldq, out, num_heads, num_kv_heads, head_dim, page_size) -> bool:
-    return (DECODE_ATTENTION == "tcgen05" and out.dtype == torch.bfloat16 and head_dim == 128 and ldq % 128 == 0
-            and num_heads // num_kv_heads <= 16 and page_size % 64 == 0 and q.data_ptr() % 16 == 0)
 
 
 def _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size) -> bool:
@@ -663,13 +654,6 @@ def attention(q, ldq, out, k_cache, v_cache, batch, num_heads, num_kv_heads, hea
     bfloat16 steps of one token per sequence take the split-key tensor-core kernel, other bfloat16
     steps the flash kernel; head sizes or pages those cannot serve, and the float32 path, take
     the any-shape kernel."""
-    if batch.is_decode and scratch is not None and _decode_tc_ok(q, ldq, out, num_heads, num_kv_heads, head_dim, page_size):
-        tiles = -(-seq_pages.shape[1] * page_size // 128)
-        nsplit = max(1, min(DECODE_TC_TARGET_CTAS // max(1, batch.n_seqs * num_kv_heads), tiles, 64))
-        buf = scratch((attention_decode_scratch_floats(batch.n_seqs, num_heads, head_dim, nsplit),), torch.float32)
-        attention_decode_tc(q, ldq, out, k_cache, v_cache, batch.seq_len, seq_pages, buf, num_heads, num_kv_heads,
-                            head_dim, page_size, nsplit, scale, window)
-        return
     if batch.is_decode and scratch is not None and _decode_kernel_ok(out, num_heads, num_kv_heads, head_dim, page_size):
         tiles = seq_pages.shape[1] * (page_size // 64)
         nsplit = decode_splits(batch.n_seqs, num_kv_heads, tiles)

@@ -365,3 +365,26 @@ def test_a_full_cache_ends_only_the_sequence_that_needs_the_page(model_dirs):
     eng.cache.check()
     too_long = hb.generate(eng, [random_ids(rng, 256, 64 * 3 + 1), [5, 6]], opt, sp)
     assert too_long.finish_reasons == ["capacity", "max_tokens"] and too_long.tokens[0] == [] and len(too_long.tokens[1]) == 20
+
+
+def test_a_kernel_that_gave_up_is_reported_and_the_counters_start_afresh(model_dirs, plain):
+    """The failure path of the bounded waits, made on the host: a non-zero error flag and arrival
+    counters left mid-count (what a kernel that gave up leaves behind).  The check raises, clears
+    the flag and every counter table, and the next steps are right again.  Nothing on the GPU waits
+    or faults for this."""
+    from herbert_rs_b200 import ops
+    eng = engine_for(model_dirs["D"], "bfloat16")
+    ids = random_ids(np.random.default_rng(41), 1000, 200)
+    ref = plain["D"].logits(ids).numpy()
+    assert_close(replay_tail_one_by_one(eng, ids, 8), ref, "bfloat16", "before", plain=plain["D"], ids=ids)   # every counter table exists now
+    dev = ops.device_key(eng.rt.device)
+    tables = [ops._decode_counters[dev], ops._tcgen05_ws[dev][1], ops._stream_buffers(eng.rt.device)[1]]
+    for t in tables:
+        t.fill_(3)
+    ops._error_flag(eng.rt.device).fill_(7)
+    with pytest.raises(hb.BackendError, match="gave up waiting on a barrier .code 7."):
+        eng.check_kernels()
+    assert int(ops._error_flag(eng.rt.device).item()) == 0 and all(int(t.abs().sum().item()) == 0 for t in tables)
+    eng.check_kernels()
+    assert_close(replay_tail_one_by_one(eng, ids, 8), ref, "bfloat16", "after", plain=plain["D"], ids=ids)
+    assert_close(replay_whole(eng, ids), ref, "bfloat16", "after, whole", plain=plain["D"], ids=ids)

@@ -397,6 +397,136 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(tmp_path, dtype):
     assert np.abs(_routed_plain(w, cfg2, reqs[0])[0] - refs[0]).max() > 1e-3
 
 
+# ---- an architecture with a model class of its own and two numbers per token position ---------------
+@dataclass(frozen=True)
+class GridMixerSpec:
+    hidden_size: int
+    rows: int
+    cols: int
+    kind: str = "toy_grid"
+
+
+class GridMixer(Mixer):
+    """out[t] = h[t] Wv^T + row_table[position component 0] + col_table[position component 1]: a mixer
+    whose position encoding takes two numbers per token and that keeps nothing in the cache."""
+
+    def __init__(self, spec, rt):
+        self.spec = spec
+
+    def param_specs(self):
+        s = self.spec
+        return {"v.weight": ParamSpec((s.hidden_size, s.hidden_size)), "row.weight": ParamSpec((s.rows, s.hidden_size)),
+                "col.weight": ParamSpec((s.cols, s.hidden_size))}
+
+    def load(self, tensors):
+        self.wv, self.row, self.col = (tensors[n].float() for n in ("v.weight", "row.weight", "col.weight"))
+
+    def forward(self, h, residual, batch, cache):
+        pos = batch.positions.long()                       # [components, T], on the device
+        residual += h.float() @ self.wv.T + self.row[pos[0]] + self.col[pos[1]]
+
+
+class CappedLogitsModel(hb.DecoderModel):
+    """A top level that differs from the generic decoder's: the embedding is scaled and the logits
+    are squashed, both by constants of the spec's `extra`."""
+
+    def load_embedding(self, t):
+        super().load_embedding(t)
+        self.embed = (self.embed.float() * self.spec.extra["embed_scale"]).to(self.embed.dtype)
+
+    def forward(self, batch, cache):
+        logits = super().forward(batch, cache)
+        if logits is not None:
+            cap = self.spec.extra["logit_cap"]
+            logits.copy_(torch.tanh(logits / cap) * cap)
+        return logits
+
+
+@dataclass(frozen=True)
+class GridConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    rows: int
+    cols: int
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(*(d[k] for k in ("vocab_size", "hidden_size", "intermediate_size", "rows", "cols")))
+
+    def to_dict(self):
+        return dict(architectures=["ToyGridForCausalLM"], **self.__dict__)
+
+    def model_spec(self):
+        H = self.hidden_size
+        norm = NormSpec(H, 1e-6)
+        att = AttentionSpec(H, 4, 2, 32, scale=32 ** -0.5, qk_norm=NormSpec(32, 1e-6), position=PositionSpec(32, 32, 1e4, self.rows))
+        names = (("norm1", "input_layernorm"), ("mixer", "grid"), ("norm2", "post_attention_layernorm"), ("ffn", "mlp"))
+        blocks = (BlockSpec(mixer=att, ffn=SwiGLUSpec(H, self.intermediate_size), norm1=norm, norm2=norm),
+                  BlockSpec(mixer=GridMixerSpec(H, self.rows, self.cols), ffn=SwiGLUSpec(H, self.intermediate_size),
+                            norm1=norm, norm2=norm, names=names))
+        return ModelSpec("ToyGridForCausalLM", self.vocab_size, H, blocks, (ScheduleStep(0), ScheduleStep(1)), norm, False,
+                         self.rows, position_components=2, extra={"embed_scale": 2.0, "logit_cap": 0.5})
+
+
+def _grid_plain(w, cfg, ids, cols):
+    T = len(ids)
+    acfg = dict(nh=4, nkv=2, hd=32, eps=1e-6, rot=32, scale=32 ** -0.5, windows=[None, None])
+    cos, sin = P.rope_tables(32, 1e4, T, torch.float64)
+    x = P.embedding(w["model.embed_tokens.weight"], ids, torch.float64)
+    x = x * 2.0                                           # exact in bfloat16 too: a power of two
+    x = P.decoder_layer(x, w, 0, acfg, cos, sin)
+    p = "model.layers.1."
+    n1 = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6)
+    x = x + n1 @ w[p + "grid.v.weight"].double().T + w[p + "grid.row.weight"].double()[torch.arange(T)] \
+        + w[p + "grid.col.weight"].double()[torch.tensor(cols)]
+    x = x + P.swiglu_mlp(P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-6), w, p + "mlp.")
+    logits = P.linear(P.rms_norm(x, w["model.norm.weight"], 1e-6), w["lm_head.weight"])
+    return (torch.tanh(logits / 0.5) * 0.5).numpy()
+
+
+def test_an_architecture_with_its_own_model_class_and_two_position_components(tmp_path):
+    """Registered from here: a configuration, a model class (scaled embedding, capped logits), and a
+    mixer that reads two numbers per token position.  The second component is given by the caller,
+    or defaults to the token's index; decode steps bump both and replay from a CUDA graph."""
+    hb.register_part("mixer", "toy_grid", GridMixer)
+    hb.register_architecture("ToyGridForCausalLM", GridConfig, model_cls=CappedLogitsModel)
+    cfg = dict(architectures=["ToyGridForCausalLM"], vocab_size=120, hidden_size=64, intermediate_size=96, rows=200, cols=200)
+    d = hb.write_random_model(cfg, str(tmp_path / "grid"), seed=12)
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    eng = engine_for(d, "float32", max_tokens=64 * 6, max_slots=3)
+    assert type(eng.model) is CappedLogitsModel and eng.model.spec.position_components == 2
+    rng = np.random.default_rng(5)
+    a, b = random_ids(rng, 120, 50), random_ids(rng, 120, 9)
+    cols_a, cols_b = [int(c) for c in rng.integers(0, 200, 50)], [int(c) for c in rng.integers(0, 200, 9)]
+    pos = lambda cols, lo, hi: np.stack([np.zeros(hi - lo, dtype=np.int64), np.asarray(cols[lo:hi])], axis=1)
+    sa, sb = eng.alloc_slot(), eng.alloc_slot()
+    got = to_np(eng.step([(sa, a[:40]), (sb, b[:5])], "all", positions=[pos(cols_a, 0, 40), pos(cols_b, 0, 5)]))
+    ref_a, ref_b = _grid_plain(w, cfg, a, cols_a), _grid_plain(w, cfg, b, cols_b)
+    assert_close(got[:40], ref_a[:40], "float32", "grid prompt a")
+    assert_close(got[40:], ref_b[:5], "float32", "grid prompt b")
+    for t in range(4):          # one token each, positions given
+        got = to_np(eng.step([(sa, [a[40 + t]]), (sb, [b[5 + t]])], "all", positions=[pos(cols_a, 40 + t, 41 + t), pos(cols_b, 5 + t, 6 + t)]))
+        assert_close(got, np.stack([ref_a[40 + t], ref_b[5 + t]]), "float32", f"grid decode {t}")
+    eng.free_slot(sa); eng.free_slot(sb)
+    with pytest.raises(hb.RequestError, match="positions of a sequence of 3 tokens"):
+        s = eng.alloc_slot()
+        eng.step([(s, [1, 2, 3])], "all", positions=[np.zeros((3, 3), dtype=np.int64)])
+    eng.free_slot(s)
+    # no positions given: the second component is the index too; generation's decode steps replay a graph
+    ids = random_ids(rng, 120, 60)
+    ref = _grid_plain(w, cfg, ids, list(range(60)))
+    assert_close(replay_tail_one_by_one(eng, ids, 20), ref, "float32", "grid default positions")
+    res = hb.generate(eng, [ids[:30], ids[:7]], hb.GenerationOptions(max_tokens=12, ignore_eos=True), hb.SamplingParams(temperature=0.0))
+    for p0, toks in zip((ids[:30], ids[:7]), res.tokens):
+        seq = list(p0)
+        for tok in toks:
+            r = _grid_plain(w, cfg, seq, list(range(len(seq))))[-1]
+            assert r.max() - r[tok] <= 1e-5
+            seq.append(tok)
+    assert eng.graph_replays > 0 and eng.fast_decode_steps > 0
+
+
 # ---- the order of layers is data -----------------------------------------------------------------
 @dataclass(frozen=True)
 class LoopedConfig(hb.Qwen3Config):
