@@ -8,8 +8,14 @@ A "step" is one decode step of a batch of sequences that were prefilled to --pro
 `value` is decoded tokens per second of K steps timed on the device (CUDA events, after W warm-up
 steps); every step reads all weights (about 15 GB, far larger than the 126 MB L2), so no flush is
 needed between steps.  `e2e` is the same through the Python entry point with host tokens in and
-out of every step.  `prefill` times one 2,048-token prompt; `points` holds decode at batch 1 and
-64.  One JSON line goes to standard output.
+out of every step, over at least 64 steps that follow an untimed round (which holds the capture of
+the step's CUDA graph).  `prefill` times one 2,048-token prompt through `Engine.step` (host packing
+and upload included); `points` holds decode at batch 1 and 64 and, unless --no-workloads, the two
+other workloads the baseline names, run through `generate` and timed by its own statistics on the
+host: 16 unequal prompts of 32 to 1,024 tokens with 256 decode steps at Qwen3-0.6B sizes, and 8
+prompts of 1,024 tokens with 128 decode steps at Qwen3-32B sizes.  `fp32_check` compares the
+bfloat16 engine with the true 32-bit engine on the same full-size model (a 64-token prompt).
+One JSON line goes to standard output.
 """
 
 from __future__ import annotations
@@ -111,6 +117,73 @@ def reference_arm() -> int:
     return 0
 
 
+WORKLOADS = {
+    # BASELINE.json's fourth and fifth configurations, as written there
+    "0.6b": dict(size="0.6b", prompts=16, min_len=32, max_len=1024, steps=256),
+    "32b": dict(size="32b", prompts=8, min_len=1024, max_len=1024, steps=128),
+}
+
+
+def run_workload(name: str, windows: list) -> dict:
+    """One of the baseline's other workloads through the public `generate`: decode tokens per second
+    by the loop's own statistics (host clock around the decode steps, tokens read back every step)."""
+    import numpy as np
+    import torch
+
+    import herbert_rs_b200 as hb
+
+    w = WORKLOADS[name]
+    cfg = dict(QWEN3_8B)
+    cfg.update(SIZES[w["size"]])
+    rng = np.random.default_rng(1)
+    lens = [int(n) for n in rng.integers(w["min_len"], w["max_len"] + 1, w["prompts"])]
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lens]
+    rt = hb.Runtime("cuda", torch.bfloat16)
+    model = hb.random_model(cfg, 0, rt)
+    per_seq = max(lens) + w["steps"] + 1
+    engine = hb.Engine(model, max_tokens=hb.Engine.pages_for(per_seq, w["prompts"]) * rt.page_size, max_slots=w["prompts"])
+    opt = hb.GenerationOptions(max_tokens=w["steps"] + 1, ignore_eos=True)      # the first token comes from the prompts' step
+    greedy = hb.SamplingParams(temperature=0.0)
+    hb.generate(engine, prompts, hb.GenerationOptions(max_tokens=12, ignore_eos=True), greedy)    # untimed: graph capture, workspace growth
+    torch.cuda.synchronize()
+    t0 = time.time()
+    res = hb.generate(engine, prompts, opt, greedy)
+    windows.append((t0, time.time()))
+    st = res.stats
+    out = {"decode_tok_s": round(st.decode_tokens_per_second, 1), "prefill_tok_s": round(st.prefill_tokens_per_second, 1),
+           "decode_steps": st.decode_steps, "prompt_tokens": st.prompt_tokens, "ms_per_step": round(st.decode_seconds / max(1, st.decode_steps) * 1e3, 4),
+           "layers": cfg["num_hidden_layers"], "prompts": w["prompts"]}
+    del engine, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def fp32_check(cfg: dict, bf16_engine, n_tokens: int = 64) -> dict:
+    """The bfloat16 engine against the true 32-bit engine on the same model (same seed, same
+    weights: bfloat16 values widened exactly) at full size: logits at every position of a prompt."""
+    import numpy as np
+    import torch
+
+    import herbert_rs_b200 as hb
+
+    ids = np.random.default_rng(7).integers(0, cfg["vocab_size"], n_tokens).tolist()
+    s = bf16_engine.alloc_slot()
+    low = bf16_engine.step([(s, ids)], "all").double().cpu()
+    bf16_engine.free_slot(s)
+    rt = hb.Runtime("cuda", torch.float32)
+    eng = hb.Engine(hb.random_model(cfg, 0, rt), max_tokens=hb.Engine.pages_for(n_tokens) * rt.page_size, max_slots=1)
+    s = eng.alloc_slot()
+    ref = eng.step([(s, ids)], "all").double().cpu()
+    eng.free_slot(s)
+    eng.check_kernels()
+    del eng
+    torch.cuda.empty_cache()
+    top2 = ref.topk(2, dim=-1).values
+    return {"tokens": n_tokens, "layers": cfg["num_hidden_layers"], "max_abs_err": round(float((low - ref).abs().max()), 5),
+            "logit_std": round(float(ref.std()), 4), "argmax_agree": round(float((low.argmax(-1) == ref.argmax(-1)).double().mean()), 4),
+            "median_top2_gap": round(float((top2[:, 0] - top2[:, 1]).median()), 5)}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -125,6 +198,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the 0.6B and 32B workloads of the baseline")
+    ap.add_argument("--no-fp32-check", action="store_true", help="skip the comparison with the 32-bit engine")
+    ap.add_argument("--workload", default=None, choices=["0.6b", "32b"],
+                    help="run only this workload of the baseline and print its line")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -132,6 +209,16 @@ def main() -> int:
         print(f"bench.py measures one GPU only (asked for {args.gpus}): this library has no multi-GPU path")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload is not None:
+        sampler, windows = ClockSampler(), []
+        sampler.start()
+        out = run_workload(args.workload, windows)
+        sampler.stop()
+        w = WORKLOADS[args.workload]
+        print(json.dumps({"metric": f"Qwen3-{w['size'].upper()} decode tok/s through generate ({w['prompts']} prompts of {w['min_len']}..{w['max_len']} tokens, {w['steps']} steps)",
+                          "value": out["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "impl": "ours", "dtype": "bf16",
+                          "data": "synthetic", "workload": out, "clocks": sampler.summary(windows)}))
+        return 0
 
     import numpy as np
     import torch
@@ -221,14 +308,12 @@ def main() -> int:
         for i in range(3 + 3):
             s = engine.alloc_slot()
             ids = rng.integers(0, V, T).tolist()
-            batch = engine._prepare([(s, ids)], "last")
             e0, e1 = events()
             t0 = time.time()
             e0.record()
-            engine._forward(batch)
+            engine.step([(s, ids)], "last")          # host packing, upload, every kernel, logits of the last token
             e1.record()
             torch.cuda.synchronize()
-            engine._finish(batch)
             engine.free_slot(s)
             if i >= 3:
                 times.append(e0.elapsed_time(e1))
@@ -252,7 +337,7 @@ def main() -> int:
     result["roofline"] = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                           "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]}
     if not args.no_e2e:
-        s_step, h2d, d2h = decode_e2e(B, max(8, args.steps // 2), args.warmup)
+        s_step, h2d, d2h = decode_e2e(B, max(64, args.steps), max(8, args.warmup))
         result["e2e"] = {"value": round(B / s_step, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     if not args.no_points:
         pts = {}
@@ -260,6 +345,15 @@ def main() -> int:
             ms_b, _ = decode_device(b, max(8, args.steps // 2), args.warmup)
             pts[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
         result["points"] = pts
+    if not args.no_fp32_check:
+        result["fp32_check"] = fp32_check(cfg, engine)
+    if not args.no_workloads and args.size == "8b" and args.layers == layers_full:
+        del engine, model
+        torch.cuda.empty_cache()
+        for name in ("0.6b", "32b"):
+            out = run_workload(name, windows)
+            result.setdefault("points", {})[f"qwen3_{name}_workload_decode"] = out["decode_tok_s"]
+            result.setdefault("workloads", {})[name] = out
     sampler.stop()
     clocks = sampler.summary(windows)
 
@@ -274,7 +368,8 @@ def main() -> int:
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": B, "seq_len": args.prompt_len, "context": args.context, "parallelism": "single-gpu",
                    "page_size": rt.page_size, "l2": "inputs larger than L2 (all weights read every step)",
-                   "cache_fill": "prefill of random prompts", "kernels_per_step": kernels_per_step},
+                   "cache_fill": "prefill of random prompts", "kernels_per_step": kernels_per_step,
+                   "timing": "value: CUDA events around upload + graph replay + argmax; e2e: host clock, tokens in and out"},
         "clocks": clocks,
     }
     line.update(result)

@@ -7,47 +7,73 @@ import torch
 from ..errors import BackendError
 
 
-class Workspace:
-    """A bump allocator over one device buffer, rewound at the start of every step.
+class _Lane:
+    """One bump allocator over one device buffer."""
 
-    The same sequence of requests yields the same addresses in every step, which is what a
-    captured CUDA graph of the step needs; nothing is allocated while a step runs once the
-    buffer has grown to the largest step seen (growth happens between steps, never during capture).
-    """
-
-    def __init__(self, device, nbytes: int = 1 << 20):
+    def __init__(self, device, nbytes: int):
         self.device = device
         self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
         self.offset = 0
+        self.wanted = 0
+        self.overflow: list = []
+
+
+class Workspace:
+    """Scratch memory of a step: bump allocators over device buffers, rewound at the start of every step.
+
+    The same sequence of requests yields the same addresses in every step, which is what a
+    captured CUDA graph of the step needs; nothing is allocated while a step runs once the
+    buffers have grown to the largest step seen (growth happens between steps, never during capture).
+
+    There are three lanes.  Lane 0 holds what lives for the whole step (the residual stream, the
+    logits).  Lanes 1 and 2 alternate between the layers: `use(lane)` makes a lane current and
+    empties it, so a layer's scratch is gone when the layer after the next begins, while what a
+    layer hands to its successor (a norm it has begun) survives that successor.  A step's scratch
+    is therefore two layers' worth, not the sum over all layers.
+    """
+
+    LANES = 3
+
+    def __init__(self, device, nbytes: int = 1 << 20):
+        self.device = device
+        self.lanes = [_Lane(device, nbytes) for _ in range(self.LANES)]
+        self.current = self.lanes[0]
         self.frozen = False
-        self._overflow: list = []
-        self._overflow_seen = False     # the buffer was replaced since this flag was last cleared
-        self._wanted = 0
+        self._overflow_seen = False     # a buffer was replaced since this flag was last cleared
 
     def rewind(self) -> None:
-        if self._wanted > self.buf.numel() and not self.frozen:
-            self.buf = torch.empty(int(self._wanted * 1.25) + 4096, dtype=torch.uint8, device=self.device)
-            self._overflow_seen = True
-        self.offset = 0
-        self._wanted = 0
-        self._overflow.clear()
+        for lane in self.lanes:
+            if lane.wanted > lane.buf.numel() and not self.frozen:
+                lane.buf = torch.empty(int(lane.wanted * 1.25) + 4096, dtype=torch.uint8, device=self.device)
+                self._overflow_seen = True
+            lane.offset = 0
+            lane.wanted = 0
+            lane.overflow.clear()
+        self.current = self.lanes[0]
+
+    def use(self, lane: int) -> None:
+        """Make `lane` current; lanes 1 and 2 start empty again (what they held is dead by now)."""
+        self.current = self.lanes[lane]
+        if lane != 0:
+            self.current.offset = 0
 
     def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        lane = self.current
         n = 1
         for s in shape:
             n *= int(s)
         es = torch.empty((), dtype=dtype).element_size()
         nbytes = (n * es + 255) & ~255
-        start = self.offset
-        self.offset += nbytes
-        self._wanted = max(self._wanted, self.offset)
-        if self.offset > self.buf.numel():
+        start = lane.offset
+        lane.offset += nbytes
+        lane.wanted = max(lane.wanted, lane.offset)
+        if lane.offset > lane.buf.numel():
             if self.frozen:
                 raise BackendError("workspace is frozen (a graph was captured) and too small for this step")
             t = torch.empty(tuple(shape), dtype=dtype, device=self.device)  # this step only; grows at rewind
-            self._overflow.append(t)
+            lane.overflow.append(t)
             return t
-        return self.buf[start:start + n * es].view(dtype).view(tuple(shape))
+        return lane.buf[start:start + n * es].view(dtype).view(tuple(shape))
 
 
 # Positions per cache page unless a caller asks otherwise: the tile of keys that the attention

@@ -102,6 +102,7 @@ class DecoderModel:
         sched, pending = self.spec.schedule, None
         for i, st in enumerate(sched):
             block = self.blocks[st.layer]
+            ws.use(1 + i % 2)           # this layer's scratch; what the layer before handed over lies in the other lane
             if not block.chains_norms:
                 block.forward(x, batch, cache.view(i))
                 pending = None
@@ -110,6 +111,7 @@ class DecoderModel:
             nxt_norm = nxt.first_norm() if nxt is not None and nxt.chains_norms else None
             pending = block.forward(x, batch, cache.view(i), normed=pending,
                                     next_norm=nxt_norm.shareable() if nxt_norm is not None else None)
+        ws.use(0)
         if batch.n_want == 0:
             return None
         hn = ws.take((batch.n_want, self.spec.hidden_size), self.rt.dtype)
