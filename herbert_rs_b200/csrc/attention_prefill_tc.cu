@@ -2,31 +2,36 @@
 //
 // The same arithmetic as attention_prefill.cu (causal grouped-query softmax attention in the flash
 // form, float softmax; reference: generic_attention/prefill/kernel_f32.rs:61-111), arranged for
-// tensor memory: a CTA owns 128 consecutive queries of one head of one sequence and walks the key
-// tiles (128 keys = two 64-key pages) of its causal range.
-//   warp 0     TMA: the Q tile once, then K and V tiles into two-stage rings (128-byte swizzle);
-//   warp 1     one lane issues tcgen05.mma:  S = Q K^T  (M=128, N=128) into one of two S buffers in
-//              tensor memory, and  O_j = P V  (M=128, N=head size; V is the MN-major operand as it
-//              lies in the cache) into one of two O buffers;
-//   warps 2-9  two threads per query row (each half of the tile's keys and of the output columns):
-//              read the row of S from tensor memory (no shuffles), mask,
-//              running maximum and sum in float, P = 2^(s*c - m) as bfloat16 into shared memory in
-//              the swizzled K-major layout the tensor cores read, and o = o * 2^(m_old - m_new) + O_j
-//              in registers; finally o / l goes to global memory.
-// The tensor cores compute S of tile j+1 while the row threads work on tile j.  Every wait on an
-// mbarrier is bounded; a wait that runs out sets *error_flag and the CTA winds down.
+// tensor memory.  A CTA works on two query heads of one key/value head at a time (the reference
+// walks the query heads of a key/value head together too, kernel_bf16.rs:236-300): 128 consecutive
+// queries of each, over the key tiles (128 keys = two 64-key pages) of their common causal range.
+// Both heads read the same K and V tiles, so those are fetched once, and while the row threads of
+// one head do their softmax the tensor cores run the products of the other ("ping-pong").
+//   warp 0     TMA: the two Q tiles, then K and V tiles into two-stage rings (128-byte swizzle);
+//   warp 1     one lane issues tcgen05.mma:  S_t = Q_t K^T  (M=128, N=128) into the head's S buffer
+//              in tensor memory, and  O_t += P_t V  (M=128, N=head size; V is the MN-major operand
+//              as it lies in the cache) into the head's O buffer, which stays in tensor memory over
+//              all key tiles;
+//   warps 2-5  head 0, warps 6-9 head 1: one thread per query row.  It reads its row of S (128
+//              values) from tensor memory into registers, frees S at once, masks, takes the row
+//              maximum, forms P = 2^(s*c - m) as bfloat16 in shared memory (K-major, swizzled: the
+//              tensor cores' A operand; one buffer that the heads use in turn) and keeps the row sum
+//              in float.  m is the maximum the row was last scaled to: it is raised, and O and l are
+//              rescaled, only when the tile's maximum exceeds it by more than 2^8 (a factor that
+//              cancels in O / l), which after the first tiles almost never happens, so O is not
+//              touched between products.
+// A head pair whose second head does not exist (an odd number of query heads per key/value head)
+// runs the first head alone.  CTAs are persistent and take items from a counter, longest first.
+// Every wait on an mbarrier is bounded; a wait that runs out sets *error_flag and the CTA winds down.
 #include "api.h"
 #include "common.cuh"
 #include "tcgen05_utils.cuh"
 
-// PARTS threads per query row (2, or 4 for head size 128): each takes 128 / PARTS keys of a tile and
-// HD / PARTS output columns.  Measured at head size 128: four threads per row are 9 % faster on long
-// prompts (8,192 tokens: 774 against 843 us) and slower on short ones (many 128-token prompts: 101
-// against 88 us), where the larger block barrier and exchange weigh more than the shorter passes.
-#define PT_THREADS(PARTS) (64 + 128 * (PARTS))         // TMA warp, MMA warp, 4 softmax warps per part
-#define PT_Q 128        // queries per CTA
-#define PT_KEYS 128     // keys per tile
+#define PT_THREADS 320       // TMA warp, MMA warp, four softmax warps per head
+#define PT_Q 128             // queries per head and item
+#define PT_KEYS 128          // keys per tile
 #define PT_SUB (128 * 128)   // bytes of one [128 rows][64 columns] swizzled sub-tile
+#define PT_RAISE 8.0f        // the reference maximum is raised when a tile exceeds it by this much (log2 units)
 
 struct PrefillTcArgs {
   bf16* out;
@@ -39,23 +44,26 @@ struct PrefillTcArgs {
   float scale_log2;   // scale * log2(e)
   int window;
   int* error_flag;
-  int n_seqs, q_tiles;   // items = q_tiles x nh x n_seqs (some without queries when the sequences differ in length)
+  int n_seqs, q_tiles;   // items = q_tiles x n_seqs x nkv x head pairs (some without queries when the sequences differ in length)
   int* work_counter;     // next item; zero when the kernel starts
 };
 
-// One unit of work: 128 consecutive queries of one head of one sequence.
+// One unit of work: 128 consecutive queries of two heads (or one) of one key/value head of one sequence.
 struct PtItem {
-  int b, h, kvh, row0, qlen, pos0, q_first, p_first, p_last, tile_lo, n_tiles;
+  int b, kvh, h0, streams, row0, qlen, pos0, q_first, p_first, p_last, tile_lo, n_tiles;
   bool valid;      // false: the sequence has no queries in this tile (shorter than the longest of the batch)
 };
 __device__ __forceinline__ PtItem pt_item(const PrefillTcArgs& a, int idx) {
   // the longest key ranges (last query tiles) first; neighbours share a sequence and a kv head
   PtItem it;
-  const int per_qt = a.nh * a.n_seqs;
+  const int G = a.nh / a.nkv, pairs = (G + 1) >> 1;
+  const int per_seq = a.nkv * pairs, per_qt = per_seq * a.n_seqs;
   const int qt = a.q_tiles - 1 - idx / per_qt, rem = idx % per_qt;
-  it.b = rem / a.nh;
-  it.h = rem % a.nh;
-  it.kvh = it.h / (a.nh / a.nkv);
+  it.b = rem / per_seq;
+  const int r2 = rem % per_seq, pair = r2 % pairs;
+  it.kvh = r2 / pairs;
+  it.h0 = it.kvh * G + 2 * pair;
+  it.streams = (2 * pair + 1 < G) ? 2 : 1;
   it.row0 = a.seq_start[it.b];
   it.qlen = a.seq_start[it.b + 1] - it.row0;
   it.pos0 = a.seq_pos0[it.b];
@@ -70,34 +78,66 @@ __device__ __forceinline__ PtItem pt_item(const PrefillTcArgs& a, int idx) {
   return it;
 }
 
-template <int HD, int PARTS>
-__global__ void __launch_bounds__(PT_THREADS(PARTS), 1)
+__device__ __forceinline__ void tc_ld32_issue(unsigned taddr, float* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]),
+        "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]), "=f"(r[16]),
+        "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]), "=f"(r[24]),
+        "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+      : "r"(taddr));
+}
+// Two floats in one 64-bit register and the packed float instructions of this architecture.
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int HD>
+__global__ void __launch_bounds__(PT_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PrefillTcArgs a) {
   constexpr int NB = HD / 64;                 // 64-column blocks of the head
   constexpr int TILE_BYTES = NB * PT_SUB;     // one Q, K, V tile
-  constexpr int ROW_WARPS = 4 * PARTS;
-  constexpr int ROW_THREADS = 32 * ROW_WARPS;
-  constexpr int KP = PT_KEYS / PARTS;         // keys of a tile per thread (64 or 32)
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
-  const unsigned q_s = base, k_s = q_s + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
+  const unsigned q_s = base, k_s = q_s + 2 * TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
   unsigned char* p_gen = gen + (p_s - base);
   const unsigned bars = p_s + 2 * PT_SUB;
-  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 s_empty
-  //           13 p_ready | 14,15 o_full | 16,17 o_empty | 18 q_empty | 19,20 item_full | 21,22 item_empty
+  // barriers: 0 q_full | 1 q_empty | 2,3 k_full | 4,5 k_empty | 6,7 v_full | 8,9 v_empty | 10,11 s_full (per head)
+  //           12,13 s_empty | 14,15 p_ready | 16,25 p_free (by use parity) | 17,18 o_full | 19,20 o_empty
+  //           21,22 item_full | 23,24 item_empty
+  constexpr int N_BARS = 26;
   auto bar = [&](int i) { return bars + i * 8; };
-  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + (bars - base) + 23 * 8);
-  volatile int* item_ring = reinterpret_cast<volatile int*>(gen + (bars - base) + 23 * 8 + 8);      // [2]
-  float* xch = reinterpret_cast<float*>(gen + (bars - base) + 256);   // [2 tile parities][PARTS][128 rows] maxima, then [PARTS][128] sums
+  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + (bars - base) + N_BARS * 8);
+  volatile int* item_ring = reinterpret_cast<volatile int*>(gen + (bars - base) + N_BARS * 8 + 8);      // [2]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 23; ++i) {
-      const bool from_rows = (i == 11 || i == 12 || i == 13 || i == 16 || i == 17);   // arrived at by the row warps
-      const bool from_consumers = (i == 21 || i == 22);                               // the MMA lane and the row warps
-      mbar_init(bar(i), from_rows ? ROW_WARPS : (from_consumers ? ROW_WARPS + 1 : 1));
+    for (int i = 0; i < N_BARS; ++i) {
+      const bool from_rows = (i == 12 || i == 13 || i == 14 || i == 15 || i == 19 || i == 20);   // the four row warps of a head
+      const bool from_consumers = (i == 23 || i == 24);                                          // the MMA lane and all row warps
+      mbar_init(bar(i), from_rows ? 4 : (from_consumers ? 9 : 1));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -113,33 +153,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const unsigned tmem = *tmem_slot;
   const unsigned tm_s[2] = {tmem, tmem + 128u};
   const unsigned tm_o[2] = {tmem + 256u, tmem + 256u + (unsigned)HD};
-  const int total_items = a.q_tiles * a.nh * a.n_seqs;
+  const int G = a.nh / a.nkv;
+  const int total_items = a.q_tiles * a.n_seqs * a.nkv * ((G + 1) >> 1);
 
   // The CTAs are persistent: each takes the next item from a counter in global memory when it has
   // issued everything for its current one.  The TMA warp fetches the index and hands it to the
   // other warps through a ring of two slots, so it can load the next item's tiles while the
-  // current item is still being worked on.  `g` counts this CTA's key tiles over all its items:
-  // ring stages and barrier phases carry on from item to item.
+  // current item is still being worked on.  Counters of key tiles, of a head's tiles and of the P
+  // buffer's uses run on from item to item: ring stages and barrier phases carry over.
   if (warp == 0) {
     if (lane == 0) {
       int g = 0, n_valid = 0;
       bool ok = true;
       for (int n = 0; ok; ++n) {
         const int slot = n & 1;
-        if (n >= 2 && !mbar_wait(bar(21 + slot), ((n >> 1) - 1) & 1)) { atomicExch(a.error_flag, 31); break; }
+        if (n >= 2 && !mbar_wait(bar(23 + slot), ((n >> 1) - 1) & 1)) { atomicExch(a.error_flag, 31); break; }
         const int fetched = atomicAdd(a.work_counter, 1);
         const int idx = fetched < total_items ? fetched : -1;
         item_ring[slot] = idx;
-        mbar_arrive_cta(bar(19 + slot));
+        mbar_arrive_cta(bar(21 + slot));
         if (idx < 0) break;
         const PtItem it = pt_item(a, idx);
         if (!it.valid) continue;
-        // the Q buffer is free once the previous item's last S product has read it
-        if (n_valid >= 1 && !mbar_wait(bar(18), (n_valid - 1) & 1)) { atomicExch(a.error_flag, 32); break; }
+        // the Q buffers are free once the previous item's last S products have read them
+        if (n_valid >= 1 && !mbar_wait(bar(1), (n_valid - 1) & 1)) { atomicExch(a.error_flag, 32); break; }
         ++n_valid;
-        mbar_expect_tx(bar(0), TILE_BYTES);
+        mbar_expect_tx(bar(0), it.streams * TILE_BYTES);
+        for (int t = 0; t < it.streams; ++t)
 #pragma unroll
-        for (int jb = 0; jb < NB; ++jb) tma_load_2d(q_s + jb * PT_SUB, &map_q, it.h * HD + jb * 64, it.row0 + it.q_first, bar(0));
+          for (int jb = 0; jb < NB; ++jb)
+            tma_load_2d(q_s + t * TILE_BYTES + jb * PT_SUB, &map_q, (it.h0 + t) * HD + jb * 64, it.row0 + it.q_first, bar(0));
         const int* pages = a.seq_pages + (size_t)it.b * a.pages_stride;
         for (int j = 0; j < it.n_tiles; ++j, ++g) {
           const int st = g & 1;
@@ -151,20 +194,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int page = lp < a.pages_stride ? pages[lp] : 0;     // beyond the sequence: any page, its keys are masked
             rows[half] = (page * a.nkv + it.kvh) * a.page_size + key0 % a.page_size;
           }
-          if (g >= 2 && !mbar_wait(bar(3 + st), ((g >> 1) - 1) & 1)) { atomicExch(a.error_flag, 21); ok = false; break; }
-          mbar_expect_tx(bar(1 + st), TILE_BYTES);
+          if (g >= 2 && !mbar_wait(bar(4 + st), ((g >> 1) - 1) & 1)) { atomicExch(a.error_flag, 21); ok = false; break; }
+          mbar_expect_tx(bar(2 + st), TILE_BYTES);
 #pragma unroll
           for (int jb = 0; jb < NB; ++jb)
 #pragma unroll
             for (int half = 0; half < 2; ++half)
-              tma_load_2d(k_s + st * TILE_BYTES + jb * PT_SUB + half * 8192, &map_k, jb * 64, rows[half], bar(1 + st));
-          if (g >= 2 && !mbar_wait(bar(7 + st), ((g >> 1) - 1) & 1)) { atomicExch(a.error_flag, 22); ok = false; break; }
-          mbar_expect_tx(bar(5 + st), TILE_BYTES);
+              tma_load_2d(k_s + st * TILE_BYTES + jb * PT_SUB + half * 8192, &map_k, jb * 64, rows[half], bar(2 + st));
+          if (g >= 2 && !mbar_wait(bar(8 + st), ((g >> 1) - 1) & 1)) { atomicExch(a.error_flag, 22); ok = false; break; }
+          mbar_expect_tx(bar(6 + st), TILE_BYTES);
 #pragma unroll
           for (int jb = 0; jb < NB; ++jb)
 #pragma unroll
             for (int half = 0; half < 2; ++half)
-              tma_load_2d(v_s + st * TILE_BYTES + jb * PT_SUB + half * 8192, &map_v, jb * 64, rows[half], bar(5 + st));
+              tma_load_2d(v_s + st * TILE_BYTES + jb * PT_SUB + half * 8192, &map_v, jb * 64, rows[half], bar(6 + st));
         }
       }
     }
@@ -174,216 +217,199 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(PT_KEYS >> 3) << 17) | ((unsigned)(PT_Q >> 4) << 24);
       const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(PT_Q >> 4) << 24);
       int g0 = 0, n_valid = 0;
+      int c[2] = {0, 0}, items_done[2] = {0, 0};     // per head: key tiles and items so far
+      int uses = 0;                                  // products that have read the P buffer so far
       bool ok = true;
       for (int n = 0; ok; ++n) {
         const int slot = n & 1;
-        if (!mbar_wait(bar(19 + slot), (n >> 1) & 1)) { atomicExch(a.error_flag, 33); break; }
+        if (!mbar_wait(bar(21 + slot), (n >> 1) & 1)) { atomicExch(a.error_flag, 33); break; }
         const int idx = item_ring[slot];
-        mbar_arrive_cta(bar(21 + slot));
+        mbar_arrive_cta(bar(23 + slot));
         if (idx < 0) break;
         const PtItem it = pt_item(a, idx);
         if (!it.valid) continue;
         if (!mbar_wait(bar(0), n_valid & 1)) { atomicExch(a.error_flag, 23); break; }
         ++n_valid;
-        const int n_tiles = it.n_tiles;
-        auto issue_qk = [&](int j) -> bool {
-          const int g = g0 + j, st = g & 1;
-          if (g >= 2 && !mbar_wait(bar(11 + st), ((g >> 1) - 1) & 1)) { atomicExch(a.error_flag, 24); return false; }   // S buffer drained
-          if (!mbar_wait(bar(1 + st), (g >> 1) & 1)) { atomicExch(a.error_flag, 25); return false; }                  // K tile landed
+        const int n_tiles = it.n_tiles, streams = it.streams;
+        auto issue_qk = [&](int t, int j) -> bool {
+          const int g = g0 + j, st = g & 1, ct = c[t] + j;
+          if (ct >= 1 && !mbar_wait(bar(12 + t), (ct - 1) & 1)) { atomicExch(a.error_flag, 24); return false; }   // S read by its rows
+          if (!mbar_wait(bar(2 + st), (g >> 1) & 1)) { atomicExch(a.error_flag, 25); return false; }             // K tile landed
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks) {
             const unsigned off = (ks >> 2) * PT_SUB + (ks & 3) * 32;
-            tc_mma_bf16(tm_s[st], umma_desc_sw128(q_s + off), umma_desc_sw128(k_s + st * TILE_BYTES + off), idesc_qk, ks > 0 ? 1u : 0u);
+            tc_mma_bf16(tm_s[t], umma_desc_sw128(q_s + t * TILE_BYTES + off), umma_desc_sw128(k_s + st * TILE_BYTES + off), idesc_qk,
+                        ks > 0 ? 1u : 0u);
           }
-          tc_commit(bar(3 + st));    // K stage free
-          tc_commit(bar(9 + st));    // S ready
-          if (j == n_tiles - 1) tc_commit(bar(18));   // Q free for the next item
+          tc_commit(bar(10 + t));    // S ready
+          if (t == streams - 1) {
+            tc_commit(bar(4 + st));                      // K stage free
+            if (j == n_tiles - 1) tc_commit(bar(1));     // Q free for the next item
+          }
           return true;
         };
-        ok = issue_qk(0);
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          const int g = g0 + j, st = g & 1;
-          if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-          if (!ok) break;
-          if (!mbar_wait(bar(13), g & 1)) { atomicExch(a.error_flag, 26); ok = false; break; }                                    // P written
-          if (!mbar_wait(bar(5 + st), (g >> 1) & 1)) { atomicExch(a.error_flag, 27); ok = false; break; }                         // V tile landed
-          if (g >= 2 && !mbar_wait(bar(16 + st), ((g >> 1) - 1) & 1)) { atomicExch(a.error_flag, 28); ok = false; break; }        // O buffer drained
+        auto issue_pv = [&](int t, int j) -> bool {
+          const int g = g0 + j, st = g & 1, ct = c[t] + j;
+          if (!mbar_wait(bar(14 + t), ct & 1)) { atomicExch(a.error_flag, 26); return false; }                     // P written (and O rescaled)
+          if (!mbar_wait(bar(6 + st), (g >> 1) & 1)) { atomicExch(a.error_flag, 27); return false; }               // V tile landed
+          if (j == 0 && items_done[t] >= 1 && !mbar_wait(bar(19 + t), (items_done[t] - 1) & 1)) { atomicExch(a.error_flag, 28); return false; }   // O read out
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < PT_KEYS / 16; ++ks) {
             const unsigned p_off = (ks >> 2) * PT_SUB + (ks & 3) * 32;
-            tc_mma_bf16(tm_o[st], umma_desc_sw128(p_s + p_off), umma_desc_sw128_mn(v_s + st * TILE_BYTES + ks * 2048, PT_SUB),
-                        idesc_pv, ks > 0 ? 1u : 0u);
+            tc_mma_bf16(tm_o[t], umma_desc_sw128(p_s + p_off), umma_desc_sw128_mn(v_s + st * TILE_BYTES + ks * 2048, PT_SUB),
+                        idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           }
-          tc_commit(bar(7 + st));    // V stage free
-          tc_commit(bar(14 + st));   // O_j ready (and P free)
-        }
+          tc_commit(bar((uses & 1) ? 25 : 16));   // P free for the next user
+          ++uses;
+          tc_commit(bar(17 + t));    // O holds this tile too
+          if (t == streams - 1) tc_commit(bar(8 + st));   // V stage free
+          return true;
+        };
+        // A head's scores of tile j+1 are issued as soon as its rows have taken tile j's out of tensor
+        // memory, ahead of the product with P of tile j: the row threads then find the next scores
+        // waiting when they have finished a tile, and only the P V products wait for them.
+        for (int t = 0; t < streams && ok; ++t) ok = issue_qk(t, 0);
+        for (int j = 0; j < n_tiles && ok; ++j)
+          for (int t = 0; t < streams && ok; ++t) {
+            if (j + 1 < n_tiles) ok = issue_qk(t, j + 1);
+            if (ok) ok = issue_pv(t, j);
+          }
         g0 += n_tiles;
+        for (int t = 0; t < streams; ++t) {
+          c[t] += n_tiles;
+          ++items_done[t];
+        }
       }
     }
   } else {
-    // PARTS threads per query row: warps 2-5 take the first KP keys of a tile and the first HD / PARTS
-    // output columns, warps 6-9 the next, and so on; a warp may only touch the 32 tensor memory lanes
-    // of its quadrant (warp index modulo 4), so the threads of a row sit in warps w, w+4, w+8, ...
+    // One thread per query row.  A warp may only touch the 32 tensor memory lanes of its quadrant
+    // (warp index modulo 4): warps 2-5 are head 0, warps 6-9 head 1.
+    const int t = (warp - 2) >> 2;               // which head of the pair
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;            // which part of the row (0..PARTS-1)
     const int r = quad * 32 + lane;              // row of the tile
     const unsigned lane_off = (unsigned)(quad * 32) << 16;
-    constexpr int HH = HD / PARTS;                // output columns per thread
-    const unsigned s_col = (unsigned)(half * KP), o_col = (unsigned)(half * HH);
-    int g0 = 0;
+    int c_t = 0, uses = 0;                       // this head's key tiles so far; uses of the P buffer so far (both heads)
     bool ok = true;
     for (int n = 0; ok; ++n) {
       const int slot = n & 1;
-      if (!mbar_wait(bar(19 + slot), (n >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 34); break; }
+      if (!mbar_wait(bar(21 + slot), (n >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 34); break; }
       const int idx = item_ring[slot];
       __syncwarp();
-      if (lane == 0) mbar_arrive_cta(bar(21 + slot));
+      if (lane == 0) mbar_arrive_cta(bar(23 + slot));
       if (idx < 0) break;
       const PtItem it = pt_item(a, idx);
       if (!it.valid) continue;
-      const int n_tiles = it.n_tiles, tile_lo = it.tile_lo, p_first = it.p_first, p_last = it.p_last;
+      const int n_tiles = it.n_tiles, streams = it.streams;
+      if (t >= streams) {          // the pair has one head only: nothing for this group, but the P buffer's uses go on
+        uses += n_tiles;
+        continue;
+      }
+      const int tile_lo = it.tile_lo, p_first = it.p_first, p_last = it.p_last;
       const int qi = it.q_first + r;
       const bool valid = qi < it.qlen;
       const int p = it.pos0 + qi;
       const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
       const int lo_last = (a.window > 0 && p_last - a.window + 1 > 0) ? p_last - a.window + 1 : 0;
-      float m = -INFINITY, l = 0.0f, m_acc = -INFINITY;   // m_acc: the maximum the rows of o are scaled to
-      float o[HH];
-#pragma unroll
-      for (int i = 0; i < HH; ++i) o[i] = 0.0f;
-      auto accumulate = [&](int g) -> bool {        // waits for O of tile g
-        const int st = g & 1;
-        if (!mbar_wait(bar(14 + st), (g >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 29); return false; }
-        tc_fence_after();
-        return true;
-      };
-      float m_tile[2] = {-INFINITY, -INFINITY};      // maximum in force when P of a tile was formed, by stage
+      float m = -INFINITY, l = 0.0f;     // m: the maximum the row's P, l and O are scaled to
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int g = g0 + j, st = g & 1;
-        const int key0 = (tile_lo + j) * PT_KEYS + half * KP;     // first key of this thread's share
-        if (!mbar_wait(bar(9 + st), (g >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 30); ok = false; break; }
+        const int ct = c_t + j;
+        const int key0 = (tile_lo + j) * PT_KEYS;
+        if (!mbar_wait(bar(10 + t), ct & 1)) { if (lane == 0) atomicExch(a.error_flag, 30); ok = false; break; }
         tc_fence_after();
-        const bool need_mask = ((tile_lo + j) * PT_KEYS + PT_KEYS - 1 > p_first) || ((tile_lo + j) * PT_KEYS < lo_last);
-        // pass 1: the row's maximum over this thread's half of the tile (raw scores: the scale is positive)
+        float s[PT_KEYS];
+#pragma unroll
+        for (int cc = 0; cc < PT_KEYS / 32; ++cc) tc_ld32_issue(tm_s[t] + lane_off + cc * 32, s + cc * 32);
+        tc_wait_ld();
+        // the row is in registers: the tensor cores may write the next tile's scores
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cta(bar(12 + t));
+        const bool need_mask = (key0 + PT_KEYS - 1 > p_first) || (key0 < lo_last);
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < PT_KEYS; ++i) {
+            const int key = key0 + i;
+            s[i] = (key <= p && key >= lo) ? s[i] : -INFINITY;
+          }
+        }
         float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < PT_KEYS; i += 2) mx = max3(mx, s[i], s[i + 1]);
+        mx *= a.scale_log2;         // the scale is positive: the maximum of the raw scores is the maximum
+        const bool raise = mx > m + PT_RAISE || (m == -INFINITY && mx > -INFINITY);
+        if (j > 0 && __any_sync(0xffffffffu, raise)) {
+          // rescale O to the new maximum (rows that keep theirs: factor 1); the product of the tile before must be complete
+          if (!mbar_wait(bar(17 + t), (ct - 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 29); ok = false; break; }
+          tc_fence_after();
+          const float f = raise ? ((m == -INFINITY) ? 0.0f : fast_exp2(m - mx)) : 1.0f;
 #pragma unroll 1
-        for (int c = 0; c < KP / 32; ++c) {
-          float s[32];
-          tc_ld32f(tm_s[st] + lane_off + s_col + c * 32, s);
-          if (need_mask) {
+          for (int cc = 0; cc < HD / 16; ++cc) {
+            float o[16];
+            tc_ld16f(tm_o[t] + lane_off + cc * 16, o);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = key0 + c * 32 + i;
-              mx = fmaxf(mx, (key <= p && key >= lo) ? s[i] : -INFINITY);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+            for (int i = 0; i < 16; ++i) o[i] *= f;
+            tc_st16f(tm_o[t] + lane_off + cc * 16, o);
           }
         }
-        mx *= a.scale_log2;
-        // the other half of the row: exchange through shared memory (buffers alternate with the tile)
-        float* xm = xch + (g & 1) * (PARTS * 128);
-        xm[half * 128 + r] = mx;
-        asm volatile("bar.sync 1, %0;" ::"n"(ROW_THREADS) : "memory");
-#pragma unroll
-        for (int q = 0; q < PARTS; ++q) mx = fmaxf(mx, xm[q * 128 + r]);
-        const float m_new = fmaxf(m, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-        // the previous tile's P V must be complete before P is overwritten
-        if (j > 0) {
-          ok = accumulate(g - 1);
-          if (!ok) break;
+        if (raise) {
+          l *= (m == -INFINITY) ? 0.0f : fast_exp2(m - mx);
+          m = mx;
         }
-        // pass 2: P = 2^(s*c - m) into shared memory (K-major, 128-byte swizzle), partial row sum in float
-        float sum = 0.0f;
-#pragma unroll 1
-        for (int c = 0; c < KP / 32; ++c) {
-          float s[32];
-          tc_ld32f(tm_s[st] + lane_off + s_col + c * 32, s);
-          unsigned pk[16];
-          if (need_mask) {
+        const float m_use = (m == -INFINITY) ? 0.0f : m;
+        // P = 2^(s*c - m) as bfloat16 pairs; masked scores are -inf and give 0
+        unsigned pk[PT_KEYS / 2];
+        const unsigned long long c2 = pack2(a.scale_log2, a.scale_log2), m2 = pack2(-m_use, -m_use);
+        unsigned long long sum2 = pack2(0.0f, 0.0f);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = key0 + c * 32 + i;
-              s[i] = (key <= p && key >= lo) ? fast_exp2(fmaf(s[i], a.scale_log2, -m_use)) : 0.0f;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) s[i] = fast_exp2(fmaf(s[i], a.scale_log2, -m_use));
-          }
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            sum += s[i] + s[i + 1];
-            __nv_bfloat162 v = __floats2bfloat162_rn(s[i], s[i + 1]);
-            pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
-          }
-          // 32 keys = four 16-byte chunks of this row in the 64-key sub-tile they belong to; chunk index xor row % 8
-          const int k_in_tile = half * KP + c * 32;
-          unsigned char* rowp = p_gen + (k_in_tile >> 6) * PT_SUB + r * 128;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = (((k_in_tile & 63) >> 3) + q4) ^ (r & 7);
-            *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-          }
+        for (int i = 0; i < PT_KEYS; i += 2) {
+          float x0, x1;
+          unpack2(fma2(pack2(s[i], s[i + 1]), c2, m2), x0, x1);      // two scores per instruction
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          sum2 = add2(sum2, pack2(e0, e1));
+          __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
+          pk[i >> 1] = *reinterpret_cast<unsigned*>(&v);
         }
-        const float corr = (m == -INFINITY) ? 0.0f : fast_exp2(m - m_use);
-        l = l * corr + sum;          // this thread's share of the row sum; the two shares meet at the end
-        m = m_new;
-        m_tile[st] = m_new;
-        // S buffer read, P written: hand both to the tensor cores
+        float sum_a, sum_b;
+        unpack2(sum2, sum_a, sum_b);
+        const float sum = sum_a + sum_b;
+        l += sum;
+        // The P buffer is shared by the two heads in turn: the product that read it last (use - 1) must
+        // be complete.  Two barriers take turns, so that the parity waited for cannot be mistaken: a
+        // head's scores arrive ahead of its own previous product (use - 2), but never ahead of use - 3.
+        const int use = uses + streams * j + t;
+        if (use >= 1 && !mbar_wait(bar(((use - 1) & 1) ? 25 : 16), ((use - 1) >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 35); ok = false; break; }
+        // 128 keys = sixteen 16-byte chunks of this row, eight per 64-key sub-tile; chunk index xor row % 8
+#pragma unroll
+        for (int q8 = 0; q8 < 16; ++q8) {
+          unsigned char* rowp = p_gen + (q8 >> 3) * PT_SUB + r * 128;
+          const int chunk = (q8 & 7) ^ (r & 7);
+          *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[q8 * 4], pk[q8 * 4 + 1], pk[q8 * 4 + 2], pk[q8 * 4 + 3]);
+        }
+        // P written (and O rescaled): hand them to the tensor cores
         tc_fence_before();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive_cta(bar(11 + st));
-          mbar_arrive_cta(bar(13));
-        }
-        // the previous tile's result goes into the registers now, while the tensor cores run this tile's P V
-        if (j > 0) {
-          const int sp = (g - 1) & 1;
-          const float mt = m_tile[sp];
-          const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
-#pragma unroll
-          for (int c = 0; c < HH / 32; ++c) {      // unrolled: o stays in registers
-            float t[32];
-            tc_ld32f(tm_o[sp] + lane_off + o_col + c * 32, t);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * f + t[i];
-          }
-          m_acc = mt;
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cta(bar(16 + sp));    // O buffer free
-        }
+        if (lane == 0) mbar_arrive_cta(bar(14 + t));
       }
       if (!ok) break;
-      // the row sum is the sum of the two threads' shares (both scaled to the same final maximum)
-      float* xl = xch + 2 * PARTS * 128;
-      xl[half * 128 + r] = l;
-      asm volatile("bar.sync 1, %0;" ::"n"(ROW_THREADS) : "memory");
-      l = 0.0f;
-#pragma unroll
-      for (int q = 0; q < PARTS; ++q) l += xl[q * 128 + r];
       {
-        const int g = g0 + n_tiles - 1, sp = g & 1;
-        ok = accumulate(g);
-        if (!ok) break;
-        const float mt = m_tile[sp];
-        const float f = (mt == -INFINITY) ? 1.0f : fast_exp2(((m_acc == -INFINITY) ? mt : m_acc) - mt);
+        const int ct = c_t + n_tiles - 1;
+        if (!mbar_wait(bar(17 + t), ct & 1)) { if (lane == 0) atomicExch(a.error_flag, 36); ok = false; break; }
+        tc_fence_after();
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        bf16* dst = a.out + (size_t)(it.row0 + qi) * a.ldo + (size_t)it.h * HD + half * HH;
+        bf16* dst = a.out + (size_t)(it.row0 + qi) * a.ldo + (size_t)(it.h0 + t) * HD;
 #pragma unroll
-        for (int c = 0; c < HH / 32; ++c) {
-          float t[32];
-          tc_ld32f(tm_o[sp] + lane_off + o_col + c * 32, t);
-          if (c == HH / 32 - 1) {
+        for (int cc = 0; cc < HD / 32; ++cc) {
+          float o[32];
+          tc_ld32_issue(tm_o[t] + lane_off + cc * 32, o);
+          tc_wait_ld();
+          if (cc == HD / 32 - 1) {
             // the last read of this O buffer: the tensor cores may have it back for the next item
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cta(bar(16 + sp));
+            if (lane == 0) mbar_arrive_cta(bar(19 + t));
           }
           if (valid) {
 #pragma unroll
@@ -391,17 +417,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
               unsigned w[4];
 #pragma unroll
               for (int u = 0; u < 4; ++u) {
-                const float x0 = (o[c * 32 + i + 2 * u] * f + t[i + 2 * u]) * inv;
-                const float x1 = (o[c * 32 + i + 2 * u + 1] * f + t[i + 2 * u + 1]) * inv;
-                __nv_bfloat162 v = __floats2bfloat162_rn(x0, x1);
+                __nv_bfloat162 v = __floats2bfloat162_rn(o[i + 2 * u] * inv, o[i + 2 * u + 1] * inv);
                 w[u] = *reinterpret_cast<unsigned*>(&v);
               }
-              *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(dst + cc * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
             }
           }
         }
       }
-      g0 += n_tiles;
+      c_t += n_tiles;
+      uses += streams * n_tiles;
     }
   }
   tc_fence_before();
@@ -440,7 +465,8 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   PrefillTcArgs a{(bf16*)out, ldo, seq_start, seq_pos0, seq_pages, pages_stride, nh, nkv, page_size,
                   scale * 1.4426950408889634f, window, error_flag, n_seqs, q_tiles, work_counter};
   cudaStream_t s = (cudaStream_t)stream;
-  const long long items = (long long)q_tiles * nh * n_seqs;
+  const int pairs = (nh / nkv + 1) / 2;
+  const long long items = (long long)q_tiles * n_seqs * nkv * pairs;
   HB_REQUIRE(items < 2147483647LL, "attention_prefill_tc: too many query tiles");
   static int sms = 0;
   if (sms == 0) {
@@ -451,19 +477,16 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   dim3 grid((unsigned)(items < sms ? items : sms));
   cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(int), s);
   if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reset the work counter: %s", cudaGetErrorString(e));
-  const int smem = 6 * (hd / 64) * PT_SUB + 2 * PT_SUB - (hd / 64) * PT_SUB + 1024 + 256 + 6144;   // tiles, slack, barriers, exchange
-  if (hd == 128 && max_q_len >= 4096) {
-    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  // two Q tiles, two stages of K and of V, one P tile; slack for the 1024-byte alignment; barriers and the item ring
+  const int smem = 6 * (hd / 64) * PT_SUB + 2 * PT_SUB + 1024 + 512;
+  if (hd == 128) {
+    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_prefill_tc_kernel<128, 4>, grid, dim3(PT_THREADS(4)), smem, s, mq, mk, mv, a);
-  } else if (hd == 128) {
-    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_prefill_tc_kernel<128, 2>, grid, dim3(PT_THREADS(2)), smem, s, mq, mk, mv, a);
+    hb_launch(attention_prefill_tc_kernel<128>, grid, dim3(PT_THREADS), smem, s, mq, mk, mv, a);
   } else {
-    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    e = cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_prefill_tc_kernel<64, 2>, grid, dim3(PT_THREADS(2)), smem, s, mq, mk, mv, a);
+    hb_launch(attention_prefill_tc_kernel<64>, grid, dim3(PT_THREADS), smem, s, mq, mk, mv, a);
   }
   HB_CHECK_LAUNCH("attention_prefill_tc");
   return 0;
