@@ -14,9 +14,10 @@
 //              all key tiles;
 //   warps 2-5  head 0, warps 6-9 head 1: one thread per query row.  It reads its row of S (128
 //              values) from tensor memory into registers, frees S at once, masks, takes the row
-//              maximum, forms P = 2^(s*c - m) as bfloat16 in shared memory (K-major, swizzled: the
-//              tensor cores' A operand; one buffer that the heads use in turn) and keeps the row sum
-//              in float.  m is the maximum the row was last scaled to: it is raised, and O and l are
+//              maximum, forms P = 2^(s*c - m) as bfloat16 and writes it back into tensor memory over
+//              the scores it came from (two values per column: the A operand of the second product is
+//              read from tensor memory, so P never passes through shared memory, whose bandwidth the
+//              tensor cores' operand reads already use up) and keeps the row sum in float.  m is the maximum the row was last scaled to: it is raised, and O and l are
 //              rescaled, only when the tile's maximum exceeds it by more than 2^8 (a factor that
 //              cancels in O / l), which after the first tiles almost never happens, so O is not
 //              touched between products.
@@ -110,6 +111,27 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
+// The product with the A operand in tensor memory (row i of A in lane i, two bfloat16 per column).
+__device__ __forceinline__ void tc_mma_bf16_ta(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                               unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st32(unsigned taddr, const unsigned* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 template <int HD>
@@ -121,13 +143,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
-  const unsigned q_s = base, k_s = q_s + 2 * TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
-  unsigned char* p_gen = gen + (p_s - base);
-  const unsigned bars = p_s + 2 * PT_SUB;
+  const unsigned q_s = base, k_s = q_s + 2 * TILE_BYTES, v_s = k_s + 2 * TILE_BYTES;
+  const unsigned bars = v_s + 2 * TILE_BYTES;
   // barriers: 0 q_full | 1 q_empty | 2,3 k_full | 4,5 k_empty | 6,7 v_full | 8,9 v_empty | 10,11 s_full (per head)
-  //           12,13 s_empty | 14,15 p_ready | 16,25 p_free (by use parity) | 17,18 o_full | 19,20 o_empty
-  //           21,22 item_full | 23,24 item_empty
-  constexpr int N_BARS = 26;
+  //           14,15 p_ready | 17,18 o_full | 19,20 o_empty | 21,22 item_full | 23,24 item_empty
+  constexpr int N_BARS = 25;
   auto bar = [&](int i) { return bars + i * 8; };
   volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + (bars - base) + N_BARS * 8);
   volatile int* item_ring = reinterpret_cast<volatile int*>(gen + (bars - base) + N_BARS * 8 + 8);      // [2]
@@ -135,7 +155,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < N_BARS; ++i) {
-      const bool from_rows = (i == 12 || i == 13 || i == 14 || i == 15 || i == 19 || i == 20);   // the four row warps of a head
+      const bool from_rows = (i == 14 || i == 15 || i == 19 || i == 20);   // the four row warps of a head
       const bool from_consumers = (i == 23 || i == 24);                                          // the MMA lane and all row warps
       mbar_init(bar(i), from_rows ? 4 : (from_consumers ? 9 : 1));
     }
@@ -216,9 +236,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // D float, A and B bfloat16; B of the second product is MN-major (bit 16)
       const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(PT_KEYS >> 3) << 17) | ((unsigned)(PT_Q >> 4) << 24);
       const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(PT_Q >> 4) << 24);
+      const unsigned long long desc_q[2] = {umma_desc_sw128(q_s), umma_desc_sw128(q_s + TILE_BYTES)};
+      const unsigned long long desc_k[2] = {umma_desc_sw128(k_s), umma_desc_sw128(k_s + TILE_BYTES)};
+      const unsigned long long desc_v[2] = {umma_desc_sw128_mn(v_s, PT_SUB), umma_desc_sw128_mn(v_s + TILE_BYTES, PT_SUB)};
       int g0 = 0, n_valid = 0;
       int c[2] = {0, 0}, items_done[2] = {0, 0};     // per head: key tiles and items so far
-      int uses = 0;                                  // products that have read the P buffer so far
       bool ok = true;
       for (int n = 0; ok; ++n) {
         const int slot = n & 1;
@@ -232,15 +254,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ++n_valid;
         const int n_tiles = it.n_tiles, streams = it.streams;
         auto issue_qk = [&](int t, int j) -> bool {
-          const int g = g0 + j, st = g & 1, ct = c[t] + j;
-          if (ct >= 1 && !mbar_wait(bar(12 + t), (ct - 1) & 1)) { atomicExch(a.error_flag, 24); return false; }   // S read by its rows
+          // The scores overwrite the head's previous P.  Its rows have read the previous scores (they
+          // wrote P after that), and the product that reads P was issued before this one: tcgen05.mma
+          // instructions of a CTA execute in the order of their issue.
+          const int g = g0 + j, st = g & 1;
           if (!mbar_wait(bar(2 + st), (g >> 1) & 1)) { atomicExch(a.error_flag, 25); return false; }             // K tile landed
           tc_fence_after();
+          // descriptors differ in their address field only (16-byte units, the low bits of the word)
+          const unsigned long long dq = desc_q[t], dk = desc_k[st];
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks) {
-            const unsigned off = (ks >> 2) * PT_SUB + (ks & 3) * 32;
-            tc_mma_bf16(tm_s[t], umma_desc_sw128(q_s + t * TILE_BYTES + off), umma_desc_sw128(k_s + st * TILE_BYTES + off), idesc_qk,
-                        ks > 0 ? 1u : 0u);
+            const unsigned off16 = ((ks >> 2) * PT_SUB + (ks & 3) * 32) >> 4;
+            tc_mma_bf16(tm_s[t], dq + off16, dk + off16, idesc_qk, ks > 0 ? 1u : 0u);
           }
           tc_commit(bar(10 + t));    // S ready
           if (t == streams - 1) {
@@ -255,26 +280,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           if (!mbar_wait(bar(6 + st), (g >> 1) & 1)) { atomicExch(a.error_flag, 27); return false; }               // V tile landed
           if (j == 0 && items_done[t] >= 1 && !mbar_wait(bar(19 + t), (items_done[t] - 1) & 1)) { atomicExch(a.error_flag, 28); return false; }   // O read out
           tc_fence_after();
+          const unsigned long long dv = desc_v[st];
 #pragma unroll
-          for (int ks = 0; ks < PT_KEYS / 16; ++ks) {
-            const unsigned p_off = (ks >> 2) * PT_SUB + (ks & 3) * 32;
-            tc_mma_bf16(tm_o[t], umma_desc_sw128(p_s + p_off), umma_desc_sw128_mn(v_s + st * TILE_BYTES + ks * 2048, PT_SUB),
-                        idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-          }
-          tc_commit(bar((uses & 1) ? 25 : 16));   // P free for the next user
-          ++uses;
+          for (int ks = 0; ks < PT_KEYS / 16; ++ks)      // 16 keys of P = 8 columns of tensor memory
+            tc_mma_bf16_ta(tm_o[t], tm_s[t] + ks * 8, dv + (unsigned)(ks * 2048 >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           tc_commit(bar(17 + t));    // O holds this tile too
           if (t == streams - 1) tc_commit(bar(8 + st));   // V stage free
           return true;
         };
-        // A head's scores of tile j+1 are issued as soon as its rows have taken tile j's out of tensor
-        // memory, ahead of the product with P of tile j: the row threads then find the next scores
-        // waiting when they have finished a tile, and only the P V products wait for them.
+        // Per head: scores, (rows: softmax), P V, next scores, ...; while one head's rows work, the
+        // tensor cores run the other head's two products.
         for (int t = 0; t < streams && ok; ++t) ok = issue_qk(t, 0);
         for (int j = 0; j < n_tiles && ok; ++j)
           for (int t = 0; t < streams && ok; ++t) {
-            if (j + 1 < n_tiles) ok = issue_qk(t, j + 1);
-            if (ok) ok = issue_pv(t, j);
+            ok = issue_pv(t, j);
+            if (ok && j + 1 < n_tiles) ok = issue_qk(t, j + 1);
           }
         g0 += n_tiles;
         for (int t = 0; t < streams; ++t) {
@@ -290,7 +310,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int quad = warp & 3;
     const int r = quad * 32 + lane;              // row of the tile
     const unsigned lane_off = (unsigned)(quad * 32) << 16;
-    int c_t = 0, uses = 0;                       // this head's key tiles so far; uses of the P buffer so far (both heads)
+    int c_t = 0;                                 // this head's key tiles so far
     bool ok = true;
     for (int n = 0; ok; ++n) {
       const int slot = n & 1;
@@ -302,10 +322,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const PtItem it = pt_item(a, idx);
       if (!it.valid) continue;
       const int n_tiles = it.n_tiles, streams = it.streams;
-      if (t >= streams) {          // the pair has one head only: nothing for this group, but the P buffer's uses go on
-        uses += n_tiles;
-        continue;
-      }
+      if (t >= streams) continue;  // the pair has one head only: nothing for this group
       const int tile_lo = it.tile_lo, p_first = it.p_first, p_last = it.p_last;
       const int qi = it.q_first + r;
       const bool valid = qi < it.qlen;
@@ -322,10 +339,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int cc = 0; cc < PT_KEYS / 32; ++cc) tc_ld32_issue(tm_s[t] + lane_off + cc * 32, s + cc * 32);
         tc_wait_ld();
-        // the row is in registers: the tensor cores may write the next tile's scores
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cta(bar(12 + t));
         const bool need_mask = (key0 + PT_KEYS - 1 > p_first) || (key0 < lo_last);
         if (need_mask) {
 #pragma unroll
@@ -334,9 +347,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             s[i] = (key <= p && key >= lo) ? s[i] : -INFINITY;
           }
         }
-        float mx = -INFINITY;
+        float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: the instruction's latency is hidden
 #pragma unroll
-        for (int i = 0; i < PT_KEYS; i += 2) mx = max3(mx, s[i], s[i + 1]);
+        for (int i = 0; i < PT_KEYS; i += 8)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) mxs[q] = max3(mxs[q], s[i + 2 * q], s[i + 2 * q + 1]);
+        float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
         mx *= a.scale_log2;         // the scale is positive: the maximum of the raw scores is the maximum
         const bool raise = mx > m + PT_RAISE || (m == -INFINITY && mx > -INFINITY);
         if (j > 0 && __any_sync(0xffffffffu, raise)) {
@@ -375,21 +391,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         unpack2(sum2, sum_a, sum_b);
         const float sum = sum_a + sum_b;
         l += sum;
-        // The P buffer is shared by the two heads in turn: the product that read it last (use - 1) must
-        // be complete.  Two barriers take turns, so that the parity waited for cannot be mistaken: a
-        // head's scores arrive ahead of its own previous product (use - 2), but never ahead of use - 3.
-        const int use = uses + streams * j + t;
-        if (use >= 1 && !mbar_wait(bar(((use - 1) & 1) ? 25 : 16), ((use - 1) >> 1) & 1)) { if (lane == 0) atomicExch(a.error_flag, 35); ok = false; break; }
-        // 128 keys = sixteen 16-byte chunks of this row, eight per 64-key sub-tile; chunk index xor row % 8
-#pragma unroll
-        for (int q8 = 0; q8 < 16; ++q8) {
-          unsigned char* rowp = p_gen + (q8 >> 3) * PT_SUB + r * 128;
-          const int chunk = (q8 & 7) ^ (r & 7);
-          *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(pk[q8 * 4], pk[q8 * 4 + 1], pk[q8 * 4 + 2], pk[q8 * 4 + 3]);
-        }
+        // P goes where the row's scores were: 64 columns of two bfloat16 each
+        tc_st32(tm_s[t] + lane_off, pk);
+        tc_st32(tm_s[t] + lane_off + 32, pk + 32);
+        tc_wait_st();
         // P written (and O rescaled): hand them to the tensor cores
         tc_fence_before();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive_cta(bar(14 + t));
       }
@@ -426,7 +433,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       }
       c_t += n_tiles;
-      uses += streams * n_tiles;
     }
   }
   tc_fence_before();
@@ -477,8 +483,8 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
   dim3 grid((unsigned)(items < sms ? items : sms));
   cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(int), s);
   if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reset the work counter: %s", cudaGetErrorString(e));
-  // two Q tiles, two stages of K and of V, one P tile; slack for the 1024-byte alignment; barriers and the item ring
-  const int smem = 6 * (hd / 64) * PT_SUB + 2 * PT_SUB + 1024 + 512;
+  // two Q tiles, two stages of K and of V; slack for the 1024-byte alignment; barriers and the item ring
+  const int smem = 6 * (hd / 64) * PT_SUB + 1024 + 512;
   if (hd == 128) {
     e = cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
