@@ -10,8 +10,8 @@
 //   warp 1   allocates tensor memory (two accumulators of BN columns); one lane issues tcgen05.mma
 //            (M=128, N=BN, K=16) four times per stage, commits the stage's "empty" barrier and, at
 //            the end of a tile, that accumulator's "full" barrier;
-//   warps 2-5  read a finished accumulator with tcgen05.ld (each warp its 32 lanes = 32 rows of
-//            C), hand it back ("empty" barrier) and apply the epilogue: store, store as float, add
+//   warps 2-9  read a finished accumulator with tcgen05.ld (each warp its 32 lanes = 32 rows of
+//            C and half of the tile's columns), hand it back ("empty" barrier) and apply the epilogue: store, store as float, add
 //            into the float residual stream, or SwiGLU over column groups of 8 gate + 8 up.
 // With two accumulators the epilogue of tile i runs while the tensor cores work on tile i+1.
 // No thread-block clusters and no multicast are used.  Rows/columns beyond M, N, K are
@@ -22,7 +22,8 @@
 #include "tcgen05_utils.cuh"
 
 #define TG_BM 128
-#define TG_THREADS 192
+#define TG_THREADS 320      // TMA warp, MMA warp, eight epilogue warps
+#define TG_EPI_WARPS 8      // two per tensor-memory lane quadrant, each half of a tile's columns
 
 template <int BN>
 struct TgSmem {
@@ -50,7 +51,7 @@ struct TgNorm {
   const float* out_w;      // producer (residual epilogue): the next norm's weight [N], or null
   bf16* out_xw;            // [M, out_ld]
   int out_ld;
-  float* out_sumsq;        // [ceil(N / BN)][out_stride]
+  float* out_sumsq;        // [2 * ceil(N / BN)][out_stride]: one row per half tile of columns
   int out_stride;
 };
 
@@ -104,6 +105,119 @@ struct TgSegments {
   }
 };
 
+// The epilogue of 32 consecutive output columns (n ..) of row m, whose float results are in r:
+// scale by 1/rms, then store / store as float / add into the residual stream (and begin the next
+// norm: x * w in bfloat16, sum of x^2 into sq) / SwiGLU.  Rows beyond M and columns beyond N are skipped.
+template <int EPI, bool NORM>
+__device__ __forceinline__ void tg_epilogue32(unsigned (&r)[32], int m, int n, int M, int N, void* Cv, int ldc, const TgNorm& nm,
+                                              float inv_rms, float& sq) {
+  if (m < M) {
+    if (NORM) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * inv_rms);
+    }
+    if (EPI == HB_EPI_SWIGLU) {
+      // columns: [8 gate | 8 up] x 2 -> 16 outputs; output column = n/2 + ...
+      bf16* out = (bf16*)Cv + (size_t)m * ldc + (n >> 1);
+      float y[16];
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float gate = __uint_as_float(r[blk * 16 + j]), up = __uint_as_float(r[blk * 16 + 8 + j]);
+          // silu(g) * u; fast exponential and division: the result is rounded to bfloat16 next
+          y[blk * 8 + j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+        }
+      if (n + 32 <= N && ((((size_t)m * ldc + (n >> 1)) & 7) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 8) {
+          uint4 v;
+          v.x = pack2(y[j], y[j + 1]); v.y = pack2(y[j + 2], y[j + 3]);
+          v.z = pack2(y[j + 4], y[j + 5]); v.w = pack2(y[j + 6], y[j + 7]);
+          *reinterpret_cast<uint4*>(out + j) = v;
+        }
+      } else {
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (n + blk * 16 + 8 + j < N) out[blk * 8 + j] = __float2bfloat16_rn(y[blk * 8 + j]);
+      }
+    } else if (EPI == HB_EPI_STORE) {
+      bf16* out = (bf16*)Cv + (size_t)m * ldc + n;
+      if (n + 32 <= N && ((((size_t)m * ldc + n) & 7) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 v;
+          v.x = pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+          v.y = pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          v.z = pack2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+          v.w = pack2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+          *reinterpret_cast<uint4*>(out + j) = v;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (n + j < N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+    } else {
+      float* out = (float*)Cv + (size_t)m * ldc + n;
+      const bool begin_norm = NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr;
+      bf16* xw = begin_norm ? nm.out_xw + (size_t)m * nm.out_ld + n : nullptr;
+      if (n + 32 <= N && ((((size_t)m * ldc + n) & 3) == 0) && (!begin_norm || ((((size_t)m * nm.out_ld + n) & 7) == 0))) {
+        // every load first, then the arithmetic, then every store: the compiler cannot tell that the
+        // three arrays do not overlap and would otherwise wait for each store before the next load
+        float4 old4[8], w4[8];
+        if (EPI == HB_EPI_RESIDUAL) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) old4[q] = *reinterpret_cast<const float4*>(out + 4 * q);
+        }
+        if (begin_norm) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) w4[q] = *reinterpret_cast<const float4*>(nm.out_w + n + 4 * q);
+        }
+        float v[32];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          v[4 * q] = __uint_as_float(r[4 * q]); v[4 * q + 1] = __uint_as_float(r[4 * q + 1]);
+          v[4 * q + 2] = __uint_as_float(r[4 * q + 2]); v[4 * q + 3] = __uint_as_float(r[4 * q + 3]);
+          if (EPI == HB_EPI_RESIDUAL) {
+            v[4 * q] += old4[q].x; v[4 * q + 1] += old4[q].y; v[4 * q + 2] += old4[q].z; v[4 * q + 3] += old4[q].w;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(out + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        if (begin_norm) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sq += v[j] * v[j];
+#pragma unroll
+          for (int q = 0; q < 8; q += 2) {
+            uint4 pk;
+            pk.x = pack2(v[4 * q] * w4[q].x, v[4 * q + 1] * w4[q].y);
+            pk.y = pack2(v[4 * q + 2] * w4[q].z, v[4 * q + 3] * w4[q].w);
+            pk.z = pack2(v[4 * q + 4] * w4[q + 1].x, v[4 * q + 5] * w4[q + 1].y);
+            pk.w = pack2(v[4 * q + 6] * w4[q + 1].z, v[4 * q + 7] * w4[q + 1].w);
+            *reinterpret_cast<uint4*>(xw + 4 * q) = pk;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (n + j < N) {
+            float v = __uint_as_float(r[j]);
+            if (EPI == HB_EPI_RESIDUAL) v += out[j];
+            out[j] = v;
+            if (begin_norm) {
+              xw[j] = __float2bfloat16_rn(v * nm.out_w[n + j]);
+              sq += v * v;
+            }
+          }
+      }
+    }
+  }
+}
+
 template <int BN, int EPI, bool NORM>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
@@ -134,7 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 4);     // one arrival per epilogue warp
+      mbar_init(acc_empty(b), TG_EPI_WARPS);     // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -211,8 +325,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // epilogue warps: TMEM lane quadrant = warp index modulo 4
+    // epilogue warps: TMEM lane quadrant = warp index modulo 4; warps 2-5 take the first half of a
+    // tile's columns, warps 6-9 the second
     const int quad = warp & 3;
+    const int c_lo = ((warp - 2) >> 2) * (BN / 64), c_hi = c_lo + BN / 64;
     int local = 0;
     bool ok = true;
     TgSegments segs(sc, num_tiles, num_kb);
@@ -246,7 +362,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // a piece is stored as [group of 4 columns][row][4]: the 32 lanes (rows) of a warp write 512 contiguous bytes
         float* mine = sc.ws + (size_t)(2 * blockIdx.x + (tsk - ((int)blockIdx.x * sc.per) / num_kb)) * TG_BM * BN + (quad * 32 + lane) * 4;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = c_lo; c < c_hi; ++c) {
           unsigned r[32];
           tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
           if (m < M) {            // rows beyond M are never read back
@@ -259,24 +375,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty(buf));
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
+        asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight epilogue warps
         if (threadIdx.x == 64) {
           const int old = atomicAdd(sc.counters + tsk, 1);
           *sk_last = old == n_pieces - 1;
           if (*sk_last) sc.counters[tsk] = 0;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         finish = *sk_last != 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");          // everyone has read the flag before it is written again
+        asm volatile("bar.sync 1, 256;" ::: "memory");          // everyone has read the flag before it is written again
         if (finish) __threadfence();
       }
       if (!finish) continue;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = c_lo; c < c_hi; ++c) {
         unsigned r[32];
         if (whole) {
           tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
-          if (c == BN / 32 - 1) {
+          if (c == c_hi - 1) {
             // everything of this accumulator is in registers: the tensor cores may have it back
             tc_fence_before();
             __syncwarp();
@@ -309,119 +425,254 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(acc[j]);
         }
-        const int n = n0 + c * 32;
-        if (m < M) {
-          if (NORM) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * inv_rms);
-          }
-          if (EPI == HB_EPI_SWIGLU) {
-            // columns: [8 gate | 8 up] x 2 -> 16 outputs; output column = n/2 + ...
-            bf16* out = (bf16*)Cv + (size_t)m * ldc + (n >> 1);
-            float y[16];
-#pragma unroll
-            for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float gate = __uint_as_float(r[blk * 16 + j]), up = __uint_as_float(r[blk * 16 + 8 + j]);
-                // silu(g) * u; fast exponential and division: the result is rounded to bfloat16 next
-                y[blk * 8 + j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
-              }
-            if (n + 32 <= N && ((((size_t)m * ldc + (n >> 1)) & 7) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 8) {
-                uint4 v;
-                v.x = pack2(y[j], y[j + 1]); v.y = pack2(y[j + 2], y[j + 3]);
-                v.z = pack2(y[j + 4], y[j + 5]); v.w = pack2(y[j + 6], y[j + 7]);
-                *reinterpret_cast<uint4*>(out + j) = v;
-              }
-            } else {
-#pragma unroll
-              for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (n + blk * 16 + 8 + j < N) out[blk * 8 + j] = __float2bfloat16_rn(y[blk * 8 + j]);
-            }
-          } else if (EPI == HB_EPI_STORE) {
-            bf16* out = (bf16*)Cv + (size_t)m * ldc + n;
-            if (n + 32 <= N && ((((size_t)m * ldc + n) & 7) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 v;
-                v.x = pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                v.y = pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                v.z = pack2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                v.w = pack2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                *reinterpret_cast<uint4*>(out + j) = v;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n + j < N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-            }
-          } else {
-            float* out = (float*)Cv + (size_t)m * ldc + n;
-            const bool begin_norm = NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr;
-            bf16* xw = begin_norm ? nm.out_xw + (size_t)m * nm.out_ld + n : nullptr;
-            if (n + 32 <= N && ((((size_t)m * ldc + n) & 3) == 0) && (!begin_norm || ((((size_t)m * nm.out_ld + n) & 7) == 0))) {
-              // every load first, then the arithmetic, then every store: the compiler cannot tell that the
-              // three arrays do not overlap and would otherwise wait for each store before the next load
-              float4 old4[8], w4[8];
-              if (EPI == HB_EPI_RESIDUAL) {
-#pragma unroll
-                for (int q = 0; q < 8; ++q) old4[q] = *reinterpret_cast<const float4*>(out + 4 * q);
-              }
-              if (begin_norm) {
-#pragma unroll
-                for (int q = 0; q < 8; ++q) w4[q] = *reinterpret_cast<const float4*>(nm.out_w + n + 4 * q);
-              }
-              float v[32];
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                v[4 * q] = __uint_as_float(r[4 * q]); v[4 * q + 1] = __uint_as_float(r[4 * q + 1]);
-                v[4 * q + 2] = __uint_as_float(r[4 * q + 2]); v[4 * q + 3] = __uint_as_float(r[4 * q + 3]);
-                if (EPI == HB_EPI_RESIDUAL) {
-                  v[4 * q] += old4[q].x; v[4 * q + 1] += old4[q].y; v[4 * q + 2] += old4[q].z; v[4 * q + 3] += old4[q].w;
-                }
-              }
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<float4*>(out + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-              if (begin_norm) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) sq += v[j] * v[j];
-#pragma unroll
-                for (int q = 0; q < 8; q += 2) {
-                  uint4 pk;
-                  pk.x = pack2(v[4 * q] * w4[q].x, v[4 * q + 1] * w4[q].y);
-                  pk.y = pack2(v[4 * q + 2] * w4[q].z, v[4 * q + 3] * w4[q].w);
-                  pk.z = pack2(v[4 * q + 4] * w4[q + 1].x, v[4 * q + 5] * w4[q + 1].y);
-                  pk.w = pack2(v[4 * q + 6] * w4[q + 1].z, v[4 * q + 7] * w4[q + 1].w);
-                  *reinterpret_cast<uint4*>(xw + 4 * q) = pk;
-                }
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (n + j < N) {
-                  float v = __uint_as_float(r[j]);
-                  if (EPI == HB_EPI_RESIDUAL) v += out[j];
-                  out[j] = v;
-                  if (begin_norm) {
-                    xw[j] = __float2bfloat16_rn(v * nm.out_w[n + j]);
-                    sq += v * v;
-                  }
-                }
-            }
-          }
-        }
+        tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, inv_rms, sq);
       }
       if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr && m < M)
-        nm.out_sumsq[(size_t)(tile / tiles_m) * nm.out_stride + m] = sq;
+        nm.out_sumsq[(size_t)(2 * (tile / tiles_m) + (c_lo > 0)) * nm.out_stride + m] = sq;
     }
   }
   tc_fence_before();
   __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same product by pairs of CTAs (a thread-block cluster of two, tcgen05 with cta_group::2).
+//
+// A pair owns a 256 x 256 tile of C.  Each CTA loads its own 128 rows of A and 128 of the tile's 256
+// rows of W per stage; one lane of the pair's first CTA issues tcgen05.mma (M=256, N=256, K=16),
+// which reads both CTAs' shared memory and accumulates each CTA's 128 rows in that CTA's tensor
+// memory.  Per CTA and k block that is 32 KB written by TMA and 32 KB read by the tensor cores, where
+// a single CTA's 128 x 256 tile needs 48 KB of each: the single-CTA kernel is bound by shared-memory
+// bandwidth (about 190 bytes a cycle wanted, 128 there), the pair is not.
+//   full[s]   lives in the first CTA: armed there with both CTAs' bytes; both CTAs' TMA loads signal it
+//             (cp.async.bulk.tensor with cta_group::2 may signal the peer's mbarrier; no multicast);
+//   empty[s], acc_full[b]   in both CTAs: tcgen05.commit arrives at both (multicast::cluster on the
+//             commit, which carries no data);
+//   acc_empty[b]  in the first CTA: the sixteen epilogue warps of the pair arrive there.
+// Whole tiles only (no tiles shared between pairs); pairs walk the tiles m fastest.
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned cluster_id_x() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned n_clusters_x() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned mapa_shared(unsigned addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned bar, unsigned parity) {      // arrivals may come from the peer CTA
+  unsigned long long start = 0;
+  for (unsigned i = 0;; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((i & 255u) == 255u) {
+      const unsigned long long now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > TG_WAIT_NS) return false;
+    }
+  }
+}
+// A TMA tile load into this CTA's shared memory that signals an mbarrier given by its cluster address.
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar_cluster) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(unsigned bar) {      // arrives at this barrier in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((unsigned short)3)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair_local(unsigned bar) {      // arrives at this CTA's barrier only
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                                 unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+#define TGP_STAGES 6
+#define TGP_STAGE_BYTES ((TG_BM + 128) * TG_BK * 2)      // 128 rows of A and 128 rows of W, 64 columns each
+#define TGP_SMEM_BYTES (TGP_STAGES * TGP_STAGE_BYTES + 1024 + 256)
+
+template <int EPI, bool NORM>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TG_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
+                         int ldc, int M, int N, int K, int* error_flag, TgNorm nm) {
+  constexpr int BN = 256;
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
+  const unsigned bars = base + TGP_STAGES * TGP_STAGE_BYTES;
+  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + TGP_STAGES * TGP_STAGE_BYTES + (2 * TGP_STAGES + 4) * 8);
+  auto full_bar = [&](int s) { return bars + s * 8; };
+  auto empty_bar = [&](int s) { return bars + (TGP_STAGES + s) * 8; };
+  auto acc_full = [&](int b) { return bars + (2 * TGP_STAGES + b) * 8; };
+  auto acc_empty = [&](int b) { return bars + (2 * TGP_STAGES + 2 + b) * 8; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_ctarank();
+  const int pair = (int)cluster_id_x(), n_pairs = (int)n_clusters_x();
+  const int tiles_m = (M + 2 * TG_BM - 1) / (2 * TG_BM), tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + TG_BK - 1) / TG_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TGP_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);      // the first CTA's producer arms it with both CTAs' bytes
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 2 * TG_EPI_WARPS);     // one arrival per epilogue warp of the pair
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // Each CTA allocates all of its own tensor memory (one CTA per SM: both get column 0), so the
+  // pair's product finds each CTA's half of the accumulator at the same address.
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();               // both CTAs' barriers are initialised before either signals the other's
+  tc_fence_after();
+  pdl_wait();
+  pdl_launch();
+  const unsigned tmem_base = *tmem_slot;
+  const bool tmem_ok = tmem_base == 0u;       // everything was asked for: anything else means the SM was not empty
+  if (!tmem_ok && threadIdx.x == 0) atomicExch(error_flag, 15);
+
+  if (!tmem_ok) {
+    // nothing is issued; fall through to the common end
+  } else if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += n_pairs) {
+        const int m0 = (tile % tiles_m) * 2 * TG_BM + (int)rank * TG_BM, n0 = (tile / tiles_m) * BN + (int)rank * 128;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % TGP_STAGES;
+          if (it >= TGP_STAGES && !mbar_wait_cluster(empty_bar(s), ((it / TGP_STAGES) - 1) & 1)) {
+            atomicExch(error_flag, 11);
+            ok = false;
+            break;
+          }
+          const unsigned full0 = mapa_shared(full_bar(s), 0);      // the first CTA's barrier
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * TGP_STAGE_BYTES);
+          const unsigned a_dst = base + s * TGP_STAGE_BYTES;
+          tma_load_2d_pair(a_dst, &map_a, kb * TG_BK, m0, full0);
+          tma_load_2d_pair(a_dst + TG_BM * TG_BK * 2, &map_w, kb * TG_BK, n0, full0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // D float, A and B bfloat16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24 (M counts both CTAs' rows)
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)((2 * TG_BM) >> 4) << 24);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, ++local) {
+        const int buf = local & 1;
+        if (local >= 2 && !mbar_wait_cluster(acc_empty(buf), ((local >> 1) - 1) & 1)) {
+          atomicExch(error_flag, 14);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % TGP_STAGES;
+          if (!mbar_wait_cluster(full_bar(s), (it / TGP_STAGES) & 1)) {
+            atomicExch(error_flag, 12);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const unsigned a_addr = base + s * TGP_STAGE_BYTES;
+          const unsigned long long da = umma_desc_sw128(a_addr), dw = umma_desc_sw128(a_addr + TG_BM * TG_BK * 2);
+#pragma unroll
+          for (int k = 0; k < TG_BK / 16; ++k)
+            tc_mma_bf16_pair(tmem_acc, da + (unsigned)(k * 32 >> 4), dw + (unsigned)(k * 32 >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit_pair(empty_bar(s));     // both CTAs' stages are free when these MMAs have read them
+        }
+        tc_commit_pair(acc_full(buf));      // both CTAs' accumulators are complete
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int c_lo = ((warp - 2) >> 2) * (BN / 64), c_hi = c_lo + BN / 64;
+    int local = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, ++local) {
+      const int buf = local & 1;
+      const int m0 = (tile % tiles_m) * 2 * TG_BM + (int)rank * TG_BM, n0 = (tile / tiles_m) * BN;
+      const int m = m0 + quad * 32 + lane;
+      float inv_rms = 1.0f, sq = 0.0f;
+      if (NORM && nm.in_sumsq != nullptr && m < M) {
+        float sum = 0.0f;
+        for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
+        inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+      }
+      if (!mbar_wait_cluster(acc_full(buf), (local >> 1) & 1)) {
+        if (lane == 0) atomicExch(error_flag, 13);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
+      const unsigned acc_empty0 = mapa_shared(acc_empty(buf), 0);
+#pragma unroll 1
+      for (int c = c_lo; c < c_hi; ++c) {
+        unsigned r[32];
+        tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+        if (c == c_hi - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty0);
+        }
+        tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, inv_rms, sq);
+      }
+      if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr && m < M)
+        nm.out_sumsq[(size_t)(2 * (tile / tiles_m) + (c_lo > 0)) * nm.out_stride + m] = sq;
+    }
+  }
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();               // neither CTA leaves while the other may still signal its barriers or use its tensor memory
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
@@ -433,6 +684,57 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 static float* g_tg_ws = nullptr;        // set by hb_gemm_tcgen05_set_workspace
 static int* g_tg_counters = nullptr;
 static int g_tg_ws_ctas = 0;
+
+static int tg_sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+// Whether the leftover tiles of a product are cut into runs of k blocks shared between CTAs.
+static bool tg_splits_tiles(int tiles, int num_kb, int sms) {
+  const int rem = tiles % sms;
+  return g_tg_ws != nullptr && g_tg_ws_ctas >= sms && rem > 0 && rem * 2 <= sms && num_kb >= 8 && (long long)rem * num_kb >= 4LL * sms;
+}
+
+// Pairs of CTAs take products of many rows whose tiles are 256 columns wide and all whole.
+static int g_tg_pairs = 1;       // hb_gemm_tcgen05_set_pairs(0) switches them off (for measurements)
+static bool tg_use_pairs(int M, int N, int K) {
+  (void)K;
+  return g_tg_pairs && M >= 512 && N >= 256;
+}
+
+template <int EPI, bool NORM>
+static int tg_launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int* err,
+                          cudaStream_t s, const TgNorm& nm) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, TGP_SMEM_BYTES);
+    if (e != cudaSuccess) HB_FAIL(3, "gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", TGP_SMEM_BYTES, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int tiles = ceil_div(M, 2 * TG_BM) * ceil_div(N, 256);
+  const int pairs = tiles < tg_sm_count() / 2 ? tiles : tg_sm_count() / 2;
+  hb_launch(gemm_tcgen05_pair_kernel<EPI, NORM>, dim3(2 * pairs), dim3(TG_THREADS), TGP_SMEM_BYTES, s, ma, mw, C, ldc, M, N, K, err, nm);
+  HB_CHECK_LAUNCH("gemm_tcgen05 (pairs)");
+  return 0;
+}
+
+template <bool NORM>
+static int tg_dispatch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int epi,
+                            int* err, cudaStream_t s, const TgNorm& nm) {
+  switch (epi) {
+    case HB_EPI_STORE: return tg_launch_pair<HB_EPI_STORE, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
+    case HB_EPI_STORE_F32: return tg_launch_pair<HB_EPI_STORE_F32, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
+    case HB_EPI_RESIDUAL: return tg_launch_pair<HB_EPI_RESIDUAL, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
+    case HB_EPI_SWIGLU: return tg_launch_pair<HB_EPI_SWIGLU, NORM>(ma, mw, C, ldc, M, N, K, err, s, nm);
+  }
+  HB_FAIL(2, "gemm_tcgen05: unknown epilogue %d", epi);
+}
 
 template <int BN, int EPI, bool NORM>
 static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int* err,
@@ -509,6 +811,11 @@ static int tg_tile_cols(int M, int N) {
 // hb_gemm_tcgen05_workspace_floats(ctas) floats and `counters` ctas ints, zero, for ctas >= the
 // number of SMs.  Without it (null) every tile is computed by one CTA.  Calls that use the same
 // workspace must be on one stream.
+// 0: every product by single CTAs (for measurements); 1 (default): pairs of CTAs where they apply.
+extern "C" int hb_gemm_tcgen05_set_pairs(int on) {
+  g_tg_pairs = on ? 1 : 0;
+  return 0;
+}
 extern "C" long long hb_gemm_tcgen05_workspace_floats(int ctas) { return (long long)ctas * TG_WS_FLOATS_PER_CTA; }
 extern "C" int hb_gemm_tcgen05_set_workspace(float* floats, int* counters, int ctas) {
   g_tg_ws = floats;
@@ -528,18 +835,20 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   HB_REQUIRE(error_flag != nullptr, "gemm_tcgen05: an error flag is required");
   CUtensorMap ma, mw;
   const int BN = tg_tile_cols(M, N);
+  const bool pairs = BN == 256 && tg_use_pairs(M, N, K);
   int rc = make_map(&ma, A, M, K, lda, TG_BM);
   if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, BN);
+  rc = make_map(&mw, W, N, K, ldw, pairs ? 128 : BN);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const TgNorm none{};
+  if (pairs) return tg_dispatch_pair<false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
   return BN == 256 ? tg_dispatch<256, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none)
                    : tg_dispatch<128, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
 }
 
-// Tiles of output columns, i.e. rows of out_sumsq, of a product with N output columns.
-extern "C" int hb_gemm_tcgen05_norm_parts(int M, int N) { return ceil_div(N, tg_tile_cols(M, N)); }
+// Half tiles of output columns (one per epilogue thread of a row), i.e. rows of out_sumsq, of a product with N output columns.
+extern "C" int hb_gemm_tcgen05_norm_parts(int M, int N) { return 2 * ceil_div(N, tg_tile_cols(M, N)); }
 
 // The same product with a shared norm on either side (any M):
 //   in_sumsq != null: A holds x * w of a norm over K; results are multiplied by 1 / rms of the rows,
@@ -561,12 +870,14 @@ extern "C" int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, 
   HB_REQUIRE(out_w == nullptr || (((uintptr_t)out_w & 15) == 0), "gemm_tcgen05_norm: the norm weight must be 16-byte aligned");
   CUtensorMap ma, mw;
   const int BN = tg_tile_cols(M, N);
+  const bool pairs = BN == 256 && tg_use_pairs(M, N, K);
   int rc = make_map(&ma, A, M, K, lda, TG_BM);
   if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, BN);
+  rc = make_map(&mw, W, N, K, ldw, pairs ? 128 : BN);
   if (rc) return rc;
   const TgNorm nm{in_sumsq, in_parts, in_stride, in_eps, out_w, (bf16*)out_xw, out_ld, out_sumsq, out_stride};
   cudaStream_t s = (cudaStream_t)stream;
+  if (pairs) return tg_dispatch_pair<true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
   return BN == 256 ? tg_dispatch<256, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm)
                    : tg_dispatch<128, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
 }

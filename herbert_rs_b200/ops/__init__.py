@@ -134,6 +134,11 @@ def set_pdl(mode: int) -> None:
     _libmod.load().hb_set_pdl(int(mode))
 
 
+def set_gemm_pairs(on: bool) -> None:
+    """Whether the prefill product runs as pairs of CTAs (cta_group::2) where that applies (default on)."""
+    _libmod.load().hb_gemm_tcgen05_set_pairs(1 if on else 0)
+
+
 def is_available() -> bool:
     """True when a CUDA device is present (the kernels still have to build and load)."""
     return torch.cuda.is_available()

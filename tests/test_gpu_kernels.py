@@ -558,7 +558,9 @@ def test_attention_decode_refuses_what_it_cannot_do():
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (1, 8, 8), (65, 96, 96), (200, 304, 224), (300, 1000, 1024),
-                                   (257, 24, 4104), (2048, 512, 256), (130, 272, 72)])
+                                   (257, 24, 4104), (2048, 512, 256), (130, 272, 72),
+                                   # 512 rows and more, whole tiles of 256 columns: pairs of CTAs (cta_group::2); ragged edges in M, N and K
+                                   (512, 256, 64), (700, 1000, 1024), (1061, 304, 4104), (513, 272, 72), (2048, 6144, 512)])
 def test_gemm_tcgen05_every_epilogue(M, N, K):
     torch.manual_seed(9)
     a, w = torch.randn(M, K).to(torch.bfloat16), (torch.randn(N, K) * 0.1).to(torch.bfloat16)
