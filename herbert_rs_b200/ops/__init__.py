@@ -89,12 +89,55 @@ def launch_count() -> int:
     return _launches
 
 
+_timeline = None     # while a `timed()` block is open: [(launcher name, start event, end event)]
+
+
 def _run(name: str, *args) -> None:
     global _launches
     _launches += _KERNELS_PER_CALL.get(name, 1)
-    rc = _fn(name)(*args)
+    if _timeline is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = _fn(name)(*args)
+        e1.record()
+        _timeline.append((name, e0, e1))
+    else:
+        rc = _fn(name)(*args)
     if rc != 0:
         raise BackendError(f"{name}: {_libmod.last_error()}")
+
+
+class timed:
+    """Where a step's time goes, by launcher: CUDA events around every launch made inside the block
+    (eager steps only: a replayed graph makes no launches here).  The reference returns per-layer
+    times on request in the same spirit (crates/core/src/backend.rs:97-102, profiler.rs:17-60).
+
+        with ops.timed() as t:
+            engine.step(...)
+        t.by_kernel()     # {launcher: (launches, milliseconds)}, and "(between launches)"
+    """
+
+    def __enter__(self):
+        global _timeline
+        self._saved, _timeline = _timeline, []
+        self._rows = _timeline
+        return self
+
+    def __exit__(self, *exc):
+        global _timeline
+        _timeline = self._saved
+        torch.cuda.synchronize()
+        return False
+
+    def by_kernel(self) -> dict:
+        out: dict = {}
+        for name, e0, e1 in self._rows:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + e0.elapsed_time(e1))
+        if self._rows:
+            whole = self._rows[0][1].elapsed_time(self._rows[-1][2])
+            out["(between launches)"] = (len(self._rows) - 1, whole - sum(ms for _, ms in out.values()))
+        return out
 
 
 def _stream() -> int:

@@ -182,7 +182,7 @@ def test_trace_run_program(model_dirs, plain, tmp_path, dtype):
     steps.append({"step": 12, "entries": [{"id": "c", "tokens": [9], "want": [0]}], "end": ["c"]})
     out = tmp_path / "out"
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["A"], "--dtype", dtype,
-                        "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                        "--out", str(out), "--max-tokens", "128", "--timing"], input="\n".join(json.dumps(s) for s in steps) + "\n",
                        capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
@@ -197,6 +197,12 @@ def test_trace_run_program(model_dirs, plain, tmp_path, dtype):
     g10 = np.fromfile(out / "10.f32", dtype="<f4").reshape(1, 256)
     assert_close(g10.astype(np.float64), ra[39:40], dtype, "trace step 10", plain=plain["A"], ids=a, rows=[39])
     assert not (out / "11.f32").exists()
+    # --timing: one line per step with its device time and, per row of the step's file, request and position
+    index = [json.loads(l) for l in open(out / "index.jsonl")]
+    assert [e["step"] for e in index] == [s["step"] for s in steps] and all(e["ms"] > 0 for e in index)
+    assert index[0]["rows"] == [{"row": 0, "id": "a", "position": 0}, {"row": 1, "id": "a", "position": 29}, {"row": 2, "id": "b", "position": 4}]
+    assert index[1]["rows"] == [{"row": 0, "id": "a", "position": 30}, {"row": 1, "id": "b", "position": 5}] and index[1]["tokens"] == 2
+    assert index[11]["rows"] == [] and index[12]["rows"] == [{"row": 0, "id": "c", "position": 70}]
     g12 = np.fromfile(out / "12.f32", dtype="<f4").reshape(1, 256)
     assert_close(g12.astype(np.float64), rc[70:71], dtype, "trace step 12", plain=plain["A"], ids=c + [9], rows=[70])
 
