@@ -26,3 +26,5 @@ class KernelOptions:
     prefill_attention: str = "tcgen05"
     # Decode attention cuts the keys so that this many CTAs stand on every SM.
     decode_ctas_per_sm: int = 2
+    # ... and into at most this many key ranges per (sequence, kv head).
+    decode_max_splits: int = 16

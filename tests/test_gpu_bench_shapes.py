@@ -139,7 +139,7 @@ def test_prefill_attention_window_edge_at_2048():
 @pytest.mark.parametrize("n_seqs,context", [(1, 2048), (8, 2048), (64, 2048), (1, 4096), (8, 4096), (64, 4095)])
 def test_decode_attention_with_the_engines_splits(n_seqs, context):
     """Plain and fused decode attention (head size 128) at the benchmark's contexts, page table 64
-    wide, with the split count the engine picks: 37 for one sequence, 4 for eight, 1 for sixty-four."""
+    wide, with the split count the engine picks: 16 for one sequence, 4 for eight, 1 for sixty-four."""
     nh, nkv, hd, page = 32, 8, 128, 64
     rng = np.random.default_rng(context + n_seqs)
     lens = [context] + [int(x) for x in rng.integers(context // 2, context + 1, n_seqs - 1)]
@@ -148,7 +148,7 @@ def test_decode_attention_with_the_engines_splits(n_seqs, context):
         sharp.append((1, lens[1] - 1, 7, 65))
     c = _case(nh, nkv, hd, lens, [1] * n_seqs, None, sharp, seed=context + n_seqs, width=64)
     nsplit = ops.decode_splits(n_seqs, nkv, c["table"].shape[1])
-    assert nsplit == {1: 37, 8: 4, 64: 1}[n_seqs]
+    assert nsplit == {1: 16, 8: 4, 64: 1}[n_seqs]
     seq_len = torch.tensor(lens, dtype=torch.int32, device="cuda")
     scratch = torch.full((ops.attention_decode_scratch_floats(n_seqs, nh, hd, nsplit),), float("nan"), device="cuda")
     out = torch.full(c["q"].shape, float("nan"), device="cuda", dtype=BF)
