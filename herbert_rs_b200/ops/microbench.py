@@ -5,6 +5,7 @@
     python -m herbert_rs_b200.ops.microbench decode-attention --seqs 8 --context 2050 --splits 4
     python -m herbert_rs_b200.ops.microbench prefill-attention --seqs 1 --len 2048
     python -m herbert_rs_b200.ops.microbench sampling --seqs 8 --vocab 151936
+    python -m herbert_rs_b200.ops.microbench step --len 2048 --seqs 8          # a whole model's steps, by launcher
 
 Shapes default to the Qwen3-8B layer (hidden 4096, 32 query / 8 key-value heads of 128,
 intermediate 12288).  Every launch of a timed loop reads other weights or another layer's cache
@@ -129,9 +130,49 @@ def sampling(a):
     print(line)
 
 
+def step(a):
+    """A whole model's step by launcher (`ops.timed()`): a prompt of --len tokens, then one eager decode
+    step of --seqs sequences of that length (decode steps normally replay a graph; eager, the gaps
+    between launches are the host's)."""
+    import numpy as np
+
+    import herbert_rs_b200 as hb
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=a.vocab, hidden_size=a.hidden,
+               num_hidden_layers=a.model_layers, num_attention_heads=a.heads, num_key_value_heads=a.kv_heads, head_dim=a.head_dim,
+               intermediate_size=a.intermediate, rope_theta=1e6, rms_norm_eps=1e-6, max_position_embeddings=32768,
+               tie_word_embeddings=False)
+    rt = hb.Runtime("cuda", torch.bfloat16)
+    eng = hb.Engine(hb.random_model(cfg, 0, rt), max_tokens=hb.Engine.pages_for(a.len + 8, a.seqs) * rt.page_size,
+                    max_slots=a.seqs, use_graphs=False)
+    rng = np.random.default_rng(0)
+    slots = [eng.alloc_slot() for _ in range(a.seqs)]
+
+    def show(title, t):
+        d = t.by_kernel()
+        print(f"{title}: {sum(ms for _, ms in d.values()):.3f} ms")
+        for k, (n, ms) in sorted(d.items(), key=lambda kv: -kv[1][1]):
+            print(f"  {k:34s} {n:5d} launches {ms:9.3f} ms {ms / n * 1e3:9.1f} us each")
+
+    for i, s in enumerate(slots):
+        ids = rng.integers(0, a.vocab, a.len).tolist()
+        if i == len(slots) - 1:
+            with ops.timed() as t:
+                eng.step([(s, ids)], "last")
+            show(f"prefill of {a.len} tokens, {a.model_layers} layers", t)
+        else:
+            eng.step([(s, ids)], "last")
+    toks = rng.integers(0, a.vocab, a.seqs).tolist()
+    for _ in range(3):
+        eng.step([(s, [x]) for s, x in zip(slots, toks)], "last")
+    with ops.timed() as t:
+        eng.step([(s, [x]) for s, x in zip(slots, toks)], "last")
+    show(f"eager decode step of {a.seqs} sequences", t)
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="python -m herbert_rs_b200.ops.microbench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=["decode-gemm", "prefill-gemm", "decode-attention", "prefill-attention", "sampling"])
+    ap.add_argument("what", choices=["decode-gemm", "prefill-gemm", "decode-attention", "prefill-attention", "sampling", "step"])
+    ap.add_argument("--model-layers", type=int, default=36, help="step: layers of the model")
     ap.add_argument("--rows", type=int, default=8, help="activation rows of the products")
     ap.add_argument("--layers", type=int, default=12, help="copies of the weights / caches cycled through")
     ap.add_argument("--reps", type=int, default=10)
@@ -157,7 +198,7 @@ def main(argv=None) -> None:
     if a.no_pairs:
         ops.set_gemm_pairs(False)
     {"decode-gemm": decode_gemm, "prefill-gemm": prefill_gemm, "decode-attention": decode_attention,
-     "prefill-attention": prefill_attention, "sampling": sampling}[a.what](a)
+     "prefill-attention": prefill_attention, "sampling": sampling, "step": step}[a.what](a)
 
 
 if __name__ == "__main__":
