@@ -118,7 +118,7 @@ def reference_arm() -> int:
 
 
 WORKLOADS = {
-    # BASELINE.json's fourth and fifth configurations, as written there
+    # the baseline's fourth and fifth configurations (Qwen3-0.6B and Qwen3-32B layer sizes), as written there
     "0.6b": dict(size="0.6b", prompts=16, min_len=32, max_len=1024, steps=256),
     "32b": dict(size="32b", prompts=8, min_len=1024, max_len=1024, steps=128),
 }
