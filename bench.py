@@ -200,7 +200,7 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end measurement")
     ap.add_argument("--no-workloads", action="store_true", help="skip the 0.6B and 32B workloads of the baseline")
     ap.add_argument("--no-fp32-check", action="store_true", help="skip the comparison with the 32-bit engine")
-    ap.add_argument("--pdl", type=int, default=0, help="programmatic dependent launch mode of the kernels (0 off, 1 all, 2 those that ask)")
+    ap.add_argument("--no-pdl", action="store_true", help="prompts without programmatic dependent launch")
     ap.add_argument("--workload", default=None, choices=["0.6b", "32b"],
                     help="run only this workload of the baseline and print its line")
     args = ap.parse_args()
@@ -228,8 +228,8 @@ def main() -> int:
     from herbert_rs_b200 import ops
     from herbert_rs_b200.sampling import device_choose
 
-    if args.pdl:
-        ops.set_pdl(args.pdl)
+    if args.no_pdl:
+        ops.options.pdl_eager = False
     pk = peaks()
     cfg = dict(QWEN3_8B)
     cfg.update(SIZES[args.size])

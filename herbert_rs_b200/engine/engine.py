@@ -246,9 +246,12 @@ class Engine:
 
     def _forward(self, batch: StepBatch):
         """Logits of the step: eagerly, or by replaying the captured graph of this step's shape."""
+        from .. import ops as _ops
         if not (self.use_graphs and batch.is_decode):
             self.rt.workspace = self._eager_ws
+            _ops.set_pdl(1 if _ops.options.pdl_eager else 0)
             return self.model.forward(batch, self.cache)
+        _ops.set_pdl(0)
         key = (batch.n_seqs, batch.n_want, batch.pages_width)
         hit = self._graphs.get(key)
         if hit is not None:
@@ -268,7 +271,6 @@ class Engine:
             if len(self._graphs) >= 64:
                 self._graphs.pop(next(iter(self._graphs)))
             graph = torch.cuda.CUDAGraph()
-            from .. import ops as _ops
             before = _ops.launch_count()
             with torch.cuda.graph(graph):                       # records only; nothing runs
                 captured = self.model.forward(batch, self.cache)

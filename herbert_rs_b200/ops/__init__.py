@@ -183,10 +183,18 @@ def _check(t: torch.Tensor, dtype, name: str) -> None:
         raise BackendError(f"{name} must be contiguous along its last axis")
 
 
+_pdl_mode = None
+
+
 def set_pdl(mode: int) -> None:
-    """Programmatic dependent launch: 0 off (default: inside captured decode graphs it measured
-    slower), 1 every kernel, 2 only the launches that ask for it."""
-    _libmod.load().hb_set_pdl(int(mode))
+    """Programmatic dependent launch: 0 off, 1 every kernel, 2 only the launches that ask for it.
+    The engine switches it on for eager steps (prompts: the next kernel's CTAs start while the last
+    ones of the kernel before drain, 1-3 % of a prefill) and off for steps it records as CUDA graphs
+    (inside a replayed graph it measured slower); see `options.pdl_eager`."""
+    global _pdl_mode
+    if _pdl_mode != int(mode):
+        _libmod.load().hb_set_pdl(int(mode))
+        _pdl_mode = int(mode)
 
 
 def set_gemm_pairs(on: bool) -> None:

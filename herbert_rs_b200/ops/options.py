@@ -28,3 +28,5 @@ class KernelOptions:
     decode_ctas_per_sm: int = 2
     # ... and into at most this many key ranges per (sequence, kv head).
     decode_max_splits: int = 16
+    # Programmatic dependent launch for eager steps (prompts); steps recorded as CUDA graphs never use it.
+    pdl_eager: bool = True
