@@ -97,6 +97,12 @@ long long hb_gemm_tcgen05_workspace_floats(int ctas);
 int hb_gemm_tcgen05_set_workspace(float* floats, int* counters, int ctas);
 int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int
     K, int epi, int* error_flag, void* stream);
+int hb_gemm_tcgen05_qkv_ok(int M, int N);
+int hb_gemm_tcgen05_qkv_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
+    int K, const float* in_sumsq, int in_parts, int in_stride, float in_eps, const float* qw, const float* kw,
+    float eps, const float* cos_tab, const float* sin_tab, int table_rows, const int* tok_seq, const int*
+    tok_pos, const int* seq_pages, int pages_stride, void* kcache, void* vcache, int nh, int nkv, int
+    page_size, int write_cache, int* error_flag, void* stream);
 int hb_gemm_tcgen05_norm_parts(int M, int N);
 int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
     int K, int epi, const float* in_sumsq, int in_parts, int in_stride, float in_eps, const float* out_w,

@@ -55,6 +55,28 @@ struct TgNorm {
   int out_stride;
 };
 
+// The q/k/v product whose epilogue also does what follows it in an attention layer with heads of
+// 128 (crates/backends/backend_common/src/generic_attention/prefill/mod.rs:115-232): per-head RMSNorm
+// of q and k (one weight vector each, or none), rotation of the pairs (j, j + 64) at the token's
+// position, q (bfloat16) into the output, k and v into the paged cache.  A half tile of 128 columns
+// is one head, so an epilogue thread (one row, one half tile) holds a whole head of one token.
+#define HB_EPI_QKV 4
+struct TgQkv {
+  const float* qw;         // norm weights [128], both or neither
+  const float* kw;
+  float eps;
+  const float* cos_tab;    // [table_rows, 64]
+  const float* sin_tab;
+  int table_rows;
+  const int* tok_seq;      // per row of A: sequence of the step, position in it
+  const int* tok_pos;
+  const int* seq_pages;    // [sequences, pages_stride]
+  int pages_stride;
+  bf16* kcache;            // [pages, nkv, page_size, 128]
+  bf16* vcache;
+  int nh, nkv, page_size, write_cache;
+};
+
 // How the tiles are dealt to the CTAs.  Whole rounds of G tiles run one tile per CTA and round.  The
 // tiles left over (fewer than G) would keep only some SMs busy for a whole tile's time; instead
 // their k blocks are laid end to end ("units") and cut into G equal runs, so every CTA gets the
@@ -523,6 +545,98 @@ __device__ __forceinline__ void tc_mma_bf16_pair(unsigned tmem_d, unsigned long 
       : "memory");
 }
 
+// One head (128 columns starting at tensor-memory address taddr) of row m.  Every lane of the warp
+// runs the tensor-memory loads; rows beyond M store nothing.
+__device__ __forceinline__ void tg_epilogue_qkv(unsigned taddr, int m, int head, int M, void* Cv, int ldc, float inv_rms,
+                                                const TgQkv& q) {
+  const int heads_total = q.nh + 2 * q.nkv;
+  if (head >= heads_total) return;                                  // uniform over the warp
+  const bool is_q = head < q.nh, is_k = !is_q && head < q.nh + q.nkv;
+  const bool live = m < M;
+  int pos = 0, seq = 0;
+  if (live) {
+    pos = q.tok_pos[m];
+    seq = q.tok_seq[m];
+  }
+  bf16* dst = nullptr;
+  if (live) {
+    if (is_q) dst = (bf16*)Cv + (size_t)m * ldc + (size_t)head * 128;
+    else if (q.write_cache) {
+      const int page = q.seq_pages[(size_t)seq * q.pages_stride + pos / q.page_size];
+      const int kvh = is_k ? head - q.nh : head - q.nh - q.nkv;
+      dst = (is_k ? q.kcache : q.vcache) + (((size_t)page * q.nkv + kvh) * q.page_size + (pos % q.page_size)) * 128;
+    }
+  }
+  auto store32 = [&](bf16* out, const float* v) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      uint4 u;
+      u.x = pack2(v[j], v[j + 1]); u.y = pack2(v[j + 2], v[j + 3]);
+      u.z = pack2(v[j + 4], v[j + 5]); u.w = pack2(v[j + 6], v[j + 7]);
+      *reinterpret_cast<uint4*>(out + j) = u;
+    }
+  };
+  if (!is_q && !is_k) {                                             // v: as projected
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float t[32];
+      tc_ld32f(taddr + c * 32, t);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) t[j] *= inv_rms;
+      if (dst != nullptr) store32(dst + c * 32, t);
+    }
+    return;
+  }
+  const float* w = is_q ? q.qw : q.kw;
+  float inv = 1.0f;
+  if (w != nullptr) {                                               // r = 1/sqrt(sum(x^2)/128 + eps), x the projected values
+    float ss = 0.0f;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float t[32];
+      tc_ld32f(taddr + c * 32, t);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float x = t[j] * inv_rms;
+        ss += x * x;
+      }
+    }
+    inv = 1.0f / sqrtf(ss / 128.0f + q.eps);
+  }
+  const int trow = pos < q.table_rows ? pos : q.table_rows - 1;
+  const float* cos_row = q.cos_tab + (size_t)trow * 64;
+  const float* sin_row = q.sin_tab + (size_t)trow * 64;
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {                                     // columns 32c.. pair with columns 64 + 32c..
+    float lo[32], hi[32];
+    tc_ld32f(taddr + c * 32, lo);
+    tc_ld32f(taddr + 64 + c * 32, hi);
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 c4 = *reinterpret_cast<const float4*>(cos_row + c * 32 + j), s4 = *reinterpret_cast<const float4*>(sin_row + c * 32 + j);
+        const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+        float wl[4] = {1.f, 1.f, 1.f, 1.f}, wh[4] = {1.f, 1.f, 1.f, 1.f};
+        if (w != nullptr) {
+          const float4 a4 = *reinterpret_cast<const float4*>(w + c * 32 + j), b4 = *reinterpret_cast<const float4*>(w + 64 + c * 32 + j);
+          wl[0] = a4.x; wl[1] = a4.y; wl[2] = a4.z; wl[3] = a4.w;
+          wh[0] = b4.x; wh[1] = b4.y; wh[2] = b4.z; wh[3] = b4.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float x0 = ((lo[j + i] * inv_rms) * inv) * wl[i], x1 = ((hi[j + i] * inv_rms) * inv) * wh[i];
+          lo[j + i] = x0 * cs[i] - x1 * sn[i];
+          hi[j + i] = x0 * sn[i] + x1 * cs[i];
+        }
+      }
+      if (dst != nullptr) {
+        store32(dst + c * 32, lo);
+        store32(dst + 64 + c * 32, hi);
+      }
+    }
+  }
+}
+
 #define TGP_STAGES 6
 #define TGP_STAGE_BYTES ((TG_BM + 128) * TG_BK * 2)      // 128 rows of A and 128 rows of W, 64 columns each
 #define TGP_SMEM_BYTES (TGP_STAGES * TGP_STAGE_BYTES + 1024 + 256)
@@ -530,7 +644,7 @@ __device__ __forceinline__ void tc_mma_bf16_pair(unsigned tmem_d, unsigned long 
 template <int EPI, bool NORM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
-                         int ldc, int M, int N, int K, int* error_flag, TgNorm nm) {
+                         int ldc, int M, int N, int K, int* error_flag, TgNorm nm, TgQkv qk) {
   constexpr int BN = 256;
   extern __shared__ unsigned char smem_raw[];
   const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -655,16 +769,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc_fence_after();
       const unsigned tmem_acc = tmem_base + (unsigned)(buf * BN);
       const unsigned acc_empty0 = mapa_shared(acc_empty(buf), 0);
+      if constexpr (EPI == HB_EPI_QKV) {
+        tg_epilogue_qkv(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c_lo * 32), m, (n0 + c_lo * 32) / 128, M, Cv, ldc, inv_rms, qk);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty0);
+      } else {
 #pragma unroll 1
-      for (int c = c_lo; c < c_hi; ++c) {
-        unsigned r[32];
-        tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
-        if (c == c_hi - 1) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc_empty0);
+        for (int c = c_lo; c < c_hi; ++c) {
+          unsigned r[32];
+          tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+          if (c == c_hi - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty0);
+          }
+          tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, inv_rms, sq);
         }
-        tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, inv_rms, sq);
       }
       if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr && m < M)
         nm.out_sumsq[(size_t)(2 * (tile / tiles_m) + (c_lo > 0)) * nm.out_stride + m] = sq;
@@ -710,7 +831,7 @@ static bool tg_use_pairs(int M, int N, int K) {
 
 template <int EPI, bool NORM>
 static int tg_launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, int* err,
-                          cudaStream_t s, const TgNorm& nm) {
+                          cudaStream_t s, const TgNorm& nm, const TgQkv& qk = TgQkv{}) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, TGP_SMEM_BYTES);
@@ -719,7 +840,7 @@ static int tg_launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C,
   }
   const int tiles = ceil_div(M, 2 * TG_BM) * ceil_div(N, 256);
   const int pairs = tiles < tg_sm_count() / 2 ? tiles : tg_sm_count() / 2;
-  hb_launch(gemm_tcgen05_pair_kernel<EPI, NORM>, dim3(2 * pairs), dim3(TG_THREADS), TGP_SMEM_BYTES, s, ma, mw, C, ldc, M, N, K, err, nm);
+  hb_launch(gemm_tcgen05_pair_kernel<EPI, NORM>, dim3(2 * pairs), dim3(TG_THREADS), TGP_SMEM_BYTES, s, ma, mw, C, ldc, M, N, K, err, nm, qk);
   HB_CHECK_LAUNCH("gemm_tcgen05 (pairs)");
   return 0;
 }
@@ -762,8 +883,7 @@ static int tg_launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
   // with 108 or 128 leftover tiles the products with K = 4096..12288 get slower, because CTAs that
   // start at different k no longer share the weight slabs in L2 in lockstep.)
   const int rem = tiles % sms;
-  if (g_tg_ws != nullptr && g_tg_ws_ctas >= sms && rem > 0 && rem * 2 <= sms && num_kb >= 8 &&
-      (long long)rem * num_kb >= 4LL * sms) {
+  if (tg_splits_tiles(tiles, num_kb, sms)) {
     G = sms;
     sc.full_rounds = tiles / sms;
     sc.sk_tiles = rem;
@@ -845,6 +965,43 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   if (pairs) return tg_dispatch_pair<false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
   return BN == 256 ? tg_dispatch<256, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none)
                    : tg_dispatch<128, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
+}
+
+// The q/k/v product of an attention layer with heads of 128 and full rotation, for steps of 512 rows
+// and more (pairs of CTAs): C[:, :nh*128] = normed, rotated q (bfloat16); k (normed, rotated) and v go
+// into the paged cache and are not written to C.  in_sumsq as in hb_gemm_tcgen05_norm_bf16 (or null).
+// hb_gemm_tcgen05_qkv_ok says whether a product of these sizes can go this way.
+extern "C" int hb_gemm_tcgen05_qkv_ok(int M, int N) {
+  return g_tg_pairs && M >= 512 && N >= 256 && N % 128 == 0 && tg_tile_cols(M, N) == 256;
+}
+extern "C" int hb_gemm_tcgen05_qkv_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K,
+                                        const float* in_sumsq, int in_parts, int in_stride, float in_eps, const float* qw,
+                                        const float* kw, float eps, const float* cos_tab, const float* sin_tab,
+                                        int table_rows, const int* tok_seq, const int* tok_pos, const int* seq_pages,
+                                        int pages_stride, void* kcache, void* vcache, int nh, int nkv, int page_size,
+                                        int write_cache, int* error_flag, void* stream) {
+  HB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05_qkv: sizes must be positive");
+  HB_REQUIRE(hb_gemm_tcgen05_qkv_ok(M, N), "gemm_tcgen05_qkv: %d rows by %d columns do not run as pairs of CTAs with whole heads per half tile", M, N);
+  HB_REQUIRE(nh > 0 && nkv > 0 && N == (nh + 2 * nkv) * 128, "gemm_tcgen05_qkv: %d columns are not %d + 2 x %d heads of 128", N, nh, nkv);
+  HB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldc % 8 == 0, "gemm_tcgen05_qkv: K (%d) and the leading dimensions (%d, %d, %d) must be multiples of 8", K, lda, ldw, ldc);
+  HB_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)C & 15) == 0, "gemm_tcgen05_qkv: operands must be 16-byte aligned");
+  HB_REQUIRE(kcache != nullptr && vcache != nullptr && ((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "gemm_tcgen05_qkv: the cache must be 16-byte aligned");
+  HB_REQUIRE((qw == nullptr) == (kw == nullptr), "gemm_tcgen05_qkv: norm weights for both q and k, or for neither");
+  HB_REQUIRE(qw == nullptr || ((((uintptr_t)qw | (uintptr_t)kw) & 15) == 0), "gemm_tcgen05_qkv: norm weights must be 16-byte aligned");
+  HB_REQUIRE(cos_tab != nullptr && sin_tab != nullptr && table_rows > 0 && ((((uintptr_t)cos_tab | (uintptr_t)sin_tab) & 15) == 0),
+             "gemm_tcgen05_qkv: needs rotation tables, 16-byte aligned");
+  HB_REQUIRE(tok_seq != nullptr && tok_pos != nullptr && seq_pages != nullptr && page_size > 0, "gemm_tcgen05_qkv: needs the step's token and page arrays");
+  HB_REQUIRE(in_sumsq == nullptr || (in_parts > 0 && in_stride >= M), "gemm_tcgen05_qkv: partial sums need a count and a row stride >= M");
+  HB_REQUIRE(error_flag != nullptr, "gemm_tcgen05_qkv: an error flag is required");
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, TG_BM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, ldw, 128);
+  if (rc) return rc;
+  const TgNorm nm{in_sumsq, in_parts, in_stride, in_eps, nullptr, nullptr, 0, nullptr, 0};
+  const TgQkv qk{qw, kw, eps, cos_tab, sin_tab, table_rows, tok_seq, tok_pos, seq_pages, pages_stride, (bf16*)kcache, (bf16*)vcache,
+                 nh, nkv, page_size, write_cache};
+  return tg_launch_pair<HB_EPI_QKV, true>(ma, mw, C, ldc, M, N, K, error_flag, (cudaStream_t)stream, nm, qk);
 }
 
 // Half tiles of output columns (one per epilogue thread of a row), i.e. rows of out_sumsq, of a product with N output columns.

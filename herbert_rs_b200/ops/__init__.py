@@ -40,6 +40,11 @@ _SIGS = {
     "hb_gemm_tcgen05_norm_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                   c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
     "hb_gemm_tcgen05_norm_parts": [c_int, c_int],
+    "hb_gemm_tcgen05_qkv_ok": [c_int, c_int],
+    "hb_gemm_tcgen05_qkv_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_void_p, c_void_p],
     "hb_gemm_tcgen05_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "hb_gemm_stream_bf16": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             ctypes.c_longlong, c_void_p, c_int, c_void_p, c_void_p],
@@ -489,6 +494,31 @@ def gemm_tcgen05_norm(a, w, c, epilogue=EPI_STORE, next_norm=None, scratch=None)
          out.xw.stride(0) if out is not None else 0, out.sumsq.data_ptr() if out is not None else None,
          out.stride if out is not None else 0, _error_flag(c.device).data_ptr(), _stream())
     return out
+
+
+def gemm_qkv_fused_ok(x, wqkv, qkv_out, head_dim, rotary_dim, position) -> bool:
+    """Whether the q/k/v product of this step can also do the per-head norm, the rotation and the
+    cache write in its epilogue: bfloat16, heads of 128 rotated whole, a step of 512 rows and more."""
+    a = x.xw if isinstance(x, PendingNorm) else x
+    return (options.qkv_epilogue and a.dtype == torch.bfloat16 and qkv_out.dtype == torch.bfloat16 and head_dim == 128
+            and rotary_dim == 128 and position is not None and _tcgen05_ok(a, wqkv) and qkv_out.stride(0) % 8 == 0
+            and qkv_out.data_ptr() % 16 == 0 and bool(_fn("hb_gemm_tcgen05_qkv_ok")(a.shape[0], wqkv.shape[0])))
+
+
+def gemm_qkv_fused(x, wqkv, qkv_out, q_weight, k_weight, eps, cos, sin, tok_seq, tok_pos, seq_pages, k_cache, v_cache,
+                   num_heads, num_kv_heads, page_size, write_cache, scratch) -> None:
+    """qkv_out[:, :num_heads*128] = rotated (and normed) q of x @ wqkv.T; k (normed, rotated) and v go
+    into the paged cache.  `x` may be a PendingNorm (its norm is finished inside)."""
+    pend = x if isinstance(x, PendingNorm) else None
+    a = pend.xw if pend is not None else x
+    _tcgen05_workspace(qkv_out.device)
+    _run("hb_gemm_tcgen05_qkv_bf16", a.data_ptr(), a.stride(0), wqkv.data_ptr(), wqkv.stride(0), qkv_out.data_ptr(), qkv_out.stride(0),
+         a.shape[0], wqkv.shape[0], a.shape[1],
+         pend.sumsq.data_ptr() if pend is not None else None, pend.parts if pend is not None else 0,
+         pend.stride if pend is not None else 0, float(pend.eps) if pend is not None else 0.0,
+         _ptr(q_weight), _ptr(k_weight), float(eps), cos.data_ptr(), sin.data_ptr(), cos.shape[0],
+         tok_seq.data_ptr(), tok_pos.data_ptr(), seq_pages.data_ptr(), seq_pages.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+         num_heads, num_kv_heads, page_size, 1 if write_cache else 0, _error_flag(qkv_out.device).data_ptr(), _stream())
 
 
 def _stream_buffers(device):

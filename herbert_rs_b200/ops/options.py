@@ -30,3 +30,5 @@ class KernelOptions:
     decode_max_splits: int = 16
     # Programmatic dependent launch for eager steps (prompts); steps recorded as CUDA graphs never use it.
     pdl_eager: bool = True
+    # Steps of 512 rows and more, heads of 128: per-head norm, rotation and cache write in the q/k/v product's epilogue.
+    qkv_epilogue: bool = True

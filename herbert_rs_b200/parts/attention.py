@@ -61,11 +61,20 @@ class AttentionMixer(Mixer):
     def forward(self, h, residual, batch, cache, next_norm=None):
         ws, T = self.rt.workspace, h.shape[0]
         qkv = ws.take((T, self.qkv_dim), h.dtype)
-        ops.gemm(h, self.wqkv, qkv, scratch=ws.take)
         pages = batch.pages[cache.kv_group]
         pos = self.position
         att = ws.take((T, self.q_dim), h.dtype)
         norm_eps = self.spec.qk_norm.eps if self.spec.qk_norm is not None else 0.0
+        if not batch.is_decode and pos is not None and cache.k is not None and \
+                ops.gemm_qkv_fused_ok(h, self.wqkv, qkv, self.hd, pos.rotary_dim, pos):
+            # long prompts: head norm, rotation and cache write happen in the product's epilogue
+            ops.gemm_qkv_fused(h, self.wqkv, qkv, self.q_norm, self.k_norm, norm_eps, pos.cos, pos.sin, batch.tok_seq,
+                               batch.tok_pos, pages, cache.k, cache.v, self.nh, self.nkv, cache.page_size, cache.writes_kv,
+                               ws.take)
+            ops.attention(qkv, qkv.stride(0), att, cache.k, cache.v, batch, self.nh, self.nkv, self.hd,
+                          cache.page_size, self.spec.scale, self.spec.window, pages, scratch=ws.take)
+            return ops.gemm(att, self.wo, residual, ops.EPI_RESIDUAL, next_norm=next_norm, scratch=ws.take)
+        ops.gemm(h, self.wqkv, qkv, scratch=ws.take)
         if batch.is_decode and pos is not None and ops.attention_decode_fused_ok(
                 qkv, att, self.nh, self.nkv, self.hd, cache.page_size, pos.rotary_dim, batch.n_seqs):
             nsplit = ops.decode_splits(batch.n_seqs, self.nkv, pages.shape[1] * (cache.page_size // 64))

@@ -752,3 +752,54 @@ def test_attention_prefill_tcgen05_finds_a_far_key_and_the_windows_edge():
         row = (0 if b == 0 else 300) + qpos - int(pos0[b])
         target = c["vs"][b][kpos, h // (nh // nkv)]
         assert (((out[row].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit
+
+
+@pytest.mark.parametrize("norm,shared_norm,write", [(True, False, True), (False, False, True), (True, True, True), (True, False, False)])
+def test_qkv_product_with_head_norm_rotation_and_cache_write_in_its_epilogue(norm, shared_norm, write):
+    """Long prompts, heads of 128: q = rotate(norm(x Wq^T)) into the output, k likewise and v as
+    projected into the paged cache, all in the product's epilogue (pairs of CTAs), against float64."""
+    torch.manual_seed(41)
+    nh, nkv, hd, page, eps = 16, 4, 128, 64, 1e-6
+    lens, pos0 = [700, 401], [130, 0]                  # the first sequence continues at position 130
+    M, K, N = sum(lens), 264, (nh + 2 * nkv) * hd
+    x = torch.randn(M, K).to(torch.bfloat16)
+    w = (torch.randn(N, K) * 0.1).to(torch.bfloat16)
+    qw, kw = 1 + 0.1 * torch.randn(hd), 1 + 0.1 * torch.randn(hd)
+    cos, sin = rope_tables(hd, 10000.0, 1024, torch.float32)
+    tok_seq = torch.tensor(sum(([b] * n for b, n in enumerate(lens)), []), dtype=torch.int32)
+    tok_pos = torch.tensor(sum((list(range(p, p + n)) for p, n in zip(pos0, lens)), []), dtype=torch.int32)
+    n_pages = 32
+    table = torch.randperm(n_pages)[:2 * 14].to(torch.int32).view(2, 14)
+    kc = torch.full((n_pages, nkv, page, hd), 9.0, dtype=torch.bfloat16, device="cuda")
+    vc = torch.full((n_pages, nkv, page, hd), 9.0, dtype=torch.bfloat16, device="cuda")
+    out = torch.full((M, N + 8), 7.0, dtype=torch.bfloat16, device="cuda")[:, :N]
+    a = dev(x)
+    ref_in = x.double()
+    if shared_norm:            # x = (residual * nw) with the row's 1/rms still to come
+        sumsq = (torch.rand(3, (M + 3) // 4 * 4) * 40.0 + 1.0)
+        a = ops.PendingNorm(dev(x), dev(sumsq), 3, 1e-5)
+        ref_in = x.double() / torch.sqrt(sumsq[:, :M].double().sum(0) / K + 1e-5)[:, None]
+    assert ops.gemm_qkv_fused_ok(a, dev(w), out, hd, hd, object())
+    ops.gemm_qkv_fused(a, dev(w), out, dev(qw) if norm else None, dev(kw) if norm else None, eps, dev(cos), dev(sin), dev(tok_seq),
+                       dev(tok_pos), dev(table), kc, vc, nh, nkv, page, write, None)
+    ops.check_kernel_errors()
+    y = ref_in @ w.double().T
+    q = y[:, :nh * hd].view(M, nh, hd)
+    k = y[:, nh * hd:(nh + nkv) * hd].view(M, nkv, hd)
+    v = y[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    if norm:
+        q, k = rms_norm(q, qw.double(), eps), rms_norm(k, kw.double(), eps)
+    c, s = cos.double()[tok_pos.long()], sin.double()[tok_pos.long()]
+    q, k = apply_rope(q, c, s, hd), apply_rope(k, c, s, hd)
+    close(out[:, :nh * hd], q.reshape(M, -1), torch.bfloat16)
+    assert (out[:, nh * hd:] == 7.0).all()                     # k and v are not written to the output
+    written = torch.zeros(n_pages, page, dtype=torch.bool)
+    if write:
+        rows = torch.stack([table[tok_seq.long(), (tok_pos // page).long()].long(), (tok_pos % page).long()], 1)
+        got_k = kc[rows[:, 0], :, rows[:, 1]].double().cpu()     # [M, nkv, hd]
+        got_v = vc[rows[:, 0], :, rows[:, 1]].double().cpu()
+        close(got_k, k, torch.bfloat16)
+        close(got_v, v, torch.bfloat16)
+        written[rows[:, 0], rows[:, 1]] = True
+    untouched = lambda cch: cch.cpu().float().permute(0, 2, 1, 3)[~written]
+    assert (untouched(kc) == 9.0).all() and (untouched(vc) == 9.0).all()
