@@ -481,7 +481,8 @@ def test_attention_decode_kernel(nh, nkv, hd, window, nsplit):
 
 
 @pytest.mark.parametrize("nh,nkv,window,nsplit,norm", [(8, 2, 0, 1, True), (8, 2, 0, 3, True), (4, 4, 100, 2, False),
-                                                       (12, 1, 0, 4, True), (16, 8, 70, 5, True)])
+                                                       (12, 1, 0, 4, True), (16, 8, 70, 5, True), (10, 2, 0, 3, True),
+                                                       (3, 1, 90, 2, True), (9, 1, 0, 2, False)])
 def test_attention_decode_fused_equals_the_three_kernels_it_replaces(nh, nkv, window, nsplit, norm):
     """Norm + rotation + cache write, attention, combine in one launch (head size 128) against the
     same work as separate kernels: the bits of the output and of the cache must agree, the counters
@@ -713,7 +714,7 @@ def test_gemm_stream_refuses_what_it_cannot_do():
         ops.gemm_stream(a[:4, :60], w[:, :60], torch.empty(4, 32, device="cuda", dtype=torch.bfloat16))
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (4, 4, 64), (6, 3, 128), (2, 1, 64)])
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (4, 4, 64), (6, 3, 128), (2, 1, 64), (10, 2, 128), (3, 1, 128), (3, 3, 128)])
 @pytest.mark.parametrize("window", [None, 70, 200])
 def test_attention_prefill_tcgen05_kernel(nh, nkv, hd, window):
     for lens, qlens in [([1, 70, 33, 200], [1, 70, 33, 200]), ([300, 130, 64], [100, 1, 64]), ([257], [129]), ([700], [700])]:
@@ -754,12 +755,13 @@ def test_attention_prefill_tcgen05_finds_a_far_key_and_the_windows_edge():
         assert (((out[row].view(nh, hd)[h].float().cpu() - target).abs().max()) < 0.05) == hit
 
 
+@pytest.mark.parametrize("heads", [(16, 4), (15, 1), (20, 4)])
 @pytest.mark.parametrize("norm,shared_norm,write", [(True, False, True), (False, False, True), (True, True, True), (True, False, False)])
-def test_qkv_product_with_head_norm_rotation_and_cache_write_in_its_epilogue(norm, shared_norm, write):
+def test_qkv_product_with_head_norm_rotation_and_cache_write_in_its_epilogue(norm, shared_norm, write, heads):
     """Long prompts, heads of 128: q = rotate(norm(x Wq^T)) into the output, k likewise and v as
     projected into the paged cache, all in the product's epilogue (pairs of CTAs), against float64."""
     torch.manual_seed(41)
-    nh, nkv, hd, page, eps = 16, 4, 128, 64, 1e-6
+    (nh, nkv), hd, page, eps = heads, 128, 64, 1e-6
     lens, pos0 = [700, 401], [130, 0]                  # the first sequence continues at position 130
     M, K, N = sum(lens), 264, (nh + 2 * nkv) * hd
     x = torch.randn(M, K).to(torch.bfloat16)
