@@ -201,6 +201,7 @@ def main() -> int:
     ap.add_argument("--no-workloads", action="store_true", help="skip the 0.6B and 32B workloads of the baseline")
     ap.add_argument("--no-fp32-check", action="store_true", help="skip the comparison with the 32-bit engine")
     ap.add_argument("--no-pdl", action="store_true", help="prompts without programmatic dependent launch")
+    ap.add_argument("--pdl-graph", type=int, default=None, help="programmatic dependent launch inside recorded decode steps (0, 1, 2)")
     ap.add_argument("--workload", default=None, choices=["0.6b", "32b"],
                     help="run only this workload of the baseline and print its line")
     args = ap.parse_args()
@@ -230,6 +231,8 @@ def main() -> int:
 
     if args.no_pdl:
         ops.options.pdl_eager = False
+    if args.pdl_graph is not None:
+        ops.options.pdl_graph = args.pdl_graph
     pk = peaks()
     cfg = dict(QWEN3_8B)
     cfg.update(SIZES[args.size])

@@ -320,8 +320,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ __align__(16) bf16 sm_q[FUSED ? 8 * NH * HD : 8];
   __shared__ int s_last;
-  pdl_wait();
-  pdl_launch();
+  // Before the wait on the kernel before: only what the host wrote ahead of the step (lengths, page
+  // tables) and what earlier steps left in the cache.
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int G = a.nh / a.nkv;
@@ -344,19 +344,6 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   __shared__ int page_ids[AD_MAX_TILES];
   for (int i = threadIdx.x; i < t1 - t0; i += AD_THREADS) page_ids[i] = pages[(t0 + i) / tiles_per_page];
   const bool writer = FUSED && f.write_cache && t0 < t1 && t1 == tile_hi;   // this CTA's keys end with the new position
-  if (writer) {
-    // store the new token's key (normed, rotated) and value before the pages are read
-    const int trow = p < f.table_rows ? p : f.table_rows - 1;
-    const bf16* row = f.qkv + (size_t)b * f.ld;
-    const size_t dst = (((size_t)pages[p / a.page_size] * a.nkv + kvh) * a.page_size + (p % a.page_size)) * HD;
-    if (warp == 0) {
-      norm_rotate_head128<bf16>(lane < 16, row + (size_t)(a.nh + kvh) * HD, f.kcache_w + dst, f.kw, f.eps,
-                                f.cos_tab + (size_t)trow * 64, f.sin_tab + (size_t)trow * 64, lane & 15);
-    } else if (warp == 1) {
-      const bf16* v = row + (size_t)(a.nh + a.nkv + kvh) * HD;
-      *reinterpret_cast<uint2*>(f.vcache_w + dst + 4 * lane) = *reinterpret_cast<const uint2*>(v + 4 * lane);
-    }
-  }
   __syncthreads();
 
   constexpr int SLOTS = HD / 16;
@@ -382,6 +369,35 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
       cp_async16_s(vs + s_off[i], vg + g_off[i]);
     }
   };
+  const int S = a.stages;
+  auto first_tiles = [&]() {
+    for (int i = 0; i < S - 1; ++i) {
+      if (t0 + i < t1) issue(t0 + i, i);
+      cp_async_commit();
+    }
+  };
+  // The tile with the new position is written in this step (here, or by a kernel before this one):
+  // a CTA whose first loads would reach it starts them after the wait, every other one before.
+  const bool early = !(t0 < t1 && t1 == tile_hi && t1 - t0 <= S - 1);
+  if (early) first_tiles();
+  pdl_wait();
+  if (writer) {
+    // store the new token's key (normed, rotated) and value before the pages are read
+    const int trow = p < f.table_rows ? p : f.table_rows - 1;
+    const bf16* row = f.qkv + (size_t)b * f.ld;
+    const size_t dst = (((size_t)pages[p / a.page_size] * a.nkv + kvh) * a.page_size + (p % a.page_size)) * HD;
+    if (warp == 0) {
+      norm_rotate_head128<bf16>(lane < 16, row + (size_t)(a.nh + kvh) * HD, f.kcache_w + dst, f.kw, f.eps,
+                                f.cos_tab + (size_t)trow * 64, f.sin_tab + (size_t)trow * 64, lane & 15);
+    } else if (warp == 1) {
+      const bf16* v = row + (size_t)(a.nh + a.nkv + kvh) * HD;
+      *reinterpret_cast<uint2*>(f.vcache_w + dst + 4 * lane) = *reinterpret_cast<const uint2*>(v + 4 * lane);
+    }
+  }
+  if (!early) {
+    __syncthreads();        // the new key and value are stored before their tile is fetched
+    first_tiles();
+  }
   // A-operand fragments come from shared memory: K rows as they lie, V transposed
   const int lm = lane >> 3;
   const unsigned k_lane = (unsigned)((warp * 16 + (lm & 1) * 8 + (lane & 7)) * row_bytes + (lm >> 1) * 16);
@@ -397,11 +413,6 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
     for (int i = 0; i < HD / 16; ++i) o[n][i][0] = o[n][i][1] = o[n][i][2] = o[n][i][3] = 0.0f;
   }
 
-  const int S = a.stages;
-  for (int i = 0; i < S - 1; ++i) {
-    if (t0 + i < t1) issue(t0 + i, i);
-    cp_async_commit();
-  }
   if (FUSED) {
     // the query heads of this group, normed and rotated, while the first pages are on their way
     const int trow = p < f.table_rows ? p : f.table_rows - 1;
@@ -504,6 +515,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
   }
   cp_async_wait<0>();
   __syncthreads();
+  pdl_launch();     // the keys are read: the next kernel's CTAs may come in while the partial results meet
 
   // ---- merge the 4 warps through shared memory ---------------------------------------------------
   constexpr int HP = 8 * NH;                               // heads, padded
@@ -754,11 +766,11 @@ extern "C" int hb_attention_decode_fused_bf16(const void* qkv, int ld, void* out
   if (nh / nkv <= 8) {
     e = cudaFuncSetAttribute(attention_decode_km_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode_fused: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_km_kernel<1, true>, dim3(grid), dim3(AD_THREADS), smem, s, a, f);
+    hb_launch_pdl(attention_decode_km_kernel<1, true>, dim3(grid), dim3(AD_THREADS), smem, s, a, f);
   } else {
     e = cudaFuncSetAttribute(attention_decode_km_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) HB_FAIL(3, "attention_decode_fused: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    hb_launch(attention_decode_km_kernel<2, true>, dim3(grid), dim3(AD_THREADS), smem, s, a, f);
+    hb_launch_pdl(attention_decode_km_kernel<2, true>, dim3(grid), dim3(AD_THREADS), smem, s, a, f);
   }
   HB_CHECK_LAUNCH("attention_decode_fused");
   return 0;

@@ -37,8 +37,10 @@ void hb_set_error(const char* fmt, ...);
 // (hb_set_pdl(1); off by default) a kernel may be scheduled while its predecessor in the stream is
 // still draining; it must then call pdl_wait() before it reads anything the predecessor wrote or
 // writes anything the predecessor may still read.  pdl_launch() tells the hardware that the next
-// kernel may start its own prologue; it is called after pdl_wait(), so that at most one kernel
-// ahead of the running one sits on the SMs (called before, the whole chain piles up there).  Both are no-ops for a kernel launched without the attribute.
+// kernel may start its own prologue.  It is called after pdl_wait(), so that at most one kernel
+// ahead of the running one sits on the SMs, and in the long decode kernels only when the CTA's own
+// loads are done: CTAs that wait beside working ones cost those issue slots (measured: the step
+// twice as long with the trigger at the start).  Both are no-ops for a kernel launched without the attribute.
 int hb_pdl_enabled(void);   // 0 off, 1 every kernel, 2 only the launches that ask for it (hb_launch_pdl)
 template <typename... KArgs, typename... Args>
 static inline cudaError_t hb_launch_ex(int want_pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

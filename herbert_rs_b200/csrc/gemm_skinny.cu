@@ -101,7 +101,6 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
   set_rows(unit);
   load_w(warp, wa, wb);
   pdl_wait();
-  pdl_launch();
   if (NORM) {
     // 1 / rms of the activation rows from the producer's partial sums: warp w sums rows w and w + 8
     // in a fixed order; the first __syncthreads() before an epilogue publishes them
@@ -152,6 +151,11 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
     if (iu + 1 < units_per_cta && unit + 1 < n_units) {   // the next unit's first batch, under this unit's reduction
       set_rows(unit + 1);
       load_w(warp, wa, wb);
+    } else {
+      // this CTA's last weights are in: the next kernel's CTAs may take the places that free up and
+      // fetch their own first weights while the partial sums here are combined.  Not earlier: CTAs
+      // that wait on an SM take issue slots from the ones that still work there.
+      pdl_launch();
     }
     // accumulator layout: acc[..][nt][0..1] = (weight row g, tokens nt*8 + 2t, 2t+1); [2..3] = row g+8
 #pragma unroll

@@ -251,7 +251,7 @@ class Engine:
             self.rt.workspace = self._eager_ws
             _ops.set_pdl(1 if _ops.options.pdl_eager else 0)
             return self.model.forward(batch, self.cache)
-        _ops.set_pdl(0)
+        _ops.set_pdl(int(_ops.options.pdl_graph))
         key = (batch.n_seqs, batch.n_want, batch.pages_width)
         hit = self._graphs.get(key)
         if hit is not None:

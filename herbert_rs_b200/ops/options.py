@@ -30,5 +30,7 @@ class KernelOptions:
     decode_max_splits: int = 16
     # Programmatic dependent launch for eager steps (prompts); steps recorded as CUDA graphs never use it.
     pdl_eager: bool = True
+    # The same inside recorded decode steps: 0 off, 1 every kernel, 2 only the products that load weights before they wait.
+    pdl_graph: int = 0
     # Steps of 512 rows and more, heads of 128: per-head norm, rotation and cache write in the q/k/v product's epilogue.
     qkv_epilogue: bool = True

@@ -394,3 +394,37 @@ def test_a_kernel_that_gave_up_is_reported_and_the_counters_start_afresh(model_d
     eng.check_kernels()
     assert_close(replay_tail_one_by_one(eng, ids, 8), ref, "bfloat16", "after", plain=plain["D"], ids=ids)
     assert_close(replay_whole(eng, ids), ref, "bfloat16", "after, whole", plain=plain["D"], ids=ids)
+
+
+@pytest.mark.gpu
+def test_decode_steps_launched_ahead_of_their_predecessor_give_the_same_bits(model_dirs, plain):
+    """Programmatic dependent launch: a product fetches its first weights, and the fused attention its
+    first keys of earlier steps, before the kernel before them has ended.  Inside recorded graphs
+    (an option, off by default) and eagerly, the logits are the bits of the plain stream order."""
+    from herbert_rs_b200 import ops
+    rng = np.random.default_rng(43)
+    lens = [150, 63, 257]
+    reqs = [random_ids(rng, 1000, n + 24) for n in lens]
+
+    def run(**kw):
+        eng = engine_for(model_dirs["D"], "bfloat16", **kw)
+        slots = [eng.alloc_slot() for _ in reqs]
+        rows = [to_np(eng.step([(s, r[:n]) for s, r, n in zip(slots, reqs, lens)], "last"))]
+        for t in range(24):        # the second request crosses into a new page, where its only tile holds the new key
+            rows.append(to_np(eng.step([(s, [r[n + t]]) for s, r, n in zip(slots, reqs, lens)], "last")))
+        return np.stack(rows)
+
+    saved = ops.options.pdl_graph, ops.options.pdl_eager
+    try:
+        ops.options.pdl_graph, ops.options.pdl_eager = 0, False
+        base = run()
+        assert_close(base[:, 0], plain["D"].logits(reqs[0]).numpy()[lens[0] - 1:lens[0] + 24], "bfloat16", "stream order",
+                     plain=plain["D"], ids=reqs[0], rows=list(range(lens[0] - 1, lens[0] + 24)))
+        for mode in (1, 2):
+            ops.options.pdl_graph = mode
+            assert np.array_equal(run(), base), f"recorded, mode {mode}"
+        ops.options.pdl_graph, ops.options.pdl_eager = 0, True
+        assert np.array_equal(run(use_graphs=False), base), "eager"
+    finally:
+        ops.options.pdl_graph, ops.options.pdl_eager = saved
+        ops.set_pdl(0)
