@@ -93,6 +93,7 @@ int hb_gemm_stream_bf16(const void* X, int ldx, const void* W, int ldw, void* C,
 
 // gemm_tcgen05.cu: prefill product, TMA + tcgen05, persistent; optional shared norm
 int hb_gemm_tcgen05_set_pairs(int on);
+int hb_gemm_tcgen05_set_ksplit(int on);
 long long hb_gemm_tcgen05_workspace_floats(int ctas);
 int hb_gemm_tcgen05_set_workspace(float* floats, int* counters, int ctas);
 int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int

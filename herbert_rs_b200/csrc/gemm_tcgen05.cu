@@ -240,6 +240,66 @@ __device__ __forceinline__ void tg_epilogue32(unsigned (&r)[32], int m, int n, i
   }
 }
 
+// The same for 8 consecutive output columns whose float results are in v (store, store as float, add
+// into the residual stream and begin the next norm; SwiGLU needs its groups of 16 and goes by 32).
+template <int EPI, bool NORM>
+__device__ __forceinline__ void tg_epilogue8(float (&v)[8], int m, int n, int M, int N, void* Cv, int ldc, const TgNorm& nm,
+                                             float inv_rms, float& sq) {
+  static_assert(EPI != HB_EPI_SWIGLU, "SwiGLU goes by chunks of 32 columns");
+  if (m >= M || n >= N) return;
+  if (NORM) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= inv_rms;
+  }
+  const bool whole = n + 8 <= N;
+  if (EPI == HB_EPI_STORE) {
+    bf16* out = (bf16*)Cv + (size_t)m * ldc + n;
+    if (whole && ((((size_t)m * ldc + n) & 7) == 0)) {
+      uint4 pk;
+      pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(out) = pk;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (n + j < N) out[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* out = (float*)Cv + (size_t)m * ldc + n;
+    const bool begin_norm = NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr;
+    bf16* xw = begin_norm ? nm.out_xw + (size_t)m * nm.out_ld + n : nullptr;
+    if (whole && ((((size_t)m * ldc + n) & 3) == 0) && (!begin_norm || ((((size_t)m * nm.out_ld + n) & 7) == 0))) {
+      if (EPI == HB_EPI_RESIDUAL) {
+        const float4 o0 = *reinterpret_cast<const float4*>(out), o1 = *reinterpret_cast<const float4*>(out + 4);
+        v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
+        v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
+      }
+      *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(out + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      if (begin_norm) {
+        const float4 w0 = *reinterpret_cast<const float4*>(nm.out_w + n), w1 = *reinterpret_cast<const float4*>(nm.out_w + n + 4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
+        uint4 pk;
+        pk.x = pack2(v[0] * w0.x, v[1] * w0.y); pk.y = pack2(v[2] * w0.z, v[3] * w0.w);
+        pk.z = pack2(v[4] * w1.x, v[5] * w1.y); pk.w = pack2(v[6] * w1.z, v[7] * w1.w);
+        *reinterpret_cast<uint4*>(xw) = pk;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (n + j < N) {
+          float x = v[j];
+          if (EPI == HB_EPI_RESIDUAL) x += out[j];
+          out[j] = x;
+          if (begin_norm) {
+            xw[j] = __float2bfloat16_rn(x * nm.out_w[n + j]);
+            sq += x * x;
+          }
+        }
+    }
+  }
+}
+
 template <int BN, int EPI, bool NORM>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
@@ -800,6 +860,244 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// At most 128 rows (a decode batch, a short prompt) against a matrix with few tiles of output
+// columns: the time is the weight stream's, and a tile per CTA would leave most SMs without work.
+// Here a thread-block cluster of S CTAs owns a tile and each CTA a range of K.  A CTA streams its
+// range through the ring into one accumulator and then sends every row of it, as floats, into the
+// shared memory of the CTA that finishes that row (rows are dealt in S blocks; stores through
+// distributed shared memory, which nobody waits for).  After one cluster barrier every CTA adds the
+// S partial rows it was sent, in the order of their k ranges, and runs the epilogue from its own
+// shared memory.  No workspace in global memory, no counters, nobody finishes alone, and no
+// multicast: every CTA loads its own slabs.  Up to 64 rows, the activation slab of a stage is 64
+// rows; the tensor cores still multiply 128, and what they make of the rows beyond (the weight slab
+// behind it) is never stored.
+__device__ __forceinline__ unsigned cluster_nctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f4(unsigned cluster_addr, float x, float y, float z, float w) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(cluster_addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+#define TGK_RING_BYTES (225 * 1024)      // per CTA: the ring of stages and, behind it, the rows it is sent
+#define TGK_SMEM_BYTES (TGK_RING_BYTES + 1024 + 256)
+#define TGK_MAX_STAGES 8
+
+struct TgKsplit {
+  int bn;         // output columns per tile: 128, 192 or 256 (whole halves of 128-column tiles: a following norm's partial sums are kept per 64 columns)
+  int ways;       // CTAs per tile = size of the cluster; 0: this product does not go that way
+  int a_rows;     // rows of the activation slab per stage: 64 or 128
+  int stages;
+  int rows_per;   // rows each CTA finishes
+};
+
+template <int EPI, bool NORM>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+gemm_tcgen05_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
+                           int ldc, int M, int N, int K, TgKsplit plan, int* error_flag, TgNorm nm) {
+  const int bn = plan.bn, STAGES = plan.stages, rows_per = plan.rows_per;
+  const int a_bytes = plan.a_rows * TG_BK * 2, STAGE_BYTES = a_bytes + bn * TG_BK * 2;
+  const int row_floats = bn + 4;      // a partial row in shared memory, padded against bank conflicts
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
+  const int recv_off = STAGES * STAGE_BYTES;                 // [S][rows_per][row_floats] floats: what the cluster sends this CTA
+  const unsigned bars = base + TGK_RING_BYTES;               // full[8], empty[8], acc_full; then the tensor-memory slot
+  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + TGK_RING_BYTES + (2 * TGK_MAX_STAGES + 1) * 8);
+  auto full_bar = [&](int st) { return bars + st * 8; };
+  auto empty_bar = [&](int st) { return bars + (TGK_MAX_STAGES + st) * 8; };
+  const unsigned acc_full = bars + 2 * TGK_MAX_STAGES * 8;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_ctarank(), S = (int)cluster_nctarank();
+  const int n0 = (int)cluster_id_x() * bn;
+  const int num_kb = (K + TG_BK - 1) / TG_BK;
+  const int kb0 = (int)(((long long)num_kb * rank) / S), kb1 = (int)(((long long)num_kb * (rank + 1)) / S);
+  const unsigned tmem_cols = bn <= 128 ? 128u : 256u;
+  float first_inv_rms = 1.0f;
+
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < STAGES; ++st) {
+      mbar_init(full_bar(st), 1);
+      mbar_init(empty_bar(st), 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  cluster_arrive();                 // "this CTA runs": waited for before anything is sent to it
+  pdl_wait();
+  const unsigned tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0, st = it % STAGES;
+        if (it >= STAGES && !mbar_wait(empty_bar(st), ((it / STAGES) - 1) & 1)) {
+          atomicExch(error_flag, 21);
+          break;
+        }
+        mbar_expect_tx(full_bar(st), STAGE_BYTES);
+        const unsigned a_dst = base + st * STAGE_BYTES;
+        tma_load_2d(a_dst, &map_a, kb * TG_BK, 0, full_bar(st));
+        tma_load_2d(a_dst + a_bytes, &map_w, kb * TG_BK, n0, full_bar(st));
+      }
+    }
+    __syncwarp();
+    cluster_wait();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0, st = it % STAGES;
+        if (!mbar_wait(full_bar(st), (it / STAGES) & 1)) {
+          atomicExch(error_flag, 22);
+          break;
+        }
+        tc_fence_after();
+        const unsigned a_addr = base + st * STAGE_BYTES;
+        const unsigned w_addr = a_addr + a_bytes;
+#pragma unroll
+        for (int k = 0; k < TG_BK / 16; ++k)
+          tc_mma_bf16(tmem_acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(w_addr + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        tc_commit(empty_bar(st));
+      }
+      tc_commit(acc_full);          // arrives when every MMA is complete
+    }
+    __syncwarp();
+    cluster_wait();
+  } else {
+    // row m of this CTA's partial tile goes to the CTA that finishes it: slot [this rank][m - first row of that CTA]
+    const int quad = warp & 3, m = quad * 32 + lane;
+    const int chunks = bn >> 5, first = (chunks + 1) >> 1;
+    const int c_lo = warp < 6 ? 0 : first, c_hi = warp < 6 ? first : chunks;
+    // While the tensor cores work: what the first piece of a row this thread finishes will need from
+    // global memory (1 / rms of the row; the residual and the next norm's weights into L1).
+    {
+      const int per_row = EPI == HB_EPI_SWIGLU ? chunks : bn >> 3, cols = EPI == HB_EPI_SWIGLU ? 32 : 8;
+      const int item = (int)threadIdx.x - 64, frl = item / per_row, fm = rank * rows_per + frl;
+      if (frl < rows_per && fm < M) {
+        if (NORM && nm.in_sumsq != nullptr) {
+          float sum = 0.0f;
+          for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + fm];
+          first_inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+        }
+        const int fn = n0 + (item % per_row) * cols;
+        if (fn < N) {
+          if (EPI == HB_EPI_RESIDUAL) prefetch_l1((const float*)Cv + (size_t)fm * ldc + fn);
+          if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) prefetch_l1(nm.out_w + fn);
+        }
+      }
+    }
+    const bool ready = mbar_wait(acc_full, 0);
+    if (!ready && lane == 0) atomicExch(error_flag, 23);
+    __syncwarp();
+    cluster_wait();
+    if (ready) {
+      tc_fence_after();
+      const int owner = m / rows_per;
+      const unsigned slot = mapa_shared(base + (unsigned)recv_off + (unsigned)(((rank * rows_per + (m - owner * rows_per)) * row_floats) * 4),
+                                        (unsigned)(owner < S ? owner : 0));
+#pragma unroll 1
+      for (int c = c_lo; c < c_hi; ++c) {
+        unsigned r[32];
+        tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+        if (m < M) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            st_cluster_f4(slot + (unsigned)((c * 32 + j) * 4), __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+      }
+    }
+  }
+  pdl_launch();                     // this CTA's loads are done: the next kernel's CTAs may take the places that free up
+  tc_fence_before();
+  cluster_arrive();                 // every row is where it is finished
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
+  } else if (warp >= 2) {
+    // rows rank * rows_per ... of the tile; a thread takes 8 columns of a row (32 for SwiGLU), consecutive lanes consecutive columns
+    const int idx = (int)threadIdx.x - 64;
+    const float* recv = reinterpret_cast<const float*>(gen + recv_off);
+    if constexpr (EPI == HB_EPI_SWIGLU) {
+      const int chunks = bn >> 5;
+      for (int item0 = 0; item0 < rows_per * chunks; item0 += TG_EPI_WARPS * 32) {
+        const int item = item0 + idx;
+        const int c = item % chunks, rl = item / chunks, m = rank * rows_per + rl;
+        if (rl >= rows_per || m >= M) continue;
+        float inv_rms = first_inv_rms, sq = 0.0f;
+        if (NORM && nm.in_sumsq != nullptr && item0 > 0) {
+          float sum = 0.0f;
+          for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
+          inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+        }
+        float acc[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+        for (int q = 0; q < S; ++q) {           // in the order of the k ranges
+          const float4* src = reinterpret_cast<const float4*>(recv + (size_t)(q * rows_per + rl) * row_floats + c * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = src[j];
+            acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
+          }
+        }
+        unsigned r[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(acc[j]);
+        tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, inv_rms, sq);
+      }
+    } else {
+      const int groups = bn >> 3;                      // a multiple of 8: the 8 lanes of 64 columns sit side by side
+      const int n_end = ((N + 127) / 128) * 128;       // the partial sums of a following norm cover whole 128-column tiles
+      for (int item0 = 0; item0 < rows_per * groups; item0 += TG_EPI_WARPS * 32) {
+        const int item = item0 + idx;
+        const int g8 = item % groups, rl = item / groups, m = rank * rows_per + rl;
+        const bool active = rl < rows_per && m < M;
+        float sq = 0.0f;
+        if (active) {
+          float inv_rms = first_inv_rms;
+          if (NORM && nm.in_sumsq != nullptr && item0 > 0) {
+            float sum = 0.0f;
+            for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
+            inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+          }
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+          for (int q = 0; q < S; ++q) {         // in the order of the k ranges
+            const float4* src = reinterpret_cast<const float4*>(recv + (size_t)(q * rows_per + rl) * row_floats + g8 * 8);
+            const float4 x = src[0], y = src[1];
+            v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+            v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+          }
+          tg_epilogue8<EPI, NORM>(v, m, n0 + g8 * 8, M, N, Cv, ldc, nm, inv_rms, sq);
+        }
+        if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) {
+          // one sum per row and 64 columns
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+          if (active && (g8 & 7) == 0 && n0 + g8 * 8 < n_end) nm.out_sumsq[(size_t)((n0 + g8 * 8) >> 6) * nm.out_stride + m] = sq;
+        }
+      }
+    }
+  }
+}
+
 // The workspace the launcher may use for shared tiles: floats and counters for a grid of `sms` CTAs.
 #define TG_WS_FLOATS_PER_CTA (2 * TG_BM * 256)
 static float* g_tg_ws = nullptr;        // set by hb_gemm_tcgen05_set_workspace
@@ -910,6 +1208,114 @@ static int tg_dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, in
   HB_FAIL(2, "gemm_tcgen05: unknown epilogue %d", epi);
 }
 
+static int g_tg_ksplit = 1;
+static int tg_tile_cols(int M, int N);
+
+// Clusters of `ways` CTAs of this kernel that the GPU holds at once (asked once per size).
+template <int EPI, bool NORM>
+static int tg_ksplit_resident(int ways) {
+  static int resident[9] = {0};
+  if (resident[ways] == 0) {
+    resident[ways] = -1;
+    if (cudaFuncSetAttribute(gemm_tcgen05_ksplit_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, TGK_SMEM_BYTES) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(ways);
+      cfg.blockDim = dim3(TG_THREADS);
+      cfg.dynamicSmemBytes = TGK_SMEM_BYTES;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = ways;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_ksplit_kernel<EPI, NORM>, &cfg) == cudaSuccess && n > 0) resident[ways] = n;
+    }
+    cudaGetLastError();
+  }
+  return resident[ways];
+}
+
+// The tile width and cluster size that put the most CTAs to work in one wave: every cluster resident
+// at once, K ranges of at least four blocks, at least four stages beside the rows a CTA is sent;
+// nothing below three quarters of the SMs.
+template <int EPI, bool NORM>
+static TgKsplit tg_ksplit_plan(int M, int N, int K) {
+  TgKsplit best{0, 0, 0, 0, 0};
+  if (!g_tg_ksplit || M > TG_BM || N < 256 || tg_tile_cols(M, N) != 128) return best;
+  const int num_kb = ceil_div(K, TG_BK), sms = tg_sm_count(), a_rows = M <= 64 ? 64 : TG_BM;
+  int best_ctas = 0;
+  for (int bn = 128; bn <= 256; bn += 64) {
+    const int tiles = ceil_div(N, bn), stage_bytes = (a_rows + bn) * TG_BK * 2;
+    for (int ways = 8; ways >= 2; --ways) {
+      const int rows_per = ceil_div(M, ways);
+      int stages = (TGK_RING_BYTES - ways * rows_per * (bn + 4) * 4) / stage_bytes;
+      if (stages > TGK_MAX_STAGES) stages = TGK_MAX_STAGES;
+      if (ways > num_kb / 4 || tiles * ways > sms || stages < 4 || tg_ksplit_resident<EPI, NORM>(ways) < tiles) continue;
+      const int ctas = (int)((long long)ways * N / bn);       // columns beyond N in the last tile are work without a result
+      if (ctas > best_ctas) {
+        best_ctas = ctas;
+        best = TgKsplit{bn, ways, a_rows, stages, rows_per};
+      }
+      break;
+    }
+  }
+  if (4 * best_ctas < 3 * sms) best.ways = 0;
+  return best;
+}
+
+template <int EPI, bool NORM>
+static int tg_launch_ksplit(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const TgKsplit& plan,
+                            int* err, cudaStream_t s, const TgNorm& nm) {
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, plan.a_rows);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, ldw, plan.bn);
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ceil_div(N, plan.bn) * plan.ways);
+  cfg.blockDim = dim3(TG_THREADS);
+  cfg.dynamicSmemBytes = TGK_SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = plan.ways;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = hb_pdl_enabled() == 1 ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, gemm_tcgen05_ksplit_kernel<EPI, NORM>, ma, mw, C, ldc, M, N, K, plan, err, nm);
+  HB_CHECK_LAUNCH("gemm_tcgen05 (K ranges in a cluster)");
+  return 0;
+}
+
+// 1: the product went that way; 0: it does not apply; negative: an error.
+template <bool NORM>
+static int tg_try_ksplit(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epi, int* err,
+                         cudaStream_t s, const TgNorm& nm) {
+  TgKsplit plan{0, 0, 0, 0, 0};
+  int rc = 0;
+  switch (epi) {
+    case HB_EPI_STORE:
+      if ((plan = tg_ksplit_plan<HB_EPI_STORE, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
+      break;
+    case HB_EPI_STORE_F32:
+      if ((plan = tg_ksplit_plan<HB_EPI_STORE_F32, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE_F32, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
+      break;
+    case HB_EPI_RESIDUAL:
+      if ((plan = tg_ksplit_plan<HB_EPI_RESIDUAL, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_RESIDUAL, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
+      break;
+    case HB_EPI_SWIGLU:
+      if ((plan = tg_ksplit_plan<HB_EPI_SWIGLU, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_SWIGLU, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
+      break;
+  }
+  if (rc) return -rc;
+  return plan.ways > 0 ? 1 : 0;
+}
+
 // Output columns per tile.  Tiles of 256 weight rows feed the tensor cores best; when there are too
 // few of them to keep half the SMs busy (decode batches, short prompts, matrices of few rows),
 // tiles of 128 give twice the tiles to spread and, where tiles are shared, pieces of half the size.
@@ -934,6 +1340,11 @@ static int tg_tile_cols(int M, int N) {
 // 0: every product by single CTAs (for measurements); 1 (default): pairs of CTAs where they apply.
 extern "C" int hb_gemm_tcgen05_set_pairs(int on) {
   g_tg_pairs = on ? 1 : 0;
+  return 0;
+}
+// 0: no product cuts K over a cluster (for measurements); 1 (default): products of at most 128 rows do where it applies.
+extern "C" int hb_gemm_tcgen05_set_ksplit(int on) {
+  g_tg_ksplit = on ? 1 : 0;
   return 0;
 }
 extern "C" long long hb_gemm_tcgen05_workspace_floats(int ctas) { return (long long)ctas * TG_WS_FLOATS_PER_CTA; }
@@ -963,6 +1374,7 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   cudaStream_t s = (cudaStream_t)stream;
   const TgNorm none{};
   if (pairs) return tg_dispatch_pair<false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
+  if (const int went = tg_try_ksplit<false>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
   return BN == 256 ? tg_dispatch<256, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none)
                    : tg_dispatch<128, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
 }
@@ -1035,6 +1447,7 @@ extern "C" int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, 
   const TgNorm nm{in_sumsq, in_parts, in_stride, in_eps, out_w, (bf16*)out_xw, out_ld, out_sumsq, out_stride};
   cudaStream_t s = (cudaStream_t)stream;
   if (pairs) return tg_dispatch_pair<true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
+  if (const int went = tg_try_ksplit<true>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, nm)) return went > 0 ? 0 : -went;
   return BN == 256 ? tg_dispatch<256, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm)
                    : tg_dispatch<128, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
 }

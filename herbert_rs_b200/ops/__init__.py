@@ -207,6 +207,11 @@ def set_gemm_pairs(on: bool) -> None:
     _libmod.load().hb_gemm_tcgen05_set_pairs(1 if on else 0)
 
 
+def set_gemm_ksplit(on: bool) -> None:
+    """Whether products of at most 128 rows cut K over a cluster of CTAs where that applies (default on)."""
+    _libmod.load().hb_gemm_tcgen05_set_ksplit(1 if on else 0)
+
+
 def is_available() -> bool:
     """True when a CUDA device is present (the kernels still have to build and load)."""
     return torch.cuda.is_available()
@@ -551,14 +556,15 @@ def _tcgen05_ok(a, w) -> bool:
 
 def _decode_gemm(a, w):
     """Which kernel multiplies at most 64 activation rows.  Measured (microseconds at 17 / 32 / 64
-    rows; mma.sync kernel, streaming tcgen05 kernel, prefill kernel with tiles of 128 weight rows) at
-    Qwen3-8B shapes: q/k/v 19 / 21 / 31, 22 / 22 / 27, 18 / 18 / 18; o 12 / 12 / 18, 26 / 29 / 41,
-    20 / 21 / 21; gate/up 58 / 65 / 93, 44 / 47 / 55, 38 / 38 / 40; down 28 / 29 / 42, 53 / 59 / 76,
-    34 / 33 / 34; at 32B shapes the prefill kernel wins all four from 32 rows on (down 60 against 103
-    and 97), at 0.6B shapes (at most 6 M elements) the mma.sync kernel wins all four.
+    rows; mma.sync kernel, streaming tcgen05 kernel, prefill kernel) at Qwen3-8B shapes: q/k/v
+    19 / 21 / 31, 23 / 23 / 28, 14 / 15 / 16; o 12 / 12 / 18, 27 / 30 / 42, 13 / 14 / 14; gate/up
+    58 / 65 / 93, 46 / 49 / 57, 41 / 41 / 42; down 28 / 29 / 42, 53 / 59 / 76, 26 / 26 / 26; at 32B shapes
+    the prefill kernel wins all four from 32 rows on, at 0.6B shapes (at most 6 M elements) the
+    mma.sync kernel wins all four.
     Up to 16 rows the mma.sync kernel streams the weights at the memory's rate; beyond that every CTA
-    of 16 weight rows reads the whole activation matrix again, and the prefill kernel wins wherever
-    the matrix is large enough to pay for its start and end.  The streaming kernel keeps the head."""
+    of 16 weight rows reads the whole activation matrix again, and the prefill kernel (K cut over a
+    cluster of CTAs where the matrix has few tiles) wins wherever the matrix is large enough to pay
+    for its start and end.  The streaming kernel keeps the head."""
     if options.decode_gemm == "stream":
         return gemm_stream
     M, N, K = a.shape[0], w.shape[0], a.shape[1]
@@ -566,7 +572,7 @@ def _decode_gemm(a, w):
         elements = N * K
         if N >= 65536:
             return gemm_stream
-        if _tcgen05_ok(a, w) and elements >= 20 * 1024 * 1024 and (M > 32 or N >= 6144 or elements >= 64 * 1024 * 1024):
+        if _tcgen05_ok(a, w) and elements >= 16 * 1024 * 1024 and (M > 32 or N >= 6144 or elements >= 48 * 1024 * 1024):
             return gemm_tcgen05
     return gemm_skinny
 

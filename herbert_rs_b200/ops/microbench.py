@@ -189,6 +189,7 @@ def main(argv=None) -> None:
     ap.add_argument("--head", action="store_true", help="decode-gemm / prefill-gemm: also the output head (vocab x hidden)")
     ap.add_argument("--spread", type=float, default=3.0, help="standard deviation of the logits of `sampling`")
     ap.add_argument("--no-pairs", action="store_true", help="prefill-gemm: single CTAs instead of pairs (cta_group::2)")
+    ap.add_argument("--no-ksplit", action="store_true", help="products of at most 128 rows: no K ranges over a cluster")
     ap.add_argument("--pdl", type=int, default=0, help="programmatic dependent launch: 0 off, 1 every kernel, 2 the launches that ask for it")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
@@ -197,6 +198,8 @@ def main(argv=None) -> None:
         ops.set_pdl(a.pdl)
     if a.no_pairs:
         ops.set_gemm_pairs(False)
+    if a.no_ksplit:
+        ops.set_gemm_ksplit(False)
     {"decode-gemm": decode_gemm, "prefill-gemm": prefill_gemm, "decode-attention": decode_attention,
      "prefill-attention": prefill_attention, "sampling": sampling, "step": step}[a.what](a)
 
