@@ -984,7 +984,13 @@ gemm_tcgen05_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     const int c_lo = warp < 6 ? 0 : first, c_hi = warp < 6 ? first : chunks;
     // While the tensor cores work: what the first piece of a row this thread finishes will need from
     // global memory (1 / rms of the row; the residual and the next norm's weights into L1).
-    {
+    if (S == 1) {
+      if (NORM && nm.in_sumsq != nullptr && m < M) {
+        float sum = 0.0f;
+        for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
+        first_inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+      }
+    } else {
       const int per_row = EPI == HB_EPI_SWIGLU ? chunks : bn >> 3, cols = EPI == HB_EPI_SWIGLU ? 32 : 8;
       const int item = (int)threadIdx.x - 64, frl = item / per_row, fm = rank * rows_per + frl;
       if (frl < rows_per && fm < M) {
@@ -1004,7 +1010,17 @@ gemm_tcgen05_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     if (!ready && lane == 0) atomicExch(error_flag, 23);
     __syncwarp();
     cluster_wait();
-    if (ready) {
+    if (ready && S == 1) {
+      // the tile is whole: straight from tensor memory (store and SwiGLU epilogues only: the launcher sees to it)
+      tc_fence_after();
+      float sq = 0.0f;
+#pragma unroll 1
+      for (int c = c_lo; c < c_hi; ++c) {
+        unsigned r[32];
+        tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+        tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, first_inv_rms, sq);
+      }
+    } else if (ready) {
       tc_fence_after();
       const int owner = m / rows_per;
       const unsigned slot = mapa_shared(base + (unsigned)recv_off + (unsigned)(((rank * rows_per + (m - owner * rows_per)) * row_floats) * 4),
@@ -1028,7 +1044,7 @@ gemm_tcgen05_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
-  } else if (warp >= 2) {
+  } else if (warp >= 2 && S > 1) {
     // rows rank * rows_per ... of the tile; a thread takes 8 columns of a row (32 for SwiGLU), consecutive lanes consecutive columns
     const int idx = (int)threadIdx.x - 64;
     const float* recv = reinterpret_cast<const float*>(gen + recv_off);
@@ -1252,7 +1268,7 @@ static TgKsplit tg_ksplit_plan(int M, int N, int K) {
       const int rows_per = ceil_div(M, ways);
       int stages = (TGK_RING_BYTES - ways * rows_per * (bn + 4) * 4) / stage_bytes;
       if (stages > TGK_MAX_STAGES) stages = TGK_MAX_STAGES;
-      if (ways > num_kb / 4 || tiles * ways > sms || stages < 4 || tg_ksplit_resident<EPI, NORM>(ways) < tiles) continue;
+      if (ways > num_kb / 4 || tiles * ways > sms || stages < 3 || tg_ksplit_resident<EPI, NORM>(ways) < tiles) continue;
       const int ctas = (int)((long long)ways * N / bn);       // columns beyond N in the last tile are work without a result
       if (ctas > best_ctas) {
         best_ctas = ctas;
@@ -1263,6 +1279,22 @@ static TgKsplit tg_ksplit_plan(int M, int N, int K) {
   }
   if (4 * best_ctas < 3 * sms) best.ways = 0;
   return best;
+}
+
+// A matrix wide enough for a tile per SM without cutting K: the narrowest tiles (a multiple of 32
+// columns) that still make one wave, every stage of the ring for loads.  Store and SwiGLU epilogues.
+template <int EPI, bool NORM>
+static TgKsplit tg_whole_plan(int M, int N, int K) {
+  TgKsplit none{0, 0, 0, 0, 0};
+  if (!g_tg_ksplit || EPI == HB_EPI_RESIDUAL || M > TG_BM) return none;
+  const int sms = tg_sm_count(), a_rows = M <= 64 ? 64 : TG_BM;
+  const int bn = ceil_div(ceil_div(N, sms), 32) * 32;
+  if (bn < 64 || bn > 256) return none;
+  const int tiles = ceil_div(N, bn);
+  int stages = TGK_RING_BYTES / ((a_rows + bn) * TG_BK * 2);
+  if (stages > TGK_MAX_STAGES) stages = TGK_MAX_STAGES;
+  if (4 * tiles < 3 * sms || stages < 4 || ceil_div(K, TG_BK) < 8 || tg_ksplit_resident<EPI, NORM>(1) < tiles) return none;
+  return TgKsplit{bn, 1, a_rows, stages, M};
 }
 
 template <int EPI, bool NORM>
@@ -1300,16 +1332,16 @@ static int tg_try_ksplit(const void* A, int lda, const void* W, int ldw, void* C
   int rc = 0;
   switch (epi) {
     case HB_EPI_STORE:
-      if ((plan = tg_ksplit_plan<HB_EPI_STORE, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
+      if ((plan = tg_ksplit_plan<HB_EPI_STORE, NORM>(M, N, K)).ways > 0 || (plan = tg_whole_plan<HB_EPI_STORE, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
       break;
     case HB_EPI_STORE_F32:
-      if ((plan = tg_ksplit_plan<HB_EPI_STORE_F32, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE_F32, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
+      if ((plan = tg_ksplit_plan<HB_EPI_STORE_F32, NORM>(M, N, K)).ways > 0 || (plan = tg_whole_plan<HB_EPI_STORE_F32, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE_F32, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
       break;
     case HB_EPI_RESIDUAL:
       if ((plan = tg_ksplit_plan<HB_EPI_RESIDUAL, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_RESIDUAL, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
       break;
     case HB_EPI_SWIGLU:
-      if ((plan = tg_ksplit_plan<HB_EPI_SWIGLU, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_SWIGLU, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
+      if ((plan = tg_ksplit_plan<HB_EPI_SWIGLU, NORM>(M, N, K)).ways > 0 || (plan = tg_whole_plan<HB_EPI_SWIGLU, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_SWIGLU, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
       break;
   }
   if (rc) return -rc;
