@@ -127,6 +127,9 @@ class Engine:
         together.  One does not fit if it would pass the length limit, or if the pages it needs are
         no longer free after the ones before it took theirs.  Nothing is reserved."""
         free = self.cache.free_pages()
+        lengths, limit = self.cache.lengths, self.cache.max_seq_len
+        if free >= len(pairs) and all(n == 1 and lengths[s] < limit for s, n in pairs):
+            return [True] * len(pairs)          # one position each takes at most one page each
         out = []
         for slot, n in pairs:
             need = self.cache.pages_needed(slot, n)

@@ -177,7 +177,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
             stats.batches += 1
             # all prompts in one step, or in pieces whose last ones meet in one step
             t0 = time.perf_counter()
-            uni = [uniform_for(seed, i, 0) for i in batch_ids]
+            uni = None if sampling.greedy else [uniform_for(seed, i, 0) for i in batch_ids]     # argmax draws nothing
             steps = plan_prefill_pieces([len(prompts[i]) for i in batch_ids], options.prefill_chunk_size)
             try:
                 for pieces in steps[:-1]:
@@ -216,7 +216,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
                     active = [i for i, good in zip(active, ok) if good]
                     if not active:
                         break
-                uni = [uniform_for(seed, i, len(out[i])) for i in active]
+                uni = None if sampling.greedy else [uniform_for(seed, i, len(out[i])) for i in active]
                 try:
                     toks = engine.step_and_choose([(slots[i], [out[i][-1]]) for i in active], sampling, uni)
                 except CacheError:

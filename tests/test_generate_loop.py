@@ -55,7 +55,7 @@ class FakeEngine:
         for s, t in entries:
             self.lengths[s] += len(t)
         self.steps.append([(s, list(t)) for s, t in entries])
-        self.uniforms.append(list(uniforms))
+        self.uniforms.append(None if uniforms is None else list(uniforms))      # None: greedy, nothing is drawn
         return [(t[-1] + 1) % 100 for _, t in entries]
 
 
@@ -67,6 +67,7 @@ def test_unequal_prompts_then_one_token_each():
     assert e.steps[0] == [(0, [1, 2, 3]), (1, [10]), (2, [20, 21])]      # all prompts in one step
     assert e.steps[1] == [(0, [4]), (1, [11]), (2, [22])]                # then one token each
     assert len(e.steps) == 3 and e.free == [0, 1, 2, 3]
+    assert e.uniforms == [None] * 3                                      # greedy draws nothing
     assert r.stats.prompt_tokens == 6 and r.stats.generated_tokens == 9 and r.stats.decode_steps == 2
 
 
