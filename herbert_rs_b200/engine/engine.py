@@ -45,7 +45,6 @@ class Engine:
         self._host = torch.empty(1 << 14, dtype=torch.int32).pin_memory()
         self._dev = torch.empty(1 << 14, dtype=torch.int32, device=self.rt.device)
         self._tok_out = torch.empty(max(num_slots, 1), dtype=torch.int32, device=self.rt.device)
-        self._tok_host = torch.empty(max(num_slots, 1), dtype=torch.int32).pin_memory()
         self._copied = torch.cuda.Event()
         self._copied.record()
         # Decode steps (one token per sequence) are launch-bound: each shape of such a step is
@@ -60,6 +59,10 @@ class Engine:
         self._host_owner = None        # the batch whose arrays the pinned buffer holds
         self.fast_decode_steps = 0
         self.kernels_per_graph: dict = {}   # batch size -> kernels in its captured decode step
+        self._chosen_on_device = False   # the step before left its chosen ids in _tok_out
+        self._tok_ring = [(torch.empty(max(num_slots, 1), dtype=torch.int32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+        self._tickets = 0
+        self._open: dict = {}
         self.launches_last = 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
@@ -205,7 +208,9 @@ class Engine:
     def _prepare_decode_again(self, entries, uniforms: Optional[np.ndarray]) -> Optional[StepBatch]:
         """The next one-token step of the sequences of the previous step: instead of building the
         step buffer anew, bump positions and lengths in place, write the new tokens (and page rows,
-        when a sequence enters a new page) and upload.  None if this is not such a step."""
+        when a sequence enters a new page) and upload.  None if this is not such a step.
+        Entries whose tokens are None take the tokens that the previous step chose, which are
+        still on the device: nothing of that step has to be known on the host."""
         st = self._decode_again
         if st is None or self._host_owner is not st[1] or st[1]._positions is not None:
             return None
@@ -213,22 +218,28 @@ class Engine:
         if len(entries) != len(slots):
             return None
         lengths = self.cache.lengths
+        from_device = entries[0][1] is None
         for i, (s, t) in enumerate(entries):
-            if s != slots[i] or len(t) != 1 or lengths[s] != lens_after[i] or not self.cache.slots.is_held(s):
+            if s != slots[i] or (t is None) != from_device or (t is not None and len(t) != 1) or lengths[s] != lens_after[i] \
+                    or not self.cache.slots.is_held(s):
                 return None
+        if from_device and not self._chosen_on_device:
+            return None
         ps = self.rt.page_size
         if -(-(max(lens_after) + 1) // ps) > batch.pages_width:
             return None
         V = self.vocab_size
-        toks = [t[0] for _, t in entries]
-        for s, x in zip(slots, toks):
-            if not (isinstance(x, (int, np.integer)) and 0 <= x < V):
-                raise RequestError(f"slot {s}: token id {x!r} is outside the vocabulary of {V}")
+        toks = None if from_device else [t[0] for _, t in entries]
+        if toks is not None:
+            for s, x in zip(slots, toks):
+                if not (isinstance(x, (int, np.integer)) and 0 <= x < V):
+                    raise RequestError(f"slot {s}: token id {x!r} is outside the vocabulary of {V}")
         new_page = any(n % ps == 0 for n in lens_after)
         self.cache.reserve([(s, 1) for s in slots])
         B, o, host = len(slots), batch.layout.offsets, self._host.numpy()
         self._copied.synchronize()
-        host[o["token_ids"]:o["token_ids"] + B] = toks
+        if toks is not None:
+            host[o["token_ids"]:o["token_ids"] + B] = toks
         for name in ("seq_pos0", "seq_len"):
             host[o[name]:o[name] + B] += 1
         row = (B + 3) // 4 * 4
@@ -241,9 +252,12 @@ class Engine:
                 rows = self.cache.page_rows(g, list(slots), batch.pages_width)
                 host[o[f"pages{g}"]:o[f"pages{g}"] + B * batch.pages_width] = rows.reshape(-1)
         n = batch.layout.total
-        self._dev[:n].copy_(self._host[:n], non_blocking=True)
+        first = o["tok_seq"] if from_device else 0          # the ids are the buffer's first array
+        self._dev[first:n].copy_(self._host[first:n], non_blocking=True)
         self._copied.record()
-        self.h2d_bytes_last = n * 4
+        if from_device:
+            self._dev[o["token_ids"]:o["token_ids"] + B].copy_(self._tok_out[:B], non_blocking=True)
+        self.h2d_bytes_last = (n - first) * 4
         self.fast_decode_steps += 1
         return batch
 
@@ -300,16 +314,30 @@ class Engine:
         batch = self._prepare(entries, want, positions=positions)
         logits = self._forward(batch)
         self._finish(batch)
+        self._chosen_on_device = False
         return logits
 
     def step_and_choose(self, entries: Sequence[Tuple[int, Sequence[int]]], params: SamplingParams,
                         uniforms: Optional[Sequence[float]] = None) -> List[int]:
         """One step with the logits at each sequence's last token, then one token id per sequence
         chosen on the device; only the ids travel back to the host."""
+        return self.chosen(self.launch_and_choose(entries, params, uniforms))
+
+    def launch_and_choose(self, entries: Sequence[Tuple[int, Optional[Sequence[int]]]], params: SamplingParams,
+                          uniforms: Optional[Sequence[float]] = None) -> int:
+        """`step_and_choose` without the wait: the step is queued and a ticket for its token ids
+        returned (`chosen`).  Entries (slot, None), for all sequences or none, continue the step
+        before with the ids it chose, taken on the device: the host may queue a step before it has
+        read the one before (`can_continue_on_device` says whether).  At most two tickets are open."""
         B = len(entries)
+        if len(self._open) >= 2:
+            raise RequestError("two queued steps are still unread: read one (`chosen`) before queueing another")
         u = None if uniforms is None else np.asarray(uniforms, dtype=np.float32)
+        from_device = B > 0 and entries[0][1] is None
         batch = self._prepare_decode_again(entries, u) if self.use_graphs else None
         if batch is None:
+            if from_device:
+                raise RequestError("a step can take its tokens from the device only right after a step of the same sequences that chose them")
             batch = self._prepare(entries, "last", u)
         logits = self._forward(batch)
         self._finish(batch)
@@ -317,10 +345,31 @@ class Engine:
             self._decode_again = (tuple(batch.slots), batch, [self.cache.lengths[s] for s in batch.slots])
         out = self._tok_out[:B]
         device_choose(logits, params, batch.uniforms, out)
-        self._tok_host[:B].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        self._chosen_on_device = True
+        ticket = self._tickets
+        self._tickets += 1
+        host, event = self._tok_ring[ticket % 2]
+        host[:B].copy_(out, non_blocking=True)
+        event.record()
+        self._open[ticket] = B
         self.d2h_bytes_last = B * 4
-        return self._tok_host[:B].tolist()
+        return ticket
+
+    def chosen(self, ticket: int) -> List[int]:
+        """The token ids of a queued step (waits for it)."""
+        B = self._open.pop(ticket)
+        host, event = self._tok_ring[ticket % 2]
+        event.synchronize()
+        return host[:B].tolist()
+
+    def can_continue_on_device(self, slots: Sequence[int]) -> bool:
+        """Whether `launch_and_choose([(slot, None), ...])` can follow now: the step before was a
+        recorded one-token-or-prompt step of exactly these sequences whose ids were chosen on the device."""
+        st = self._decode_again
+        return bool(self.use_graphs and st is not None and self._chosen_on_device and self._host_owner is st[1]
+                    and tuple(slots) == st[0] and len(self._open) < 2 and st[1]._positions is None
+                    and all(self.cache.lengths[s] == n for s, n in zip(st[0], st[2]))
+                    and -(-(max(st[2]) + 1) // self.rt.page_size) <= st[1].pages_width)
 
 
 def _dtype(d) -> torch.dtype:

@@ -113,7 +113,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
     `engine` needs: alloc_slot(), free_slot(slot), step_and_choose(entries, params, uniforms) -> ids,
     step(entries, None) when prompts enter in pieces, and optionally `default_stop_token_ids`,
     `max_slots` and `admit(pairs)` (for (slot, new positions) pairs in order of priority: which of
-    them fit into the next step together).  With `admit`, a batch takes only the prompts that fit
+    them fit into the next step together).  An engine that also has `launch_and_choose`, `chosen`
+    and `can_continue_on_device` is kept one step ahead: the next step is queued, with its tokens
+    taken on the device, before the host has read the one before; what the host does with a
+    step's ids (stop checks, bookkeeping) then runs beside the GPU, not between its steps.  With `admit`, a batch takes only the prompts that fit
     (the others wait for the next batch), and a sequence that runs out of room ends alone.
     finish_reason is one of: "stop_token", "max_tokens", "repetition", "capacity".
     """
@@ -157,6 +160,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
     while pending:
         # the next batch: requests in their order, as many as have slots and room for their prompts
         batch_ids, slots = [], {}
+        flying = None
         try:
             cand = pending[:max_batch]
             for i in cand:
@@ -203,29 +207,64 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
             stats.first_tokens += len(batch_ids)
             # then one token each, for the sequences that still run
             t0 = time.perf_counter()
-            while active:
-                # only the sequences that have no room left end with "capacity" (a length limit reached,
-                # or no page left for the ones that need a new one); they give their pages back at once,
-                # and the others go on
-                ok = fits([(slots[i], 1) for i in active])
-                if not all(ok):
-                    for i, good in zip(active, ok):
-                        if not good:
+            ahead = all(hasattr(engine, a) for a in ("launch_and_choose", "chosen", "can_continue_on_device"))
+            flying = None          # (ticket, requests) of a queued step whose ids the host has not read yet
+            while active or flying is not None:
+                if flying is None:
+                    # only the sequences that have no room left end with "capacity" (a length limit reached,
+                    # or no page left for the ones that need a new one); they give their pages back at once,
+                    # and the others go on
+                    ok = fits([(slots[i], 1) for i in active])
+                    if not all(ok):
+                        for i, good in zip(active, ok):
+                            if not good:
+                                reasons[i] = "capacity"
+                                engine.free_slot(slots.pop(i))
+                        active = [i for i, good in zip(active, ok) if good]
+                        if not active:
+                            break
+                    uni = None if sampling.greedy else [uniform_for(seed, i, len(out[i])) for i in active]
+                    entries = [(slots[i], [out[i][-1]]) for i in active]
+                    try:
+                        if ahead:
+                            flying = (engine.launch_and_choose(entries, sampling, uni), list(active))
+                        else:
+                            toks = engine.step_and_choose(entries, sampling, uni)
+                    except CacheError:
+                        for i in active:
                             reasons[i] = "capacity"
-                            engine.free_slot(slots.pop(i))
-                    active = [i for i, good in zip(active, ok) if good]
-                    if not active:
                         break
-                uni = None if sampling.greedy else [uniform_for(seed, i, len(out[i])) for i in active]
-                try:
-                    toks = engine.step_and_choose([(slots[i], [out[i][-1]]) for i in active], sampling, uni)
-                except CacheError:
-                    for i in active:
-                        reasons[i] = "capacity"
-                    break
-                stats.decode_steps += 1
+                    stats.decode_steps += 1
+                    if not ahead:
+                        still = []
+                        for i, tok in zip(active, toks):
+                            out[i].append(int(tok))
+                            r = finished(i, int(tok))
+                            if r is None:
+                                still.append(i)
+                            else:
+                                reasons[i] = r
+                        active = still
+                        continue
+                # A step is queued.  Unless one of its sequences is sure to end with it (max_tokens) or has no
+                # room for another position, the step after it is queued before its ids are read: that step
+                # takes them on the device.  A sequence that turns out to have ended (a stop token, a
+                # repetition) has then run one token too far; that token is dropped.
+                ticket, ids = flying
+                nxt = None
+                if ids == active and all(len(out[i]) + 1 < options.max_tokens for i in ids) \
+                        and engine.can_continue_on_device([slots[i] for i in ids]) and all(fits([(slots[i], 1) for i in ids])):
+                    uni = None if sampling.greedy else [uniform_for(seed, i, len(out[i]) + 1) for i in ids]
+                    try:
+                        nxt = (engine.launch_and_choose([(slots[i], None) for i in ids], sampling, uni), ids)
+                        stats.decode_steps += 1
+                    except CacheError:
+                        nxt = None
+                toks = engine.chosen(ticket)
                 still = []
-                for i, tok in zip(active, toks):
+                for i, tok in zip(ids, toks):
+                    if i not in active:
+                        continue                       # ended a step ago: this token is one too many
                     out[i].append(int(tok))
                     r = finished(i, int(tok))
                     if r is None:
@@ -233,8 +272,11 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
                     else:
                         reasons[i] = r
                 active = still
+                flying = nxt
             stats.decode_seconds += time.perf_counter() - t0
         finally:
+            if flying is not None:
+                engine.chosen(flying[0])        # an error above left a queued step unread
             for s in slots.values():
                 engine.free_slot(s)
         if hasattr(engine, "check_kernels"):

@@ -218,3 +218,71 @@ def test_generation_with_a_prefill_chunk_size_steps_the_pieces_then_decodes():
     whole = generate(FakeEngine(), [[1, 2, 3, 4, 5, 6, 7], [10], [20, 21, 22]],
                      hb.GenerationOptions(max_tokens=2), hb.SamplingParams(temperature=0.0))
     assert whole.tokens == r.tokens
+
+
+class AheadEngine(FakeEngine):
+    """The stand-in with the calls that let the loop queue a step before it has read the one before:
+    tokens a step chose stay "on the device" (`last`), and a step of (slot, None) entries takes them."""
+
+    def __init__(self, *a, stop_after=None, **kw):
+        super().__init__(*a, **kw)
+        self.open, self.tickets, self.last, self.from_device, self.unread_peak = {}, 0, None, 0, 0
+
+    def launch_and_choose(self, entries, params, uniforms):
+        assert len(self.open) < 2
+        if entries[0][1] is None:
+            assert self.last is not None and [s for s, _ in entries] == [s for s, _ in self.last]
+            entries = [(s, [t]) for (s, _), (_, t) in zip(entries, self.last)]
+            self.from_device += 1
+        toks = FakeEngine.step_and_choose(self, entries, params, uniforms)
+        self.last = [(s, t) for (s, _), t in zip(entries, toks)]
+        self.open[self.tickets] = toks
+        self.unread_peak = max(self.unread_peak, len(self.open))
+        self.tickets += 1
+        return self.tickets - 1
+
+    def chosen(self, ticket):
+        return self.open.pop(ticket)
+
+    def can_continue_on_device(self, slots):
+        return self.last is not None and list(slots) == [s for s, _ in self.last] and len(self.open) < 2
+
+    def step_and_choose(self, entries, params, uniforms):
+        self.last = None          # the prompts' step: its ids are read at once
+        return FakeEngine.step_and_choose(self, entries, params, uniforms)
+
+
+@pytest.mark.parametrize("stops,max_tokens", [((), 7), ((30,), 40), ((13, 30), 40), ((), 1), ((), 2)])
+def test_a_loop_one_step_ahead_decides_as_the_plain_one(stops, max_tokens):
+    prompts = [[1, 2, 3], [10], [20, 21], [27]]
+    opt = hb.GenerationOptions(max_tokens=max_tokens, stop_token_ids=list(stops))
+    plain, ahead = FakeEngine(), AheadEngine()
+    a = generate(plain, prompts, opt, hb.SamplingParams(temperature=0.0))
+    b = generate(ahead, prompts, opt, hb.SamplingParams(temperature=0.0))
+    assert a.tokens == b.tokens and a.finish_reasons == b.finish_reasons
+    assert not ahead.open and sorted(ahead.free) == sorted(plain.free)
+    if max_tokens > 3:
+        assert ahead.from_device > 0 and ahead.unread_peak == 2            # it did run ahead
+    if not stops:
+        assert len(ahead.steps) == len(plain.steps)                          # an end by max_tokens is foreseen: no step too many
+    else:
+        assert len(plain.steps) <= len(ahead.steps) <= len(plain.steps) + len(stops)   # one dropped token per unforeseen end
+
+
+def test_a_loop_one_step_ahead_draws_the_same_uniforms():
+    p = hb.SamplingParams(temperature=0.8, seed=5)
+    plain, ahead = FakeEngine(), AheadEngine()
+    generate(plain, [[1], [2], [3]], hb.GenerationOptions(max_tokens=6), p)
+    generate(ahead, [[1], [2], [3]], hb.GenerationOptions(max_tokens=6), p)
+    assert plain.uniforms == ahead.uniforms
+
+
+@pytest.mark.parametrize("kw", [dict(capacity=8), dict(capacity=4), dict(pool=14), dict(capacity=8, admits=False)])
+def test_a_loop_one_step_ahead_runs_out_of_room_as_the_plain_one(kw):
+    prompts = [[1, 2, 3, 4, 5], [10], [20, 21]]
+    opt = hb.GenerationOptions(max_tokens=12, stop_token_ids=[])
+    plain, ahead = FakeEngine(**kw), AheadEngine(**kw)
+    a = generate(plain, prompts, opt, hb.SamplingParams(temperature=0.0))
+    b = generate(ahead, prompts, opt, hb.SamplingParams(temperature=0.0))
+    assert a.tokens == b.tokens and a.finish_reasons == b.finish_reasons and "capacity" in a.finish_reasons
+    assert not ahead.open and ahead.free == plain.free

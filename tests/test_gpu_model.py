@@ -428,3 +428,43 @@ def test_decode_steps_launched_ahead_of_their_predecessor_give_the_same_bits(mod
     finally:
         ops.options.pdl_graph, ops.options.pdl_eager = saved
         ops.set_pdl(0)
+
+
+class _OneStepAtATime:
+    """The engine without the calls that let `generate` run a step ahead: the plain loop."""
+
+    def __init__(self, engine):
+        self._e = engine
+
+    def __getattr__(self, name):
+        if name in ("launch_and_choose", "chosen", "can_continue_on_device"):
+            raise AttributeError(name)
+        return getattr(self._e, name)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16")])
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_generation_one_step_ahead_gives_the_plain_loops_tokens(model_dirs, name, dtype, temperature):
+    """`generate` queues a decode step before it has read the ids of the one before (those stay on
+    the device).  Same tokens, same reasons, also where a stop token ends a sequence one step after
+    the next step was queued, where a new page is entered, and over two batches that share slots."""
+    rng = np.random.default_rng(61)
+    cfg = json.load(open(os.path.join(model_dirs[name], "config.json")))
+    prompts = [random_ids(rng, cfg["vocab_size"], n) for n in (60, 3, 130, 17, 64)]
+    sampling = hb.SamplingParams(temperature=temperature, top_k=20, seed=9)
+    free_run = hb.GenerationOptions(max_tokens=40, ignore_eos=True, max_batch=3)
+    eng = engine_for(model_dirs[name], dtype, max_tokens=4096)
+    probe = hb.generate(_OneStepAtATime(eng), prompts, free_run, sampling)
+    # stop tokens taken from what the model really emits, so that sequences end early and unforeseen
+    stops = sorted({probe.tokens[0][7], probe.tokens[2][20], probe.tokens[4][1]})
+    opt = hb.GenerationOptions(max_tokens=40, stop_token_ids=stops, max_batch=3)
+    plain_run = hb.generate(_OneStepAtATime(eng), prompts, opt, sampling)
+    before = eng.fast_decode_steps
+    ahead_run = hb.generate(eng, prompts, opt, sampling)
+    assert ahead_run.tokens == plain_run.tokens and ahead_run.finish_reasons == plain_run.finish_reasons
+    assert "stop_token" in plain_run.finish_reasons and eng.fast_decode_steps > before
+    assert not eng._open
+    assert hb.generate(eng, prompts, free_run, sampling).tokens == probe.tokens
+    eng.cache.check()
+    assert eng.cache.slots.free_count == eng.cache.num_slots
