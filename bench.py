@@ -179,9 +179,16 @@ def fp32_check(cfg: dict, bf16_engine, n_tokens: int = 64) -> dict:
     del eng
     torch.cuda.empty_cache()
     top2 = ref.topk(2, dim=-1).values
+    gap = top2[:, 0] - top2[:, 1]
+    differ = low.argmax(-1) != ref.argmax(-1)
+    # where the two engines choose another token, how far apart the 32-bit engine's two best logits were there,
+    # and how much lower it rates the bfloat16 engine's choice: both small against max_abs_err if the choice was a near-tie
+    lost = (ref.max(-1).values - ref.gather(1, low.argmax(-1, keepdim=True))[:, 0])
     return {"tokens": n_tokens, "layers": cfg["num_hidden_layers"], "max_abs_err": round(float((low - ref).abs().max()), 5),
-            "logit_std": round(float(ref.std()), 4), "argmax_agree": round(float((low.argmax(-1) == ref.argmax(-1)).double().mean()), 4),
-            "median_top2_gap": round(float((top2[:, 0] - top2[:, 1]).median()), 5)}
+            "logit_std": round(float(ref.std()), 4), "argmax_agree": round(float((~differ).double().mean()), 4),
+            "median_top2_gap": round(float(gap.median()), 5),
+            "largest_gap_where_they_differ": round(float(gap[differ].max()) if bool(differ.any()) else 0.0, 5),
+            "largest_logit_given_up": round(float(lost.max()), 5)}
 
 
 def main() -> int:
