@@ -1114,6 +1114,201 @@ gemm_tcgen05_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// 129 to about 512 rows against a matrix with few tiles: too few 256 x 256 tiles for the pairs of CTAs,
+// and what an SM takes in from L2 per k block bounds every smaller tile.  Here a cluster of 2 S CTAs
+// owns a 256 x 256 tile: S pairs, each pair a range of K (tcgen05 with cta_group::2 inside a pair, as
+// in the pair kernel above).  When all of them are through (first cluster barrier: every ring is
+// free) each CTA sends the rows of its accumulator, as floats, into the ring of the CTA that
+// finishes them (the CTAs with the same half of the tile's rows, rows dealt in S blocks); after the
+// second cluster barrier every CTA adds the S partial rows it holds in k order and runs the epilogue,
+// 8 columns per thread.  No workspace, no counters, no multicast loads.
+#define TGQ_STAGES 6
+#define TGQ_STAGE_BYTES (2 * TG_BM * TG_BK * 2)
+#define TGQ_SMEM_BYTES (TGQ_STAGES * TGQ_STAGE_BYTES + 1024 + 256)
+#define TGQ_BN 256
+#define TGQ_ROW_FLOATS (TGQ_BN + 4)
+
+__device__ __forceinline__ void tc_commit_pair_of(unsigned bar, unsigned leader) {      // arrives at this barrier in both CTAs of the pair that starts at rank `leader`
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((unsigned short)(3u << leader))
+               : "memory");
+}
+
+template <int EPI, bool NORM>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+gemm_tcgen05_pair_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
+                                int ldc, int M, int N, int K, int rows_per, int part_cols, int* error_flag, TgNorm nm) {
+  static_assert(EPI != HB_EPI_SWIGLU, "store and residual epilogues only");
+  static_assert((TG_BM + 8) * TGQ_ROW_FLOATS * 4 <= TGQ_STAGES * TGQ_STAGE_BYTES, "the rows a CTA is sent must fit into its ring");
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
+  const unsigned bars = base + TGQ_STAGES * TGQ_STAGE_BYTES;       // full[STAGES], empty[STAGES], acc_full; then the tensor-memory slot
+  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + TGQ_STAGES * TGQ_STAGE_BYTES + (2 * TGQ_STAGES + 1) * 8);
+  auto full_bar = [&](int st) { return bars + st * 8; };
+  auto empty_bar = [&](int st) { return bars + (TGQ_STAGES + st) * 8; };
+  const unsigned acc_full = bars + 2 * TGQ_STAGES * 8;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_ctarank(), leader = rank & ~1u, half = rank & 1u;
+  const int S = (int)(cluster_nctarank() >> 1), pair = (int)(rank >> 1);
+  const int tiles_m = (M + 2 * TG_BM - 1) / (2 * TG_BM);
+  const int tile = (int)cluster_id_x();
+  const int m0 = (tile % tiles_m) * 2 * TG_BM + (int)half * TG_BM;      // this CTA's 128 rows of the tile
+  const int n0 = (tile / tiles_m) * TGQ_BN;
+  const int num_kb = (K + TG_BK - 1) / TG_BK;
+  const int kb0 = (int)(((long long)num_kb * pair) / S), kb1 = (int)(((long long)num_kb * (pair + 1)) / S);
+
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < TGQ_STAGES; ++st) {
+      mbar_init(full_bar(st), 1);     // the pair's first CTA arms it with both CTAs' bytes
+      mbar_init(empty_bar(st), 1);
+    }
+    mbar_init(acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TGQ_BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();               // every CTA's barriers are initialised before its peer signals them
+  tc_fence_after();
+  pdl_wait();
+  const unsigned tmem_acc = *tmem_slot;
+  const bool tmem_ok = tmem_acc == 0u;        // the pair's two CTAs must hold their accumulators at one address: the first allocation of an empty SM
+  if (!tmem_ok && threadIdx.x == 0) atomicExch(error_flag, 35);
+  float first_inv_rms = 1.0f;
+  bool ready = false;
+
+  if (!tmem_ok) {
+    // nothing is issued; the barriers below are still passed
+  } else if (warp == 0) {
+    if (lane == 0) {
+      const int w_row0 = n0 + (int)half * TG_BM;                     // this CTA's half of the tile's rows of W
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0, st = it % TGQ_STAGES;
+        if (it >= TGQ_STAGES && !mbar_wait_cluster(empty_bar(st), ((it / TGQ_STAGES) - 1) & 1)) {
+          atomicExch(error_flag, 31);
+          break;
+        }
+        const unsigned full0 = mapa_shared(full_bar(st), leader);
+        if (half == 0) mbar_expect_tx(full_bar(st), 2 * TGQ_STAGE_BYTES);
+        const unsigned a_dst = base + st * TGQ_STAGE_BYTES;
+        tma_load_2d_pair(a_dst, &map_a, kb * TG_BK, m0, full0);
+        tma_load_2d_pair(a_dst + TG_BM * TG_BK * 2, &map_w, kb * TG_BK, w_row0, full0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && half == 0) {
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TGQ_BN >> 3) << 17) | ((unsigned)((2 * TG_BM) >> 4) << 24);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0, st = it % TGQ_STAGES;
+        if (!mbar_wait_cluster(full_bar(st), (it / TGQ_STAGES) & 1)) {
+          atomicExch(error_flag, 32);
+          break;
+        }
+        tc_fence_after();
+        const unsigned a_addr = base + st * TGQ_STAGE_BYTES;
+        const unsigned long long da = umma_desc_sw128(a_addr), dw = umma_desc_sw128(a_addr + TG_BM * TG_BK * 2);
+#pragma unroll
+        for (int k = 0; k < TG_BK / 16; ++k)
+          tc_mma_bf16_pair(tmem_acc, da + (unsigned)(k * 32 >> 4), dw + (unsigned)(k * 32 >> 4), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        tc_commit_pair_of(empty_bar(st), leader);     // both CTAs' stages are free when these MMAs have read them
+      }
+      tc_commit_pair_of(acc_full, leader);            // both CTAs' accumulators are complete
+    }
+  } else {
+    // while the tensor cores work: 1 / rms of the first row this thread finishes, its residual and norm weights into L1
+    const int item = (int)threadIdx.x - 64, frl = item / (TGQ_BN / 8), fm = m0 + pair * rows_per + frl;
+    if (frl < rows_per && pair * rows_per + frl < TG_BM && fm < M) {
+      if (NORM && nm.in_sumsq != nullptr) {
+        float sum = 0.0f;
+        for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + fm];
+        first_inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+      }
+      const int fn = n0 + (item % (TGQ_BN / 8)) * 8;
+      if (fn < N) {
+        if (EPI == HB_EPI_RESIDUAL) prefetch_l1((const float*)Cv + (size_t)fm * ldc + fn);
+        if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) prefetch_l1(nm.out_w + fn);
+      }
+    }
+    ready = mbar_wait_cluster(acc_full, 0);
+    if (!ready && lane == 0) atomicExch(error_flag, 33);
+  }
+  pdl_launch();                     // this CTA's loads are done
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();               // every pair is through with its ring: rows may be sent into it
+  if (warp >= 2 && ready) {
+    // row l of this CTA's accumulator goes to the CTA with the same half whose block of rows holds l: slot [this pair][l - its first row]
+    tc_fence_after();
+    const int quad = warp & 3, l = quad * 32 + lane;
+    const int c_lo = warp < 6 ? 0 : TGQ_BN / 64, c_hi = c_lo + TGQ_BN / 64;
+    const int owner = l / rows_per;
+    const unsigned slot = mapa_shared(base + (unsigned)(((pair * rows_per + (l - owner * rows_per)) * TGQ_ROW_FLOATS) * 4),
+                                      (unsigned)(owner < S ? 2 * owner : 0) + half);
+#pragma unroll 1
+    for (int c = c_lo; c < c_hi; ++c) {
+      unsigned r[32];
+      tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
+      if (m0 + l < M) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          st_cluster_f4(slot + (unsigned)((c * 32 + j) * 4), __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();               // every row is where it is finished
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TGQ_BN) : "memory");
+  } else if (warp >= 2) {
+    // rows pair * rows_per ... of this CTA's 128; a thread takes 8 columns of a row, consecutive lanes consecutive columns
+    constexpr int GROUPS = TGQ_BN / 8;
+    const int idx = (int)threadIdx.x - 64;
+    const int part_lanes = part_cols >> 3;                                         // 8 or 16 lanes share a partial sum of a following norm
+    const int n_end = ((N + 2 * part_cols - 1) / (2 * part_cols)) * 2 * part_cols;   // ... which cover whole tiles of twice that width
+    const float* recv = reinterpret_cast<const float*>(gen);
+    for (int item0 = 0; item0 < rows_per * GROUPS; item0 += TG_EPI_WARPS * 32) {
+      const int item = item0 + idx;
+      const int g8 = item % GROUPS, rl = item / GROUPS, l = pair * rows_per + rl, m = m0 + l;
+      const bool active = rl < rows_per && l < TG_BM && m < M;
+      float sq = 0.0f;
+      if (active) {
+        float inv_rms = first_inv_rms;
+        if (NORM && nm.in_sumsq != nullptr && item0 > 0) {
+          float sum = 0.0f;
+          for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
+          inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
+        }
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        for (int q = 0; q < S; ++q) {           // in the order of the k ranges
+          const float4* src = reinterpret_cast<const float4*>(recv + (size_t)(q * rows_per + rl) * TGQ_ROW_FLOATS + g8 * 8);
+          const float4 x = src[0], y = src[1];
+          v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+          v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+        }
+        tg_epilogue8<EPI, NORM>(v, m, n0 + g8 * 8, M, N, Cv, ldc, nm, inv_rms, sq);
+      }
+      if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+        if (part_lanes == 16) sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+        if (active && (g8 & (part_lanes - 1)) == 0 && n0 + g8 * 8 < n_end)
+          nm.out_sumsq[(size_t)((n0 + g8 * 8) / part_cols) * nm.out_stride + m] = sq;
+      }
+    }
+  }
+}
+
 // The workspace the launcher may use for shared tiles: floats and counters for a grid of `sms` CTAs.
 #define TG_WS_FLOATS_PER_CTA (2 * TG_BM * 256)
 static float* g_tg_ws = nullptr;        // set by hb_gemm_tcgen05_set_workspace
@@ -1348,6 +1543,88 @@ static int tg_try_ksplit(const void* A, int lda, const void* W, int ldw, void* C
   return plan.ways > 0 ? 1 : 0;
 }
 
+// Pairs of CTAs per 256 x 256 tile (0: this product does not go that way): the most that make one wave
+// with K ranges of at least four blocks, and nothing below three fifths of the SMs.
+template <int EPI, bool NORM>
+static int tg_pairk_ways(int M, int N, int K) {
+  if (!g_tg_ksplit || !g_tg_pairs || M <= TG_BM || N < TGQ_BN) return 0;
+  const int tiles = ceil_div(M, 2 * TG_BM) * ceil_div(N, TGQ_BN), num_kb = ceil_div(K, TG_BK), sms = tg_sm_count();
+  static int resident[5] = {0};       // clusters of 2 * ways CTAs that the GPU holds at once, asked once per size
+  for (int ways = 4; ways >= 2; --ways) {
+    if (ways > num_kb / 4 || tiles * 2 * ways > sms) continue;
+    if (resident[ways] == 0) {
+      resident[ways] = -1;
+      if (cudaFuncSetAttribute(gemm_tcgen05_pair_ksplit_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, TGQ_SMEM_BYTES) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * ways);
+        cfg.blockDim = dim3(TG_THREADS);
+        cfg.dynamicSmemBytes = TGQ_SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2 * ways;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_ksplit_kernel<EPI, NORM>, &cfg) == cudaSuccess && n > 0) resident[ways] = n;
+      }
+      cudaGetLastError();
+    }
+    if (resident[ways] < tiles) continue;
+    return 5 * tiles * 2 * ways >= 3 * sms ? ways : 0;
+  }
+  return 0;
+}
+
+template <int EPI, bool NORM>
+static int tg_launch_pairk(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int ways, int* err,
+                           cudaStream_t s, const TgNorm& nm) {
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, TG_BM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, ldw, TG_BM);
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ceil_div(M, 2 * TG_BM) * ceil_div(N, TGQ_BN) * 2 * ways);
+  cfg.blockDim = dim3(TG_THREADS);
+  cfg.dynamicSmemBytes = TGQ_SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2 * ways;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = hb_pdl_enabled() == 1 ? 2 : 1;
+  const int part_cols = tg_tile_cols(M, N) / 2;        // a following norm's partial sums are kept per half of the other kernels' tiles
+  cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_ksplit_kernel<EPI, NORM>, ma, mw, C, ldc, M, N, K, ceil_div(TG_BM, ways), part_cols, err, nm);
+  HB_CHECK_LAUNCH("gemm_tcgen05 (pairs with K ranges in a cluster)");
+  return 0;
+}
+
+// 1: the product went that way; 0: it does not apply; negative: an error.
+template <bool NORM>
+static int tg_try_pairk(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epi, int* err,
+                        cudaStream_t s, const TgNorm& nm) {
+  int ways = 0, rc = 0;
+  switch (epi) {
+    case HB_EPI_STORE:
+      if ((ways = tg_pairk_ways<HB_EPI_STORE, NORM>(M, N, K)) > 0) rc = tg_launch_pairk<HB_EPI_STORE, NORM>(A, lda, W, ldw, C, ldc, M, N, K, ways, err, s, nm);
+      break;
+    case HB_EPI_STORE_F32:
+      if ((ways = tg_pairk_ways<HB_EPI_STORE_F32, NORM>(M, N, K)) > 0) rc = tg_launch_pairk<HB_EPI_STORE_F32, NORM>(A, lda, W, ldw, C, ldc, M, N, K, ways, err, s, nm);
+      break;
+    case HB_EPI_RESIDUAL:
+      if ((ways = tg_pairk_ways<HB_EPI_RESIDUAL, NORM>(M, N, K)) > 0) rc = tg_launch_pairk<HB_EPI_RESIDUAL, NORM>(A, lda, W, ldw, C, ldc, M, N, K, ways, err, s, nm);
+      break;
+  }
+  if (rc) return -rc;
+  return ways > 0 ? 1 : 0;
+}
+
 // Output columns per tile.  Tiles of 256 weight rows feed the tensor cores best; when there are too
 // few of them to keep half the SMs busy (decode batches, short prompts, matrices of few rows),
 // tiles of 128 give twice the tiles to spread and, where tiles are shared, pieces of half the size.
@@ -1405,6 +1682,7 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const TgNorm none{};
+  if (const int went = tg_try_pairk<false>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
   if (pairs) return tg_dispatch_pair<false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
   if (const int went = tg_try_ksplit<false>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
   return BN == 256 ? tg_dispatch<256, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none)
@@ -1478,6 +1756,7 @@ extern "C" int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, 
   if (rc) return rc;
   const TgNorm nm{in_sumsq, in_parts, in_stride, in_eps, out_w, (bf16*)out_xw, out_ld, out_sumsq, out_stride};
   cudaStream_t s = (cudaStream_t)stream;
+  if (const int went = tg_try_pairk<true>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, nm)) return went > 0 ? 0 : -went;
   if (pairs) return tg_dispatch_pair<true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
   if (const int went = tg_try_ksplit<true>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, nm)) return went > 0 ? 0 : -went;
   return BN == 256 ? tg_dispatch<256, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm)

@@ -390,7 +390,7 @@ def test_gemm_skinny_every_epilogue(M, N, K):
 @pytest.mark.parametrize("M,H,N2,eps", [(M, H, N2, eps) for M in (1, 5, 8, 13, 16, 65, 200, 333)
                                         for H, N2, eps in ((96, 64, 1e-5), (304, 16 * 1024, 1e-6), (1000, 48, 3e-3))]
                          + [(17, 6144, 6144, 1e-6), (40, 6160, 6144, 1e-5), (64, 6144, 16 * 1024, 1e-6), (100, 4096, 4096, 1e-6),
-                            (128, 4160, 6144, 1e-5)])
+                            (128, 4160, 6144, 1e-5), (200, 4096, 4096, 1e-6), (512, 4160, 4096, 1e-5), (300, 8192, 4096, 1e-6)])
 def test_products_with_a_norm_shared_between_them(M, H, N2, eps):
     """First product: x += a w1^T, and it begins RMSNorm(x; nw, eps).  Second product: finishes the
     norm and multiplies with w2 (store, SwiGLU and residual epilogues).  Up to 16 rows the decode
@@ -399,8 +399,8 @@ def test_products_with_a_norm_shared_between_them(M, H, N2, eps):
     step of its own in double precision, rounded to bfloat16 where the engine's plain path rounds."""
     torch.manual_seed(31)
     # between 17 and 64 rows only a large matrix goes through the tensor-memory kernel; up to 128 rows a
-    # large one has its K cut over a cluster of CTAs
-    K1 = 4096 if (16 < M <= 64 or (M <= 128 and H >= 4096)) else 72
+    # large one has its K cut over a cluster of CTAs, up to 512 over a cluster of pairs of CTAs
+    K1 = 4096 if (16 < M <= 64 or (M <= 512 and H >= 4096)) else 72
     a = torch.randn(M, K1).to(torch.bfloat16)
     w1 = (torch.randn(H, K1) * 0.3 * (72 / K1) ** 0.5).to(torch.bfloat16)
     x0 = torch.randn(M, H) * 3.0
@@ -595,12 +595,14 @@ def test_gemm_tcgen05_every_epilogue(M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(200, 4112, 2056), (700, 6512, 4800), (129, 4096, 4096),
                                    (64, 6144, 1024), (33, 4112, 4104), (17, 24592, 512), (50, 1000, 12288),
-                                   (100, 4096, 4096), (128, 6144, 2048), (65, 4096, 12288), (1, 5120, 5120), (64, 10240, 5120)])
+                                   (100, 4096, 4096), (128, 6144, 2048), (65, 4096, 12288), (1, 5120, 5120), (64, 10240, 5120),
+                                   (256, 4096, 4096), (300, 4112, 12288), (512, 4096, 2048), (192, 6144, 4096), (257, 5120, 8192)])
 def test_gemm_tcgen05_tiles_shared_between_ctas(M, N, K):
     """Sizes whose leftover tiles are cut into runs of k blocks (all 34 tiles; 8 of 156; 32 tiles;
     then decode batches, whose tiles are 128 weight rows wide and whose pieces hold only the rows
     there are: 48 tiles, 33 tiles, 45 of 193 tiles, 8 tiles of 192 k blocks; up to 128 rows a matrix
-    with few tiles has its K cut over a cluster of CTAs instead, in tiles of 128 to 256 columns):
+    with few tiles has its K cut over a cluster of CTAs instead, in tiles of 128 to 256 columns, and
+    up to about 512 rows over a cluster of pairs of CTAs, in tiles of 256 x 256):
     every epilogue, the norm begun by the residual epilogue, twice the same bits, and the counters
     back at zero (the second and third call)."""
     torch.manual_seed(19)
