@@ -46,7 +46,7 @@ struct PrefillTcArgs {
   int window;
   int* error_flag;
   int n_seqs, q_tiles;   // items = q_tiles x n_seqs x nkv x head pairs (some without queries when the sequences differ in length)
-  int* work_counter;     // next item; zero when the kernel starts
+  int* work_counter;     // next item; zero when the kernel starts, and left at zero by the CTA that fetches last
 };
 
 // One unit of work: 128 consecutive queries of two heads (or one) of one key/value head of one sequence.
@@ -189,6 +189,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int slot = n & 1;
         if (n >= 2 && !mbar_wait(bar(23 + slot), ((n >> 1) - 1) & 1)) { atomicExch(a.error_flag, 31); break; }
         const int fetched = atomicAdd(a.work_counter, 1);
+        // every CTA stops at its first index beyond the items, so the fetch that returns items + CTAs - 1
+        // is the last of the launch: it leaves the counter at zero for the next one
+        if (fetched == total_items + (int)gridDim.x - 1) atomicExch(a.work_counter, 0);
         const int idx = fetched < total_items ? fetched : -1;
         item_ring[slot] = idx;
         mbar_arrive_cta(bar(21 + slot));
@@ -481,8 +484,7 @@ extern "C" int hb_attention_prefill_tc_bf16(const void* q, int ldq, int n_tokens
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   }
   dim3 grid((unsigned)(items < sms ? items : sms));
-  cudaError_t e = cudaMemsetAsync(work_counter, 0, sizeof(int), s);
-  if (e != cudaSuccess) HB_FAIL(3, "attention_prefill_tc: cannot reset the work counter: %s", cudaGetErrorString(e));
+  cudaError_t e;
   // two Q tiles, two stages of K and of V; slack for the 1024-byte alignment; barriers and the item ring
   const int smem = 6 * (hd / 64) * PT_SUB + 1024 + 512;
   if (hd == 128) {

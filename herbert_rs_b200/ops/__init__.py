@@ -428,7 +428,7 @@ def check_kernel_errors() -> None:
         if code != 0:
             flag.zero_()
             # a kernel that gave up may have left arrival counters mid-count: start them afresh
-            for table in (_decode_counters, ):
+            for table in (_decode_counters, _work_counters):
                 if key in table:
                     table[key].zero_()
             if _tcgen05_ws.get(key) is not None:
@@ -731,8 +731,8 @@ _work_counters: dict = {}
 
 
 def _work_counter(device) -> torch.Tensor:
-    """One int per device from which the CTAs of a persistent kernel take their next item of work
-    (the launcher zeroes it on the stream before the kernel)."""
+    """One int per device from which the CTAs of a persistent kernel take their next item of work;
+    zero between launches (the CTA that fetches last puts it back)."""
     key = device_key(device)
     if key not in _work_counters:
         _work_counters[key] = torch.zeros(1, dtype=torch.int32, device=device)

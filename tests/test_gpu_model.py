@@ -384,7 +384,7 @@ def test_a_kernel_that_gave_up_is_reported_and_the_counters_start_afresh(model_d
     ref = plain["D"].logits(ids).numpy()
     assert_close(replay_tail_one_by_one(eng, ids, 8), ref, "bfloat16", "before", plain=plain["D"], ids=ids)   # every counter table exists now
     dev = ops.device_key(eng.rt.device)
-    tables = [ops._decode_counters[dev], ops._tcgen05_ws[dev][1], ops._stream_buffers(eng.rt.device)[1]]
+    tables = [ops._decode_counters[dev], ops._tcgen05_ws[dev][1], ops._stream_buffers(eng.rt.device)[1], ops._work_counters[dev]]
     for t in tables:
         t.fill_(3)
     ops._error_flag(eng.rt.device).fill_(7)
