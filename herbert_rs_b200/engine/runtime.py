@@ -16,6 +16,7 @@ class _Lane:
         self.offset = 0
         self.wanted = 0
         self.overflow: list = []
+        self.views: dict = {}           # (offset, shape, dtype) -> the tensor over that place
 
 
 class Workspace:
@@ -45,6 +46,7 @@ class Workspace:
         for lane in self.lanes:
             if lane.wanted > lane.buf.numel() and not self.frozen:
                 lane.buf = torch.empty(int(lane.wanted * 1.25) + 4096, dtype=torch.uint8, device=self.device)
+                lane.views.clear()      # they point into the old buffer
                 self._overflow_seen = True
             lane.offset = 0
             lane.wanted = 0
@@ -59,21 +61,30 @@ class Workspace:
 
     def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
         lane = self.current
+        shape = tuple(shape)
         n = 1
         for s in shape:
             n *= int(s)
-        es = torch.empty((), dtype=dtype).element_size()
+        es = dtype.itemsize
         nbytes = (n * es + 255) & ~255
         start = lane.offset
         lane.offset += nbytes
-        lane.wanted = max(lane.wanted, lane.offset)
+        if lane.offset > lane.wanted:
+            lane.wanted = lane.offset
         if lane.offset > lane.buf.numel():
             if self.frozen:
                 raise BackendError("workspace is frozen (a graph was captured) and too small for this step")
-            t = torch.empty(tuple(shape), dtype=dtype, device=self.device)  # this step only; grows at rewind
+            t = torch.empty(shape, dtype=dtype, device=self.device)  # this step only; grows at rewind
             lane.overflow.append(t)
             return t
-        return lane.buf[start:start + n * es].view(dtype).view(tuple(shape))
+        # the same requests come again every step and every layer: the view of a place is made once
+        key = (start, shape, dtype)
+        t = lane.views.get(key)
+        if t is None:
+            if len(lane.views) > 4096:
+                lane.views.clear()
+            t = lane.views[key] = lane.buf[start:start + n * es].view(dtype).view(shape)
+        return t
 
 
 # Positions per cache page unless a caller asks otherwise: the tile of keys that the attention

@@ -169,10 +169,18 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise BackendError(f"unsupported activation dtype {dtype}: float32 or bfloat16")
 
 
+_device_keys: dict = {}
+
+
 def device_key(device) -> str:
     """One name per CUDA device ("cuda:0"), whether it was given with or without its index."""
-    d = torch.device(device)
-    return f"cuda:{d.index if d.index is not None else torch.cuda.current_device()}"
+    key = _device_keys.get(device)
+    if key is None:
+        d = torch.device(device)
+        if d.index is None:      # depends on the current device: not remembered
+            return f"cuda:{torch.cuda.current_device()}"
+        key = _device_keys[device] = f"cuda:{d.index}"
+    return key
 
 
 def _ptr(t) -> int | None:
