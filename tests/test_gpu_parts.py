@@ -1,6 +1,8 @@
 """Each part alone, and the generality of the layer list: a toy mixer with state of its own
-that is registered, built and stepped from here, a layer that runs twice, and a layer that
-reads another layer's cache, none of which changes a file of the library."""
+that is registered, built and stepped from here, a routed feed-forward, other position encodings,
+another norm and another arrangement of a layer, an architecture with a model class of its own, a
+layer that runs twice, and a layer that reads another layer's cache, none of which changes a file
+of the library."""
 import json
 import os
 from dataclasses import dataclass
@@ -609,3 +611,148 @@ def test_block_part_alone(dtype):
     cos, sin = P.rope_tables(hd, 1e4, 21, torch.float64)
     ref = P.decoder_layer(x0.double(), {"model.layers.0." + k: v.float() for k, v in w.items()}, 0, cfg, cos, sin)
     assert_close(to_np(x), ref.numpy(), dtype, "block part")
+
+
+# ---- another norm and another arrangement of a layer -----------------------------------------------
+@dataclass(frozen=True)
+class OffsetNormSpec:
+    """y = x / sqrt(mean(x^2) + eps) * (1 + w): the stored weight is an offset from one."""
+    dim: int
+    eps: float
+    kind: str = "toy_offset_norm"
+
+
+class OffsetNorm(hb.parts.Norm):
+    """It has the form a product before it and a product after it can compute between them, with the
+    weight 1 + w, and says so (`shareable`); alone it runs as torch operations on the device."""
+
+    def __init__(self, spec, rt):
+        self.dim, self.eps = spec.dim, spec.eps
+
+    def param_specs(self):
+        return {"weight": ParamSpec((self.dim,), role="vector", init="normal")}
+
+    def load(self, tensors):
+        self.scale = (1.0 + tensors["weight"].float()).contiguous()
+
+    def forward(self, x, out, rows=None):
+        src = x if rows is None else x[rows.long()]
+        out.copy_((src * torch.rsqrt(src.pow(2).mean(dim=1, keepdim=True) + self.eps) * self.scale).to(out.dtype))
+
+    def shareable(self):
+        return (self.scale, self.eps)
+
+
+@dataclass(frozen=True)
+class SandwichSpec:
+    """x += post(mixer(norm1(x))); x += ffn(norm2(x)): a third norm, on the mixer's result."""
+    mixer: object
+    ffn: object
+    norm1: object
+    norm2: object
+    post: object
+    kind: str = "toy_sandwich"
+    names: tuple = (("norm1", "input_layernorm"), ("mixer", "self_attn"), ("post", "post_mixer_layernorm"),
+                    ("norm2", "pre_feedforward_layernorm"), ("ffn", "mlp"))
+
+
+class SandwichBlock(hb.parts.PreNormBlock):
+    """Takes the library's block for the bookkeeping of its parts and replaces the arrangement; it
+    neither takes a norm begun by the block before nor begins the next block's."""
+    chains_norms = False
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.post = hb.build_part("norm", spec.post, rt=rt)
+
+    def children(self):
+        return super().children() + (("post", self.post),)
+
+    def first_norm(self):
+        return None
+
+    def forward(self, x, batch, cache):
+        ws = self.rt.workspace
+        h = ws.take(x.shape, self.rt.dtype)
+        self.norm1.forward(x, h)
+        mixed = ws.take(x.shape, torch.float32)
+        mixed.zero_()
+        self.mixer.forward(h, mixed, batch, cache)          # adds into what it is given
+        normed = ws.take(x.shape, self.rt.dtype)
+        self.post.forward(mixed, normed)
+        x += normed.float()
+        h2 = ws.take(x.shape, self.rt.dtype)
+        self.norm2.forward(x, h2)
+        self.ffn.forward(h2, x, batch)
+
+
+@dataclass(frozen=True)
+class SandwichConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    num_hidden_layers: int
+    eps: float
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(*(d[k] for k in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "eps")))
+
+    def to_dict(self):
+        return dict(architectures=["ToySandwichForCausalLM"], **self.__dict__)
+
+    def model_spec(self):
+        H = self.hidden_size
+        off = OffsetNormSpec(H, self.eps)
+        att = AttentionSpec(H, 4, 2, 32, scale=32 ** -0.5, qk_norm=NormSpec(32, 1e-6), position=PositionSpec(32, 32, 1e4, 256))
+        ffn = SwiGLUSpec(H, self.intermediate_size)
+        # even layers: the sandwich with offset norms; odd layers: the library's block, offset norms too (shared with its products)
+        blocks = tuple(SandwichSpec(att, ffn, off, off, off) if i % 2 == 0 else BlockSpec(mixer=att, ffn=ffn, norm1=off, norm2=off)
+                       for i in range(self.num_hidden_layers))
+        return ModelSpec("ToySandwichForCausalLM", self.vocab_size, H, blocks,
+                         tuple(ScheduleStep(i) for i in range(self.num_hidden_layers)), off, True, 256)
+
+
+def _sandwich_plain(w, cfg, ids):
+    T, eps = len(ids), cfg["eps"]
+    acfg = dict(nh=4, nkv=2, hd=32, eps=1e-6, rot=32, scale=32 ** -0.5)
+    cos, sin = P.rope_tables(32, 1e4, T, torch.float64)
+    norm = lambda x, name: P.rms_norm(x, 1.0 + w[name].double(), eps)
+    x = P.embedding(w["model.embed_tokens.weight"], ids, torch.float64)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        a = P.attention_block(norm(x, p + "input_layernorm.weight"), w, p + "self_attn.", acfg, cos, sin, None)
+        if i % 2 == 0:
+            x = x + norm(a, p + "post_mixer_layernorm.weight")
+            x = x + P.swiglu_mlp(norm(x, p + "pre_feedforward_layernorm.weight"), w, p + "mlp.")
+        else:
+            x = x + a
+            x = x + P.swiglu_mlp(norm(x, p + "post_attention_layernorm.weight"), w, p + "mlp.")
+    return P.linear(norm(x, "model.norm.weight"), w["model.embed_tokens.weight"]).numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_norm_with_offset_weights_and_a_layer_with_a_third_norm(tmp_path, dtype):
+    """A norm kind and a block kind defined and registered here.  The norm stands in the toy block, in
+    the library's own block (where the products on either side of it share it) and as the final norm."""
+    hb.register_part("norm", "toy_offset_norm", OffsetNorm)
+    hb.register_part("block", "toy_sandwich", SandwichBlock)
+    hb.register_architecture("ToySandwichForCausalLM", SandwichConfig)
+    cfg = dict(architectures=["ToySandwichForCausalLM"], vocab_size=140, hidden_size=96, intermediate_size=160,
+               num_hidden_layers=4, eps=3e-5)
+    d = hb.write_random_model(cfg, str(tmp_path / "sandwich"), seed=8)
+    w = P.read_safetensors(os.path.join(d, "model.safetensors"))
+    assert "model.layers.0.post_mixer_layernorm.weight" in w and "model.layers.1.post_attention_layernorm.weight" in w
+    assert "model.layers.1.post_mixer_layernorm.weight" not in w
+    assert abs(float(w["model.layers.0.input_layernorm.weight"].float().mean())) < 0.02        # offsets, not weights near one
+    eng = engine_for(d, dtype, max_tokens=64 * 8, max_slots=3)
+    rng = np.random.default_rng(9)
+    reqs = [random_ids(rng, 140, n) for n in (70, 9, 33)]
+    refs = [_sandwich_plain(w, cfg, r) for r in reqs]
+    for r, ref in zip(reqs[:2], refs):
+        assert_close(replay_whole(eng, r), ref, dtype, "sandwich whole")
+        assert_close(replay_tail_one_by_one(eng, r, 8), ref, dtype, "sandwich one by one")
+    got = replay_batches(eng, reqs, [len(r) - 5 for r in reqs], [[0, 1, 2]])
+    for g, ref in zip(got, refs):
+        assert_close(g, ref, dtype, "sandwich batched")
+    assert eng.graph_replays > 0
