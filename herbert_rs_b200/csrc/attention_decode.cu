@@ -377,22 +377,29 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
     }
   };
   // The tile with the new position is written in this step (here, or by a kernel before this one):
-  // a CTA whose first loads would reach it starts them after the wait, every other one before.
+  // a CTA whose first loads would reach it starts them after the new key and value are stored.
   const bool early = !(t0 < t1 && t1 == tile_hi && t1 - t0 <= S - 1);
-  if (early) first_tiles();
   pdl_wait();
+  // This step's q (and, in the CTA that stores them, k and v) are asked for before the tiles: behind
+  // the tiles' bulk loads these few bytes would wait for all of them.
+  const int trow = p < f.table_rows ? p : f.table_rows - 1;
+  const bf16* row = FUSED ? f.qkv + (size_t)b * f.ld : nullptr;
+  const int qh = 2 * warp + (lane >> 4), qhc = qh < G ? qh : 0;     // a head per half-warp (the first 2 * AD_WARPS heads)
+  NormRotateLoads q_regs, k_regs;
+  uint2 v_regs = make_uint2(0u, 0u);
+  if (FUSED) q_regs = norm_rotate_load<bf16>(qh < G, row + (size_t)(kvh * G + qhc) * HD, f.qw, f.cos_tab + (size_t)trow * 64,
+                                             f.sin_tab + (size_t)trow * 64, lane & 15);
   if (writer) {
-    // store the new token's key (normed, rotated) and value before the pages are read
-    const int trow = p < f.table_rows ? p : f.table_rows - 1;
-    const bf16* row = f.qkv + (size_t)b * f.ld;
+    if (warp == 0) k_regs = norm_rotate_load<bf16>(lane < 16, row + (size_t)(a.nh + kvh) * HD, f.kw, f.cos_tab + (size_t)trow * 64,
+                                                   f.sin_tab + (size_t)trow * 64, lane & 15);
+    else if (warp == 1) v_regs = *reinterpret_cast<const uint2*>(row + (size_t)(a.nh + a.nkv + kvh) * HD + 4 * lane);
+  }
+  if (early) first_tiles();
+  if (writer) {
+    // store the new token's key (normed, rotated) and value before their page is read
     const size_t dst = (((size_t)pages[p / a.page_size] * a.nkv + kvh) * a.page_size + (p % a.page_size)) * HD;
-    if (warp == 0) {
-      norm_rotate_head128<bf16>(lane < 16, row + (size_t)(a.nh + kvh) * HD, f.kcache_w + dst, f.kw, f.eps,
-                                f.cos_tab + (size_t)trow * 64, f.sin_tab + (size_t)trow * 64, lane & 15);
-    } else if (warp == 1) {
-      const bf16* v = row + (size_t)(a.nh + a.nkv + kvh) * HD;
-      *reinterpret_cast<uint2*>(f.vcache_w + dst + 4 * lane) = *reinterpret_cast<const uint2*>(v + 4 * lane);
-    }
+    if (warp == 0) norm_rotate_finish<bf16>(k_regs, lane < 16, f.kcache_w + dst, f.kw != nullptr, f.eps, lane & 15);
+    else if (warp == 1) *reinterpret_cast<uint2*>(f.vcache_w + dst + 4 * lane) = v_regs;
   }
   if (!early) {
     __syncthreads();        // the new key and value are stored before their tile is fetched
@@ -415,9 +422,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_km_kernel(DecodeA
 
   if (FUSED) {
     // the query heads of this group, normed and rotated, while the first pages are on their way
-    const int trow = p < f.table_rows ? p : f.table_rows - 1;
-    const bf16* row = f.qkv + (size_t)b * f.ld;
-    for (int h0 = 0; h0 < G; h0 += 2 * AD_WARPS) {           // a head per half-warp
+    norm_rotate_finish<bf16>(q_regs, qh < G, sm_q + qhc * HD, f.qw != nullptr, f.eps, lane & 15);
+    for (int h0 = 2 * AD_WARPS; h0 < G; h0 += 2 * AD_WARPS) {           // more heads than half-warps
       const int h = h0 + 2 * warp + (lane >> 4);
       const int hc = h < G ? h : 0;
       norm_rotate_head128<bf16>(h < G, row + (size_t)(kvh * G + hc) * HD, sm_q + hc * HD, f.qw, f.eps,

@@ -32,19 +32,40 @@ template <> struct Vec4<bf16> {
   }
 };
 
+// The loads of one head's values, norm weights and angles, apart from the arithmetic: a caller that
+// has bulk loads to issue as well asks for these first, or they queue up behind the bulk.
+struct NormRotateLoads {
+  float lo[4], hi[4];
+  float4 wl, wh, c4, s4;
+};
+template <typename T>
+__device__ __forceinline__ NormRotateLoads norm_rotate_load(bool active, const T* x, const float* w, const float* cos_row,
+                                                            const float* sin_row, int l) {
+  NormRotateLoads r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.lo[i] = r.hi[i] = 0.0f;
+  r.wl = r.wh = r.c4 = make_float4(1.f, 1.f, 1.f, 1.f);
+  r.s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (active) {
+    Vec4<T>::load(x + 4 * l, r.lo);
+    Vec4<T>::load(x + 64 + 4 * l, r.hi);
+    if (w != nullptr) {
+      r.wl = *reinterpret_cast<const float4*>(w + 4 * l);
+      r.wh = *reinterpret_cast<const float4*>(w + 64 + 4 * l);
+    }
+    r.c4 = *reinterpret_cast<const float4*>(cos_row + 4 * l);
+    r.s4 = *reinterpret_cast<const float4*>(sin_row + 4 * l);
+  }
+  return r;
+}
+
 // Every lane of the warp must call this (the sums use full-warp shuffles that stay inside a
 // half-warp); a half-warp with nothing to do passes active = false and touches no memory.
-// x, dst: 8-byte (bfloat16) or 16-byte (float) aligned; w: norm weight [128] or null;
-// cos_row, sin_row: the 64 angles of the token's position, 16-byte aligned.
 template <typename T>
-__device__ __forceinline__ void norm_rotate_head128(bool active, const T* x, T* dst, const float* w, float eps,
-                                                    const float* cos_row, const float* sin_row, int l) {
-  float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-  if (active) {
-    Vec4<T>::load(x + 4 * l, lo);
-    Vec4<T>::load(x + 64 + 4 * l, hi);
-  }
-  if (w != nullptr) {
+__device__ __forceinline__ void norm_rotate_finish(NormRotateLoads& r, bool active, T* dst, bool normed, float eps, int l) {
+  float* lo = r.lo;
+  float* hi = r.hi;
+  if (normed) {
     float ss = lo[0] * lo[0] + lo[1] * lo[1] + lo[2] * lo[2] + lo[3] * lo[3] + hi[0] * hi[0] + hi[1] * hi[1] + hi[2] * hi[2] + hi[3] * hi[3];
     ss += __shfl_xor_sync(0xffffffffu, ss, 8);
     ss += __shfl_xor_sync(0xffffffffu, ss, 4);
@@ -52,14 +73,12 @@ __device__ __forceinline__ void norm_rotate_head128(bool active, const T* x, T* 
     ss += __shfl_xor_sync(0xffffffffu, ss, 1);
     if (active) {
       const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
-      const float4 wl = *reinterpret_cast<const float4*>(w + 4 * l), wh = *reinterpret_cast<const float4*>(w + 64 + 4 * l);
-      lo[0] = (lo[0] * inv) * wl.x; lo[1] = (lo[1] * inv) * wl.y; lo[2] = (lo[2] * inv) * wl.z; lo[3] = (lo[3] * inv) * wl.w;
-      hi[0] = (hi[0] * inv) * wh.x; hi[1] = (hi[1] * inv) * wh.y; hi[2] = (hi[2] * inv) * wh.z; hi[3] = (hi[3] * inv) * wh.w;
+      lo[0] = (lo[0] * inv) * r.wl.x; lo[1] = (lo[1] * inv) * r.wl.y; lo[2] = (lo[2] * inv) * r.wl.z; lo[3] = (lo[3] * inv) * r.wl.w;
+      hi[0] = (hi[0] * inv) * r.wh.x; hi[1] = (hi[1] * inv) * r.wh.y; hi[2] = (hi[2] * inv) * r.wh.z; hi[3] = (hi[3] * inv) * r.wh.w;
     }
   }
   if (active) {
-    const float4 c4 = *reinterpret_cast<const float4*>(cos_row + 4 * l), s4 = *reinterpret_cast<const float4*>(sin_row + 4 * l);
-    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, s[4] = {s4.x, s4.y, s4.z, s4.w};
+    const float c[4] = {r.c4.x, r.c4.y, r.c4.z, r.c4.w}, s[4] = {r.s4.x, r.s4.y, r.s4.z, r.s4.w};
     float olo[4], ohi[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -69,4 +88,13 @@ __device__ __forceinline__ void norm_rotate_head128(bool active, const T* x, T* 
     Vec4<T>::store(dst + 4 * l, olo);
     Vec4<T>::store(dst + 64 + 4 * l, ohi);
   }
+}
+
+// Both in one: x, dst: 8-byte (bfloat16) or 16-byte (float) aligned; w: norm weight [128] or null;
+// cos_row, sin_row: the 64 angles of the token's position, 16-byte aligned.  Every lane of the warp calls it.
+template <typename T>
+__device__ __forceinline__ void norm_rotate_head128(bool active, const T* x, T* dst, const float* w, float eps,
+                                                    const float* cos_row, const float* sin_row, int l) {
+  NormRotateLoads r = norm_rotate_load<T>(active, x, w, cos_row, sin_row, l);
+  norm_rotate_finish<T>(r, active, dst, w != nullptr, eps, l);
 }
