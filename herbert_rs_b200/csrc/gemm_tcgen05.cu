@@ -14,16 +14,13 @@
 //            C and half of the tile's columns), hand it back ("empty" barrier) and apply the epilogue: store, store as float, add
 //            into the float residual stream, or SwiGLU over column groups of 8 gate + 8 up.
 // With two accumulators the epilogue of tile i runs while the tensor cores work on tile i+1.
-// No thread-block clusters and no multicast are used.  Rows/columns beyond M, N, K are
+// This kernel uses no thread-block clusters; no kernel of the product uses multicast loads.  Below it: the
+// same product by pairs of CTAs (long prompts), and the entry points, which choose between these
+// two and the kernels of gemm_tcgen05_cluster.cu (few rows or few tiles: K cut over a cluster).
+// What they share is in gemm_tcgen05_parts.cuh.  Rows/columns beyond M, N, K are
 // zero-filled by TMA on load and skipped on store.  Every wait on an mbarrier is bounded; a wait
 // that runs out sets *error_flag and the CTA winds down (tensor memory is always released).
-#include "api.h"
-#include "common.cuh"
-#include "tcgen05_utils.cuh"
-
-#define TG_BM 128
-#define TG_THREADS 320      // TMA warp, MMA warp, eight epilogue warps
-#define TG_EPI_WARPS 8      // two per tensor-memory lane quadrant, each half of a tile's columns
+#include "gemm_tcgen05_parts.cuh"
 
 template <int BN>
 struct TgSmem {
@@ -32,34 +29,6 @@ struct TgSmem {
   static constexpr int kBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ unsigned pack2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<unsigned*>(&v);
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-// A norm shared between two products (see gemm_skinny.cu): RMSNorm y = x * w / rms(x) between "add
-// into the residual stream x" and "the next product".  The residual epilogue also writes x * w in
-// bfloat16 and, per tile of BN output columns, each row's sum of x^2; the product that reads x * w
-// multiplies its results by 1 / rms, summed from those partial sums in the order of the tiles.
-struct TgNorm {
-  const float* in_sumsq;   // consumer: [in_parts][in_stride] partial sums of the activation rows, or null
-  int in_parts, in_stride;
-  float in_eps;
-  const float* out_w;      // producer (residual epilogue): the next norm's weight [N], or null
-  bf16* out_xw;            // [M, out_ld]
-  int out_ld;
-  float* out_sumsq;        // [2 * ceil(N / BN)][out_stride]: one row per half tile of columns
-  int out_stride;
-};
-
-// The q/k/v product whose epilogue also does what follows it in an attention layer with heads of
-// 128 (crates/backends/backend_common/src/generic_attention/prefill/mod.rs:115-232): per-head RMSNorm
-// of q and k (one weight vector each, or none), rotation of the pairs (j, j + 64) at the token's
-// position, q (bfloat16) into the output, k and v into the paged cache.  A half tile of 128 columns
-// is one head, so an epilogue thread (one row, one half tile) holds a whole head of one token.
 #define HB_EPI_QKV 4
 struct TgQkv {
   const float* qw;         // norm weights [128], both or neither
@@ -126,179 +95,6 @@ struct TgSegments {
     return false;
   }
 };
-
-// The epilogue of 32 consecutive output columns (n ..) of row m, whose float results are in r:
-// scale by 1/rms, then store / store as float / add into the residual stream (and begin the next
-// norm: x * w in bfloat16, sum of x^2 into sq) / SwiGLU.  Rows beyond M and columns beyond N are skipped.
-template <int EPI, bool NORM>
-__device__ __forceinline__ void tg_epilogue32(unsigned (&r)[32], int m, int n, int M, int N, void* Cv, int ldc, const TgNorm& nm,
-                                              float inv_rms, float& sq) {
-  if (m < M) {
-    if (NORM) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * inv_rms);
-    }
-    if (EPI == HB_EPI_SWIGLU) {
-      // columns: [8 gate | 8 up] x 2 -> 16 outputs; output column = n/2 + ...
-      bf16* out = (bf16*)Cv + (size_t)m * ldc + (n >> 1);
-      float y[16];
-#pragma unroll
-      for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float gate = __uint_as_float(r[blk * 16 + j]), up = __uint_as_float(r[blk * 16 + 8 + j]);
-          // silu(g) * u; fast exponential and division: the result is rounded to bfloat16 next
-          y[blk * 8 + j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
-        }
-      if (n + 32 <= N && ((((size_t)m * ldc + (n >> 1)) & 7) == 0)) {
-#pragma unroll
-        for (int j = 0; j < 16; j += 8) {
-          uint4 v;
-          v.x = pack2(y[j], y[j + 1]); v.y = pack2(y[j + 2], y[j + 3]);
-          v.z = pack2(y[j + 4], y[j + 5]); v.w = pack2(y[j + 6], y[j + 7]);
-          *reinterpret_cast<uint4*>(out + j) = v;
-        }
-      } else {
-#pragma unroll
-        for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (n + blk * 16 + 8 + j < N) out[blk * 8 + j] = __float2bfloat16_rn(y[blk * 8 + j]);
-      }
-    } else if (EPI == HB_EPI_STORE) {
-      bf16* out = (bf16*)Cv + (size_t)m * ldc + n;
-      if (n + 32 <= N && ((((size_t)m * ldc + n) & 7) == 0)) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 v;
-          v.x = pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-          v.y = pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          v.z = pack2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-          v.w = pack2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-          *reinterpret_cast<uint4*>(out + j) = v;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (n + j < N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-      }
-    } else {
-      float* out = (float*)Cv + (size_t)m * ldc + n;
-      const bool begin_norm = NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr;
-      bf16* xw = begin_norm ? nm.out_xw + (size_t)m * nm.out_ld + n : nullptr;
-      if (n + 32 <= N && ((((size_t)m * ldc + n) & 3) == 0) && (!begin_norm || ((((size_t)m * nm.out_ld + n) & 7) == 0))) {
-        // every load first, then the arithmetic, then every store: the compiler cannot tell that the
-        // three arrays do not overlap and would otherwise wait for each store before the next load
-        float4 old4[8], w4[8];
-        if (EPI == HB_EPI_RESIDUAL) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) old4[q] = *reinterpret_cast<const float4*>(out + 4 * q);
-        }
-        if (begin_norm) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) w4[q] = *reinterpret_cast<const float4*>(nm.out_w + n + 4 * q);
-        }
-        float v[32];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          v[4 * q] = __uint_as_float(r[4 * q]); v[4 * q + 1] = __uint_as_float(r[4 * q + 1]);
-          v[4 * q + 2] = __uint_as_float(r[4 * q + 2]); v[4 * q + 3] = __uint_as_float(r[4 * q + 3]);
-          if (EPI == HB_EPI_RESIDUAL) {
-            v[4 * q] += old4[q].x; v[4 * q + 1] += old4[q].y; v[4 * q + 2] += old4[q].z; v[4 * q + 3] += old4[q].w;
-          }
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<float4*>(out + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        if (begin_norm) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) sq += v[j] * v[j];
-#pragma unroll
-          for (int q = 0; q < 8; q += 2) {
-            uint4 pk;
-            pk.x = pack2(v[4 * q] * w4[q].x, v[4 * q + 1] * w4[q].y);
-            pk.y = pack2(v[4 * q + 2] * w4[q].z, v[4 * q + 3] * w4[q].w);
-            pk.z = pack2(v[4 * q + 4] * w4[q + 1].x, v[4 * q + 5] * w4[q + 1].y);
-            pk.w = pack2(v[4 * q + 6] * w4[q + 1].z, v[4 * q + 7] * w4[q + 1].w);
-            *reinterpret_cast<uint4*>(xw + 4 * q) = pk;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (n + j < N) {
-            float v = __uint_as_float(r[j]);
-            if (EPI == HB_EPI_RESIDUAL) v += out[j];
-            out[j] = v;
-            if (begin_norm) {
-              xw[j] = __float2bfloat16_rn(v * nm.out_w[n + j]);
-              sq += v * v;
-            }
-          }
-      }
-    }
-  }
-}
-
-// The same for 8 consecutive output columns whose float results are in v (store, store as float, add
-// into the residual stream and begin the next norm; SwiGLU needs its groups of 16 and goes by 32).
-template <int EPI, bool NORM>
-__device__ __forceinline__ void tg_epilogue8(float (&v)[8], int m, int n, int M, int N, void* Cv, int ldc, const TgNorm& nm,
-                                             float inv_rms, float& sq) {
-  static_assert(EPI != HB_EPI_SWIGLU, "SwiGLU goes by chunks of 32 columns");
-  if (m >= M || n >= N) return;
-  if (NORM) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= inv_rms;
-  }
-  const bool whole = n + 8 <= N;
-  if (EPI == HB_EPI_STORE) {
-    bf16* out = (bf16*)Cv + (size_t)m * ldc + n;
-    if (whole && ((((size_t)m * ldc + n) & 7) == 0)) {
-      uint4 pk;
-      pk.x = pack2(v[0], v[1]); pk.y = pack2(v[2], v[3]); pk.z = pack2(v[4], v[5]); pk.w = pack2(v[6], v[7]);
-      *reinterpret_cast<uint4*>(out) = pk;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (n + j < N) out[j] = __float2bfloat16_rn(v[j]);
-    }
-  } else {
-    float* out = (float*)Cv + (size_t)m * ldc + n;
-    const bool begin_norm = NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr;
-    bf16* xw = begin_norm ? nm.out_xw + (size_t)m * nm.out_ld + n : nullptr;
-    if (whole && ((((size_t)m * ldc + n) & 3) == 0) && (!begin_norm || ((((size_t)m * nm.out_ld + n) & 7) == 0))) {
-      if (EPI == HB_EPI_RESIDUAL) {
-        const float4 o0 = *reinterpret_cast<const float4*>(out), o1 = *reinterpret_cast<const float4*>(out + 4);
-        v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
-        v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
-      }
-      *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(out + 4) = make_float4(v[4], v[5], v[6], v[7]);
-      if (begin_norm) {
-        const float4 w0 = *reinterpret_cast<const float4*>(nm.out_w + n), w1 = *reinterpret_cast<const float4*>(nm.out_w + n + 4);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sq += v[j] * v[j];
-        uint4 pk;
-        pk.x = pack2(v[0] * w0.x, v[1] * w0.y); pk.y = pack2(v[2] * w0.z, v[3] * w0.w);
-        pk.z = pack2(v[4] * w1.x, v[5] * w1.y); pk.w = pack2(v[6] * w1.z, v[7] * w1.w);
-        *reinterpret_cast<uint4*>(xw) = pk;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (n + j < N) {
-          float x = v[j];
-          if (EPI == HB_EPI_RESIDUAL) x += out[j];
-          out[j] = x;
-          if (begin_norm) {
-            xw[j] = __float2bfloat16_rn(x * nm.out_w[n + j]);
-            sq += x * x;
-          }
-        }
-    }
-  }
-}
 
 template <int BN, int EPI, bool NORM>
 __global__ void __launch_bounds__(TG_THREADS, 1)
@@ -536,75 +332,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //             commit, which carries no data);
 //   acc_empty[b]  in the first CTA: the sixteen epilogue warps of the pair arrive there.
 // Whole tiles only (no tiles shared between pairs); pairs walk the tiles m fastest.
-__device__ __forceinline__ unsigned cluster_ctarank() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ unsigned cluster_id_x() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ unsigned n_clusters_x() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ unsigned mapa_shared(unsigned addr, unsigned rank) {
-  unsigned r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait_cluster(unsigned bar, unsigned parity) {      // arrivals may come from the peer CTA
-  unsigned long long start = 0;
-  for (unsigned i = 0;; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-    if ((i & 255u) == 255u) {
-      const unsigned long long now = global_ns();
-      if (start == 0) start = now;
-      else if (now - start > TG_WAIT_NS) return false;
-    }
-  }
-}
-// A TMA tile load into this CTA's shared memory that signals an mbarrier given by its cluster address.
-__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar_cluster) {
-  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster)
-               : "memory");
-}
-__device__ __forceinline__ void tc_commit_pair(unsigned bar) {      // arrives at this barrier in both CTAs of the pair
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"((unsigned short)3)
-               : "memory");
-}
-__device__ __forceinline__ void tc_commit_pair_local(unsigned bar) {      // arrives at this CTA's barrier only
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
-                                                 unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // One head (128 columns starting at tensor-memory address taddr) of row m.  Every lane of the warp
 // runs the tensor-memory loads; rows beyond M store nothing.
 __device__ __forceinline__ void tg_epilogue_qkv(unsigned taddr, int m, int head, int M, void* Cv, int ldc, float inv_rms,
@@ -860,462 +587,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
-// ---------------------------------------------------------------------------------------------
-// At most 128 rows (a decode batch, a short prompt) against a matrix with few tiles of output
-// columns: the time is the weight stream's, and a tile per CTA would leave most SMs without work.
-// Here a thread-block cluster of S CTAs owns a tile and each CTA a range of K.  A CTA streams its
-// range through the ring into one accumulator and then sends every row of it, as floats, into the
-// shared memory of the CTA that finishes that row (rows are dealt in S blocks; stores through
-// distributed shared memory, which nobody waits for).  After one cluster barrier every CTA adds the
-// S partial rows it was sent, in the order of their k ranges, and runs the epilogue from its own
-// shared memory.  No workspace in global memory, no counters, nobody finishes alone, and no
-// multicast: every CTA loads its own slabs.  Up to 64 rows, the activation slab of a stage is 64
-// rows; the tensor cores still multiply 128, and what they make of the rows beyond (the weight slab
-// behind it) is never stored.
-__device__ __forceinline__ unsigned cluster_nctarank() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_f4(unsigned cluster_addr, float x, float y, float z, float w) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(cluster_addr), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
-}
-__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
-#define TGK_RING_BYTES (225 * 1024)      // per CTA: the ring of stages and, behind it, the rows it is sent
-#define TGK_SMEM_BYTES (TGK_RING_BYTES + 1024 + 256)
-#define TGK_MAX_STAGES 8
-
-struct TgKsplit {
-  int bn;         // output columns per tile: 128, 192 or 256 (whole halves of 128-column tiles: a following norm's partial sums are kept per 64 columns)
-  int ways;       // CTAs per tile = size of the cluster; 0: this product does not go that way
-  int a_rows;     // rows of the activation slab per stage: 64 or 128
-  int stages;
-  int rows_per;   // rows each CTA finishes
-};
-
-template <int EPI, bool NORM>
-__global__ void __launch_bounds__(TG_THREADS, 1)
-gemm_tcgen05_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
-                           int ldc, int M, int N, int K, TgKsplit plan, int* error_flag, TgNorm nm) {
-  const int bn = plan.bn, STAGES = plan.stages, rows_per = plan.rows_per;
-  const int a_bytes = plan.a_rows * TG_BK * 2, STAGE_BYTES = a_bytes + bn * TG_BK * 2;
-  const int row_floats = bn + 4;      // a partial row in shared memory, padded against bank conflicts
-  extern __shared__ unsigned char smem_raw[];
-  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
-  const int recv_off = STAGES * STAGE_BYTES;                 // [S][rows_per][row_floats] floats: what the cluster sends this CTA
-  const unsigned bars = base + TGK_RING_BYTES;               // full[8], empty[8], acc_full; then the tensor-memory slot
-  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + TGK_RING_BYTES + (2 * TGK_MAX_STAGES + 1) * 8);
-  auto full_bar = [&](int st) { return bars + st * 8; };
-  auto empty_bar = [&](int st) { return bars + (TGK_MAX_STAGES + st) * 8; };
-  const unsigned acc_full = bars + 2 * TGK_MAX_STAGES * 8;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rank = (int)cluster_ctarank(), S = (int)cluster_nctarank();
-  const int n0 = (int)cluster_id_x() * bn;
-  const int num_kb = (K + TG_BK - 1) / TG_BK;
-  const int kb0 = (int)(((long long)num_kb * rank) / S), kb1 = (int)(((long long)num_kb * (rank + 1)) / S);
-  const unsigned tmem_cols = bn <= 128 ? 128u : 256u;
-  float first_inv_rms = 1.0f;
-
-  if (threadIdx.x == 0) {
-    for (int st = 0; st < STAGES; ++st) {
-      mbar_init(full_bar(st), 1);
-      mbar_init(empty_bar(st), 1);
-    }
-    mbar_init(acc_full, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  cluster_arrive();                 // "this CTA runs": waited for before anything is sent to it
-  pdl_wait();
-  const unsigned tmem_acc = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      for (int kb = kb0; kb < kb1; ++kb) {
-        const int it = kb - kb0, st = it % STAGES;
-        if (it >= STAGES && !mbar_wait(empty_bar(st), ((it / STAGES) - 1) & 1)) {
-          atomicExch(error_flag, 21);
-          break;
-        }
-        mbar_expect_tx(full_bar(st), STAGE_BYTES);
-        const unsigned a_dst = base + st * STAGE_BYTES;
-        tma_load_2d(a_dst, &map_a, kb * TG_BK, 0, full_bar(st));
-        tma_load_2d(a_dst + a_bytes, &map_w, kb * TG_BK, n0, full_bar(st));
-      }
-    }
-    __syncwarp();
-    cluster_wait();
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
-      for (int kb = kb0; kb < kb1; ++kb) {
-        const int it = kb - kb0, st = it % STAGES;
-        if (!mbar_wait(full_bar(st), (it / STAGES) & 1)) {
-          atomicExch(error_flag, 22);
-          break;
-        }
-        tc_fence_after();
-        const unsigned a_addr = base + st * STAGE_BYTES;
-        const unsigned w_addr = a_addr + a_bytes;
-#pragma unroll
-        for (int k = 0; k < TG_BK / 16; ++k)
-          tc_mma_bf16(tmem_acc, umma_desc_sw128(a_addr + k * 32), umma_desc_sw128(w_addr + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-        tc_commit(empty_bar(st));
-      }
-      tc_commit(acc_full);          // arrives when every MMA is complete
-    }
-    __syncwarp();
-    cluster_wait();
-  } else {
-    // row m of this CTA's partial tile goes to the CTA that finishes it: slot [this rank][m - first row of that CTA]
-    const int quad = warp & 3, m = quad * 32 + lane;
-    const int chunks = bn >> 5, first = (chunks + 1) >> 1;
-    const int c_lo = warp < 6 ? 0 : first, c_hi = warp < 6 ? first : chunks;
-    // While the tensor cores work: what the first piece of a row this thread finishes will need from
-    // global memory (1 / rms of the row; the residual and the next norm's weights into L1).
-    if (S == 1) {
-      if (NORM && nm.in_sumsq != nullptr && m < M) {
-        float sum = 0.0f;
-        for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
-        first_inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
-      }
-    } else {
-      const int per_row = EPI == HB_EPI_SWIGLU ? chunks : bn >> 3, cols = EPI == HB_EPI_SWIGLU ? 32 : 8;
-      const int item = (int)threadIdx.x - 64, frl = item / per_row, fm = rank * rows_per + frl;
-      if (frl < rows_per && fm < M) {
-        if (NORM && nm.in_sumsq != nullptr) {
-          float sum = 0.0f;
-          for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + fm];
-          first_inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
-        }
-        const int fn = n0 + (item % per_row) * cols;
-        if (fn < N) {
-          if (EPI == HB_EPI_RESIDUAL) prefetch_l1((const float*)Cv + (size_t)fm * ldc + fn);
-          if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) prefetch_l1(nm.out_w + fn);
-        }
-      }
-    }
-    const bool ready = mbar_wait(acc_full, 0);
-    if (!ready && lane == 0) atomicExch(error_flag, 23);
-    __syncwarp();
-    cluster_wait();
-    if (ready && S == 1) {
-      // the tile is whole: straight from tensor memory (store and SwiGLU epilogues only: the launcher sees to it)
-      tc_fence_after();
-      float sq = 0.0f;
-#pragma unroll 1
-      for (int c = c_lo; c < c_hi; ++c) {
-        unsigned r[32];
-        tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
-        tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, first_inv_rms, sq);
-      }
-    } else if (ready) {
-      tc_fence_after();
-      const int owner = m / rows_per;
-      const unsigned slot = mapa_shared(base + (unsigned)recv_off + (unsigned)(((rank * rows_per + (m - owner * rows_per)) * row_floats) * 4),
-                                        (unsigned)(owner < S ? owner : 0));
-#pragma unroll 1
-      for (int c = c_lo; c < c_hi; ++c) {
-        unsigned r[32];
-        tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
-        if (m < M) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            st_cluster_f4(slot + (unsigned)((c * 32 + j) * 4), __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-        }
-      }
-    }
-  }
-  pdl_launch();                     // this CTA's loads are done: the next kernel's CTAs may take the places that free up
-  tc_fence_before();
-  cluster_arrive();                 // every row is where it is finished
-  cluster_wait();
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(tmem_cols) : "memory");
-  } else if (warp >= 2 && S > 1) {
-    // rows rank * rows_per ... of the tile; a thread takes 8 columns of a row (32 for SwiGLU), consecutive lanes consecutive columns
-    const int idx = (int)threadIdx.x - 64;
-    const float* recv = reinterpret_cast<const float*>(gen + recv_off);
-    if constexpr (EPI == HB_EPI_SWIGLU) {
-      const int chunks = bn >> 5;
-      for (int item0 = 0; item0 < rows_per * chunks; item0 += TG_EPI_WARPS * 32) {
-        const int item = item0 + idx;
-        const int c = item % chunks, rl = item / chunks, m = rank * rows_per + rl;
-        if (rl >= rows_per || m >= M) continue;
-        float inv_rms = first_inv_rms, sq = 0.0f;
-        if (NORM && nm.in_sumsq != nullptr && item0 > 0) {
-          float sum = 0.0f;
-          for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
-          inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
-        }
-        float acc[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
-        for (int q = 0; q < S; ++q) {           // in the order of the k ranges
-          const float4* src = reinterpret_cast<const float4*>(recv + (size_t)(q * rows_per + rl) * row_floats + c * 32);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 v = src[j];
-            acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
-          }
-        }
-        unsigned r[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(acc[j]);
-        tg_epilogue32<EPI, NORM>(r, m, n0 + c * 32, M, N, Cv, ldc, nm, inv_rms, sq);
-      }
-    } else {
-      const int groups = bn >> 3;                      // a multiple of 8: the 8 lanes of 64 columns sit side by side
-      const int n_end = ((N + 127) / 128) * 128;       // the partial sums of a following norm cover whole 128-column tiles
-      for (int item0 = 0; item0 < rows_per * groups; item0 += TG_EPI_WARPS * 32) {
-        const int item = item0 + idx;
-        const int g8 = item % groups, rl = item / groups, m = rank * rows_per + rl;
-        const bool active = rl < rows_per && m < M;
-        float sq = 0.0f;
-        if (active) {
-          float inv_rms = first_inv_rms;
-          if (NORM && nm.in_sumsq != nullptr && item0 > 0) {
-            float sum = 0.0f;
-            for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
-            inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
-          }
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = 0.0f;
-          for (int q = 0; q < S; ++q) {         // in the order of the k ranges
-            const float4* src = reinterpret_cast<const float4*>(recv + (size_t)(q * rows_per + rl) * row_floats + g8 * 8);
-            const float4 x = src[0], y = src[1];
-            v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-            v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
-          }
-          tg_epilogue8<EPI, NORM>(v, m, n0 + g8 * 8, M, N, Cv, ldc, nm, inv_rms, sq);
-        }
-        if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) {
-          // one sum per row and 64 columns
-          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-          sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-          if (active && (g8 & 7) == 0 && n0 + g8 * 8 < n_end) nm.out_sumsq[(size_t)((n0 + g8 * 8) >> 6) * nm.out_stride + m] = sq;
-        }
-      }
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// 129 to about 512 rows against a matrix with few tiles: too few 256 x 256 tiles for the pairs of CTAs,
-// and what an SM takes in from L2 per k block bounds every smaller tile.  Here a cluster of 2 S CTAs
-// owns a 256 x 256 tile: S pairs, each pair a range of K (tcgen05 with cta_group::2 inside a pair, as
-// in the pair kernel above).  When all of them are through (first cluster barrier: every ring is
-// free) each CTA sends the rows of its accumulator, as floats, into the ring of the CTA that
-// finishes them (the CTAs with the same half of the tile's rows, rows dealt in S blocks); after the
-// second cluster barrier every CTA adds the S partial rows it holds in k order and runs the epilogue,
-// 8 columns per thread.  No workspace, no counters, no multicast loads.
-#define TGQ_STAGES 6
-#define TGQ_STAGE_BYTES (2 * TG_BM * TG_BK * 2)
-#define TGQ_SMEM_BYTES (TGQ_STAGES * TGQ_STAGE_BYTES + 1024 + 256)
-#define TGQ_BN 256
-#define TGQ_ROW_FLOATS (TGQ_BN + 4)
-
-__device__ __forceinline__ void tc_commit_pair_of(unsigned bar, unsigned leader) {      // arrives at this barrier in both CTAs of the pair that starts at rank `leader`
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"((unsigned short)(3u << leader))
-               : "memory");
-}
-
-template <int EPI, bool NORM>
-__global__ void __launch_bounds__(TG_THREADS, 1)
-gemm_tcgen05_pair_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* Cv,
-                                int ldc, int M, int N, int K, int rows_per, int part_cols, int* error_flag, TgNorm nm) {
-  static_assert(EPI != HB_EPI_SWIGLU, "store and residual epilogues only");
-  static_assert((TG_BM + 8) * TGQ_ROW_FLOATS * 4 <= TGQ_STAGES * TGQ_STAGE_BYTES, "the rows a CTA is sent must fit into its ring");
-  extern __shared__ unsigned char smem_raw[];
-  const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
-  const unsigned bars = base + TGQ_STAGES * TGQ_STAGE_BYTES;       // full[STAGES], empty[STAGES], acc_full; then the tensor-memory slot
-  volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(gen + TGQ_STAGES * TGQ_STAGE_BYTES + (2 * TGQ_STAGES + 1) * 8);
-  auto full_bar = [&](int st) { return bars + st * 8; };
-  auto empty_bar = [&](int st) { return bars + (TGQ_STAGES + st) * 8; };
-  const unsigned acc_full = bars + 2 * TGQ_STAGES * 8;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned rank = cluster_ctarank(), leader = rank & ~1u, half = rank & 1u;
-  const int S = (int)(cluster_nctarank() >> 1), pair = (int)(rank >> 1);
-  const int tiles_m = (M + 2 * TG_BM - 1) / (2 * TG_BM);
-  const int tile = (int)cluster_id_x();
-  const int m0 = (tile % tiles_m) * 2 * TG_BM + (int)half * TG_BM;      // this CTA's 128 rows of the tile
-  const int n0 = (tile / tiles_m) * TGQ_BN;
-  const int num_kb = (K + TG_BK - 1) / TG_BK;
-  const int kb0 = (int)(((long long)num_kb * pair) / S), kb1 = (int)(((long long)num_kb * (pair + 1)) / S);
-
-  if (threadIdx.x == 0) {
-    for (int st = 0; st < TGQ_STAGES; ++st) {
-      mbar_init(full_bar(st), 1);     // the pair's first CTA arms it with both CTAs' bytes
-      mbar_init(empty_bar(st), 1);
-    }
-    mbar_init(acc_full, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TGQ_BN) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncwarp();
-  cluster_sync_all();               // every CTA's barriers are initialised before its peer signals them
-  tc_fence_after();
-  pdl_wait();
-  const unsigned tmem_acc = *tmem_slot;
-  const bool tmem_ok = tmem_acc == 0u;        // the pair's two CTAs must hold their accumulators at one address: the first allocation of an empty SM
-  if (!tmem_ok && threadIdx.x == 0) atomicExch(error_flag, 35);
-  float first_inv_rms = 1.0f;
-  bool ready = false;
-
-  if (!tmem_ok) {
-    // nothing is issued; the barriers below are still passed
-  } else if (warp == 0) {
-    if (lane == 0) {
-      const int w_row0 = n0 + (int)half * TG_BM;                     // this CTA's half of the tile's rows of W
-      for (int kb = kb0; kb < kb1; ++kb) {
-        const int it = kb - kb0, st = it % TGQ_STAGES;
-        if (it >= TGQ_STAGES && !mbar_wait_cluster(empty_bar(st), ((it / TGQ_STAGES) - 1) & 1)) {
-          atomicExch(error_flag, 31);
-          break;
-        }
-        const unsigned full0 = mapa_shared(full_bar(st), leader);
-        if (half == 0) mbar_expect_tx(full_bar(st), 2 * TGQ_STAGE_BYTES);
-        const unsigned a_dst = base + st * TGQ_STAGE_BYTES;
-        tma_load_2d_pair(a_dst, &map_a, kb * TG_BK, m0, full0);
-        tma_load_2d_pair(a_dst + TG_BM * TG_BK * 2, &map_w, kb * TG_BK, w_row0, full0);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && half == 0) {
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TGQ_BN >> 3) << 17) | ((unsigned)((2 * TG_BM) >> 4) << 24);
-      for (int kb = kb0; kb < kb1; ++kb) {
-        const int it = kb - kb0, st = it % TGQ_STAGES;
-        if (!mbar_wait_cluster(full_bar(st), (it / TGQ_STAGES) & 1)) {
-          atomicExch(error_flag, 32);
-          break;
-        }
-        tc_fence_after();
-        const unsigned a_addr = base + st * TGQ_STAGE_BYTES;
-        const unsigned long long da = umma_desc_sw128(a_addr), dw = umma_desc_sw128(a_addr + TG_BM * TG_BK * 2);
-#pragma unroll
-        for (int k = 0; k < TG_BK / 16; ++k)
-          tc_mma_bf16_pair(tmem_acc, da + (unsigned)(k * 32 >> 4), dw + (unsigned)(k * 32 >> 4), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-        tc_commit_pair_of(empty_bar(st), leader);     // both CTAs' stages are free when these MMAs have read them
-      }
-      tc_commit_pair_of(acc_full, leader);            // both CTAs' accumulators are complete
-    }
-  } else {
-    // while the tensor cores work: 1 / rms of the first row this thread finishes, its residual and norm weights into L1
-    const int item = (int)threadIdx.x - 64, frl = item / (TGQ_BN / 8), fm = m0 + pair * rows_per + frl;
-    if (frl < rows_per && pair * rows_per + frl < TG_BM && fm < M) {
-      if (NORM && nm.in_sumsq != nullptr) {
-        float sum = 0.0f;
-        for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + fm];
-        first_inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
-      }
-      const int fn = n0 + (item % (TGQ_BN / 8)) * 8;
-      if (fn < N) {
-        if (EPI == HB_EPI_RESIDUAL) prefetch_l1((const float*)Cv + (size_t)fm * ldc + fn);
-        if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) prefetch_l1(nm.out_w + fn);
-      }
-    }
-    ready = mbar_wait_cluster(acc_full, 0);
-    if (!ready && lane == 0) atomicExch(error_flag, 33);
-  }
-  pdl_launch();                     // this CTA's loads are done
-  tc_fence_before();
-  __syncwarp();
-  cluster_sync_all();               // every pair is through with its ring: rows may be sent into it
-  if (warp >= 2 && ready) {
-    // row l of this CTA's accumulator goes to the CTA with the same half whose block of rows holds l: slot [this pair][l - its first row]
-    tc_fence_after();
-    const int quad = warp & 3, l = quad * 32 + lane;
-    const int c_lo = warp < 6 ? 0 : TGQ_BN / 64, c_hi = c_lo + TGQ_BN / 64;
-    const int owner = l / rows_per;
-    const unsigned slot = mapa_shared(base + (unsigned)(((pair * rows_per + (l - owner * rows_per)) * TGQ_ROW_FLOATS) * 4),
-                                      (unsigned)(owner < S ? 2 * owner : 0) + half);
-#pragma unroll 1
-    for (int c = c_lo; c < c_hi; ++c) {
-      unsigned r[32];
-      tc_ld32(tmem_acc + ((unsigned)(quad * 32) << 16) + (unsigned)(c * 32), r);
-      if (m0 + l < M) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          st_cluster_f4(slot + (unsigned)((c * 32 + j) * 4), __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-      }
-    }
-  }
-  tc_fence_before();
-  __syncwarp();
-  cluster_sync_all();               // every row is where it is finished
-  if (warp == 1) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TGQ_BN) : "memory");
-  } else if (warp >= 2) {
-    // rows pair * rows_per ... of this CTA's 128; a thread takes 8 columns of a row, consecutive lanes consecutive columns
-    constexpr int GROUPS = TGQ_BN / 8;
-    const int idx = (int)threadIdx.x - 64;
-    const int part_lanes = part_cols >> 3;                                         // 8 or 16 lanes share a partial sum of a following norm
-    const int n_end = ((N + 2 * part_cols - 1) / (2 * part_cols)) * 2 * part_cols;   // ... which cover whole tiles of twice that width
-    const float* recv = reinterpret_cast<const float*>(gen);
-    for (int item0 = 0; item0 < rows_per * GROUPS; item0 += TG_EPI_WARPS * 32) {
-      const int item = item0 + idx;
-      const int g8 = item % GROUPS, rl = item / GROUPS, l = pair * rows_per + rl, m = m0 + l;
-      const bool active = rl < rows_per && l < TG_BM && m < M;
-      float sq = 0.0f;
-      if (active) {
-        float inv_rms = first_inv_rms;
-        if (NORM && nm.in_sumsq != nullptr && item0 > 0) {
-          float sum = 0.0f;
-          for (int i = 0; i < nm.in_parts; ++i) sum += nm.in_sumsq[(size_t)i * nm.in_stride + m];
-          inv_rms = rsqrtf(sum / (float)K + nm.in_eps);
-        }
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = 0.0f;
-        for (int q = 0; q < S; ++q) {           // in the order of the k ranges
-          const float4* src = reinterpret_cast<const float4*>(recv + (size_t)(q * rows_per + rl) * TGQ_ROW_FLOATS + g8 * 8);
-          const float4 x = src[0], y = src[1];
-          v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-          v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
-        }
-        tg_epilogue8<EPI, NORM>(v, m, n0 + g8 * 8, M, N, Cv, ldc, nm, inv_rms, sq);
-      }
-      if (NORM && EPI == HB_EPI_RESIDUAL && nm.out_w != nullptr) {
-        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
-        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
-        if (part_lanes == 16) sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-        if (active && (g8 & (part_lanes - 1)) == 0 && n0 + g8 * 8 < n_end)
-          nm.out_sumsq[(size_t)((n0 + g8 * 8) / part_cols) * nm.out_stride + m] = sq;
-      }
-    }
-  }
-}
-
 // The workspace the launcher may use for shared tiles: floats and counters for a grid of `sms` CTAs.
 #define TG_WS_FLOATS_PER_CTA (2 * TG_BM * 256)
 static float* g_tg_ws = nullptr;        // set by hb_gemm_tcgen05_set_workspace
 static int* g_tg_counters = nullptr;
 static int g_tg_ws_ctas = 0;
 
-static int tg_sm_count() {
+int tg_sm_count() {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -1333,6 +611,9 @@ static bool tg_splits_tiles(int tiles, int num_kb, int sms) {
 
 // Pairs of CTAs take products of many rows whose tiles are 256 columns wide and all whole.
 static int g_tg_pairs = 1;       // hb_gemm_tcgen05_set_pairs(0) switches them off (for measurements)
+static int g_tg_cluster = 1;     // hb_gemm_tcgen05_set_ksplit(0): no product cuts K over a cluster
+int tg_pairs_enabled() { return g_tg_pairs; }
+int tg_cluster_enabled() { return g_tg_cluster; }
 static bool tg_use_pairs(int M, int N, int K) {
   (void)K;
   return g_tg_pairs && M >= 512 && N >= 256;
@@ -1419,219 +700,13 @@ static int tg_dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, in
   HB_FAIL(2, "gemm_tcgen05: unknown epilogue %d", epi);
 }
 
-static int g_tg_ksplit = 1;
-static int tg_tile_cols(int M, int N);
-
-// Clusters of `ways` CTAs of this kernel that the GPU holds at once (asked once per size).
-template <int EPI, bool NORM>
-static int tg_ksplit_resident(int ways) {
-  static int resident[9] = {0};
-  if (resident[ways] == 0) {
-    resident[ways] = -1;
-    if (cudaFuncSetAttribute(gemm_tcgen05_ksplit_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, TGK_SMEM_BYTES) == cudaSuccess) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(ways);
-      cfg.blockDim = dim3(TG_THREADS);
-      cfg.dynamicSmemBytes = TGK_SMEM_BYTES;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = ways;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_ksplit_kernel<EPI, NORM>, &cfg) == cudaSuccess && n > 0) resident[ways] = n;
-    }
-    cudaGetLastError();
-  }
-  return resident[ways];
-}
-
-// The tile width and cluster size that put the most CTAs to work in one wave: every cluster resident
-// at once, K ranges of at least four blocks, at least four stages beside the rows a CTA is sent;
-// nothing below three quarters of the SMs.
-template <int EPI, bool NORM>
-static TgKsplit tg_ksplit_plan(int M, int N, int K) {
-  TgKsplit best{0, 0, 0, 0, 0};
-  if (!g_tg_ksplit || M > TG_BM || N < 256 || tg_tile_cols(M, N) != 128) return best;
-  const int num_kb = ceil_div(K, TG_BK), sms = tg_sm_count(), a_rows = M <= 64 ? 64 : TG_BM;
-  int best_ctas = 0;
-  for (int bn = 128; bn <= 256; bn += 64) {
-    const int tiles = ceil_div(N, bn), stage_bytes = (a_rows + bn) * TG_BK * 2;
-    for (int ways = 8; ways >= 2; --ways) {
-      const int rows_per = ceil_div(M, ways);
-      int stages = (TGK_RING_BYTES - ways * rows_per * (bn + 4) * 4) / stage_bytes;
-      if (stages > TGK_MAX_STAGES) stages = TGK_MAX_STAGES;
-      if (ways > num_kb / 4 || tiles * ways > sms || stages < 3 || tg_ksplit_resident<EPI, NORM>(ways) < tiles) continue;
-      const int ctas = (int)((long long)ways * N / bn);       // columns beyond N in the last tile are work without a result
-      if (ctas > best_ctas) {
-        best_ctas = ctas;
-        best = TgKsplit{bn, ways, a_rows, stages, rows_per};
-      }
-      break;
-    }
-  }
-  if (4 * best_ctas < 3 * sms) best.ways = 0;
-  return best;
-}
-
-// A matrix wide enough for a tile per SM without cutting K: the narrowest tiles (a multiple of 32
-// columns) that still make one wave, every stage of the ring for loads.  Store and SwiGLU epilogues.
-template <int EPI, bool NORM>
-static TgKsplit tg_whole_plan(int M, int N, int K) {
-  TgKsplit none{0, 0, 0, 0, 0};
-  if (!g_tg_ksplit || EPI == HB_EPI_RESIDUAL || M > TG_BM) return none;
-  const int sms = tg_sm_count(), a_rows = M <= 64 ? 64 : TG_BM;
-  const int bn = ceil_div(ceil_div(N, sms), 32) * 32;
-  if (bn < 64 || bn > 256) return none;
-  const int tiles = ceil_div(N, bn);
-  int stages = TGK_RING_BYTES / ((a_rows + bn) * TG_BK * 2);
-  if (stages > TGK_MAX_STAGES) stages = TGK_MAX_STAGES;
-  if (4 * tiles < 3 * sms || stages < 4 || ceil_div(K, TG_BK) < 8 || tg_ksplit_resident<EPI, NORM>(1) < tiles) return none;
-  return TgKsplit{bn, 1, a_rows, stages, M};
-}
-
-template <int EPI, bool NORM>
-static int tg_launch_ksplit(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, const TgKsplit& plan,
-                            int* err, cudaStream_t s, const TgNorm& nm) {
-  CUtensorMap ma, mw;
-  int rc = make_map(&ma, A, M, K, lda, plan.a_rows);
-  if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, plan.bn);
-  if (rc) return rc;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ceil_div(N, plan.bn) * plan.ways);
-  cfg.blockDim = dim3(TG_THREADS);
-  cfg.dynamicSmemBytes = TGK_SMEM_BYTES;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = plan.ways;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = hb_pdl_enabled() == 1 ? 2 : 1;
-  cudaLaunchKernelEx(&cfg, gemm_tcgen05_ksplit_kernel<EPI, NORM>, ma, mw, C, ldc, M, N, K, plan, err, nm);
-  HB_CHECK_LAUNCH("gemm_tcgen05 (K ranges in a cluster)");
-  return 0;
-}
-
-// 1: the product went that way; 0: it does not apply; negative: an error.
-template <bool NORM>
-static int tg_try_ksplit(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epi, int* err,
-                         cudaStream_t s, const TgNorm& nm) {
-  TgKsplit plan{0, 0, 0, 0, 0};
-  int rc = 0;
-  switch (epi) {
-    case HB_EPI_STORE:
-      if ((plan = tg_ksplit_plan<HB_EPI_STORE, NORM>(M, N, K)).ways > 0 || (plan = tg_whole_plan<HB_EPI_STORE, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
-      break;
-    case HB_EPI_STORE_F32:
-      if ((plan = tg_ksplit_plan<HB_EPI_STORE_F32, NORM>(M, N, K)).ways > 0 || (plan = tg_whole_plan<HB_EPI_STORE_F32, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_STORE_F32, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
-      break;
-    case HB_EPI_RESIDUAL:
-      if ((plan = tg_ksplit_plan<HB_EPI_RESIDUAL, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_RESIDUAL, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
-      break;
-    case HB_EPI_SWIGLU:
-      if ((plan = tg_ksplit_plan<HB_EPI_SWIGLU, NORM>(M, N, K)).ways > 0 || (plan = tg_whole_plan<HB_EPI_SWIGLU, NORM>(M, N, K)).ways > 0) rc = tg_launch_ksplit<HB_EPI_SWIGLU, NORM>(A, lda, W, ldw, C, ldc, M, N, K, plan, err, s, nm);
-      break;
-  }
-  if (rc) return -rc;
-  return plan.ways > 0 ? 1 : 0;
-}
-
-// Pairs of CTAs per 256 x 256 tile (0: this product does not go that way): the most that make one wave
-// with K ranges of at least four blocks, and nothing below three fifths of the SMs.
-template <int EPI, bool NORM>
-static int tg_pairk_ways(int M, int N, int K) {
-  if (!g_tg_ksplit || !g_tg_pairs || M <= TG_BM || N < TGQ_BN) return 0;
-  const int tiles = ceil_div(M, 2 * TG_BM) * ceil_div(N, TGQ_BN), num_kb = ceil_div(K, TG_BK), sms = tg_sm_count();
-  static int resident[5] = {0};       // clusters of 2 * ways CTAs that the GPU holds at once, asked once per size
-  for (int ways = 4; ways >= 2; --ways) {
-    if (ways > num_kb / 4 || tiles * 2 * ways > sms) continue;
-    if (resident[ways] == 0) {
-      resident[ways] = -1;
-      if (cudaFuncSetAttribute(gemm_tcgen05_pair_ksplit_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, TGQ_SMEM_BYTES) == cudaSuccess) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * ways);
-        cfg.blockDim = dim3(TG_THREADS);
-        cfg.dynamicSmemBytes = TGQ_SMEM_BYTES;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2 * ways;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_ksplit_kernel<EPI, NORM>, &cfg) == cudaSuccess && n > 0) resident[ways] = n;
-      }
-      cudaGetLastError();
-    }
-    if (resident[ways] < tiles) continue;
-    return 5 * tiles * 2 * ways >= 3 * sms ? ways : 0;
-  }
-  return 0;
-}
-
-template <int EPI, bool NORM>
-static int tg_launch_pairk(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int ways, int* err,
-                           cudaStream_t s, const TgNorm& nm) {
-  CUtensorMap ma, mw;
-  int rc = make_map(&ma, A, M, K, lda, TG_BM);
-  if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, TG_BM);
-  if (rc) return rc;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ceil_div(M, 2 * TG_BM) * ceil_div(N, TGQ_BN) * 2 * ways);
-  cfg.blockDim = dim3(TG_THREADS);
-  cfg.dynamicSmemBytes = TGQ_SMEM_BYTES;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2 * ways;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = hb_pdl_enabled() == 1 ? 2 : 1;
-  const int part_cols = tg_tile_cols(M, N) / 2;        // a following norm's partial sums are kept per half of the other kernels' tiles
-  cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_ksplit_kernel<EPI, NORM>, ma, mw, C, ldc, M, N, K, ceil_div(TG_BM, ways), part_cols, err, nm);
-  HB_CHECK_LAUNCH("gemm_tcgen05 (pairs with K ranges in a cluster)");
-  return 0;
-}
-
-// 1: the product went that way; 0: it does not apply; negative: an error.
-template <bool NORM>
-static int tg_try_pairk(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epi, int* err,
-                        cudaStream_t s, const TgNorm& nm) {
-  int ways = 0, rc = 0;
-  switch (epi) {
-    case HB_EPI_STORE:
-      if ((ways = tg_pairk_ways<HB_EPI_STORE, NORM>(M, N, K)) > 0) rc = tg_launch_pairk<HB_EPI_STORE, NORM>(A, lda, W, ldw, C, ldc, M, N, K, ways, err, s, nm);
-      break;
-    case HB_EPI_STORE_F32:
-      if ((ways = tg_pairk_ways<HB_EPI_STORE_F32, NORM>(M, N, K)) > 0) rc = tg_launch_pairk<HB_EPI_STORE_F32, NORM>(A, lda, W, ldw, C, ldc, M, N, K, ways, err, s, nm);
-      break;
-    case HB_EPI_RESIDUAL:
-      if ((ways = tg_pairk_ways<HB_EPI_RESIDUAL, NORM>(M, N, K)) > 0) rc = tg_launch_pairk<HB_EPI_RESIDUAL, NORM>(A, lda, W, ldw, C, ldc, M, N, K, ways, err, s, nm);
-      break;
-  }
-  if (rc) return -rc;
-  return ways > 0 ? 1 : 0;
-}
-
 // Output columns per tile.  Tiles of 256 weight rows feed the tensor cores best; when there are too
 // few of them to keep half the SMs busy (decode batches, short prompts, matrices of few rows),
 // tiles of 128 give twice the tiles to spread and, where tiles are shared, pieces of half the size.
 // Measured at the 8B sizes: 64 rows q/k/v 27.6 -> 18.1 us, down 52.3 -> 33.9; 256 rows o 41.8 ->
 // 26.8, down 70 -> 47; 512 rows o 41 -> 30, down 85 -> 67; with more tiles the wide ones win
 // (512 rows gate/up 89 against 108).
-static int tg_tile_cols(int M, int N) {
+int tg_tile_cols(int M, int N) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
@@ -1653,7 +728,7 @@ extern "C" int hb_gemm_tcgen05_set_pairs(int on) {
 }
 // 0: no product cuts K over a cluster (for measurements); 1 (default): products of at most 128 rows do where it applies.
 extern "C" int hb_gemm_tcgen05_set_ksplit(int on) {
-  g_tg_ksplit = on ? 1 : 0;
+  g_tg_cluster = on ? 1 : 0;
   return 0;
 }
 extern "C" long long hb_gemm_tcgen05_workspace_floats(int ctas) { return (long long)ctas * TG_WS_FLOATS_PER_CTA; }
@@ -1682,9 +757,9 @@ extern "C" int hb_gemm_tcgen05_bf16(const void* A, int lda, const void* W, int l
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const TgNorm none{};
-  if (const int went = tg_try_pairk<false>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
+  if (const int went = tg_try_pairk(false, A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
   if (pairs) return tg_dispatch_pair<false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
-  if (const int went = tg_try_ksplit<false>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
+  if (const int went = tg_try_ksplit(false, A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, none)) return went > 0 ? 0 : -went;
   return BN == 256 ? tg_dispatch<256, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none)
                    : tg_dispatch<128, false>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, none);
 }
@@ -1756,9 +831,9 @@ extern "C" int hb_gemm_tcgen05_norm_bf16(const void* A, int lda, const void* W, 
   if (rc) return rc;
   const TgNorm nm{in_sumsq, in_parts, in_stride, in_eps, out_w, (bf16*)out_xw, out_ld, out_sumsq, out_stride};
   cudaStream_t s = (cudaStream_t)stream;
-  if (const int went = tg_try_pairk<true>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, nm)) return went > 0 ? 0 : -went;
+  if (const int went = tg_try_pairk(true, A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, nm)) return went > 0 ? 0 : -went;
   if (pairs) return tg_dispatch_pair<true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
-  if (const int went = tg_try_ksplit<true>(A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, nm)) return went > 0 ? 0 : -went;
+  if (const int went = tg_try_ksplit(true, A, lda, W, ldw, C, ldc, M, N, K, epi, error_flag, s, nm)) return went > 0 ? 0 : -went;
   return BN == 256 ? tg_dispatch<256, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm)
                    : tg_dispatch<128, true>(ma, mw, C, ldc, M, N, K, epi, error_flag, s, nm);
 }
