@@ -275,3 +275,48 @@ def test_two_layers_at_8b_widths_with_the_full_vocabulary(tmp_path):
     top2 = np.sort(got["float32"], axis=-1)[:, -2:]
     clear = (top2[:, 1] - top2[:, 0]) > 6.0 * own
     assert (got["bfloat16"].argmax(-1) == got["float32"].argmax(-1))[clear].all()
+
+
+def test_prompts_and_decode_batches_of_17_to_700_rows_at_8b_widths(tmp_path):
+    """The row counts between a decode batch of 16 and a long prompt go through kernels of their own
+    (K cut over a cluster of CTAs up to 128 rows, over a cluster of pairs up to about 512): at 8B
+    widths, prompts of such lengths and decode steps of such batches against the float32 engine,
+    and no further from it than the same steps are with those kernels switched off."""
+    cfg = dict(WIDE2, vocab_size=20040)
+    d = str(tmp_path / "wide2s")
+    hb.write_random_model(cfg, d, seed=73, device="cuda")
+    rng = np.random.default_rng(73)
+    prompts = {n: rng.integers(0, cfg["vocab_size"], n).tolist() for n in (17, 40, 64, 100, 128, 200, 300, 512, 700)}
+    batches = {b: [rng.integers(0, cfg["vocab_size"], int(n)).tolist() for n in rng.integers(3, 90, b)] for b in (17, 40, 64)}
+
+    def run(dtype, cluster):
+        ops.set_gemm_ksplit(cluster)
+        try:
+            eng = hb.Engine.from_folder(d, dtype=dtype, max_tokens=64 * 64 * 4, max_slots=64)
+            out = {}
+            for n, ids in prompts.items():
+                s = eng.alloc_slot()
+                out["prompt", n] = eng.step([(s, ids)], [[0, n // 2, n - 1]]).double().cpu().numpy()
+                eng.free_slot(s)
+            for b, seqs in batches.items():
+                slots = [eng.alloc_slot() for _ in seqs]
+                eng.step([(s, ids[:-2]) for s, ids in zip(slots, seqs)], None)
+                for t in (-2, -1):          # two decode steps: the second replays the recorded one
+                    out["batch", b, t] = eng.step([(s, [ids[t]]) for s, ids in zip(slots, seqs)], "last").double().cpu().numpy()
+                for s in slots:
+                    eng.free_slot(s)
+            eng.check_kernels()
+            return out
+        finally:
+            ops.set_gemm_ksplit(True)
+
+    ref, new, old = run("float32", True), run("bfloat16", True), run("bfloat16", False)
+    worst = 0.0
+    for key in ref:
+        e_new, e_old = np.abs(new[key] - ref[key]).max(), np.abs(old[key] - ref[key]).max()
+        worst = max(worst, e_new / max(e_old, 1e-9))
+        assert e_new <= 1.5 * e_old + 1e-3, f"{key}: {e_new:.3e} with the cluster kernels, {e_old:.3e} without"
+        top2 = np.sort(ref[key], axis=-1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 4.0 * max(e_new, e_old)
+        assert (new[key].argmax(-1) == ref[key].argmax(-1))[clear].all(), key
+    print(f"17 to 700 rows at 8B widths: largest ratio of errors (cluster kernels / without) {worst:.2f}")
