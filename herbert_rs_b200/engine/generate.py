@@ -134,7 +134,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
         stops = getattr(engine, "default_stop_token_ids", ())
     stops = set() if options.ignore_eos else set(int(s) for s in stops)
     seed = sampling.resolved_seed()
-    max_batch = options.max_batch or getattr(engine, "max_slots", None) or len(prompts) or 1
+    max_slots = getattr(engine, "max_slots", None)
+    max_batch = options.max_batch or max_slots or len(prompts) or 1
+    if max_slots:
+        max_batch = min(max_batch, max_slots)       # a batch larger than the engine has slots is cut, not refused
 
     out: List[List[int]] = [[] for _ in prompts]
     reasons: List[str] = ["max_tokens"] * len(prompts)
@@ -271,6 +274,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: Optional[Generat
                         still.append(i)
                     else:
                         reasons[i] = r
+                        if nxt is not None and hasattr(engine, "truncate"):
+                            # the queued step takes it one position too far: given back at once (a page, if it
+                            # was a new one), so that the others find the room they would have found
+                            try:
+                                engine.truncate(slots[i], engine.length(slots[i]) - 1)
+                            except CacheError:
+                                pass                   # a model whose cache cannot step back keeps the position
                 active = still
                 flying = nxt
             stats.decode_seconds += time.perf_counter() - t0

@@ -226,7 +226,7 @@ class AheadEngine(FakeEngine):
 
     def __init__(self, *a, stop_after=None, **kw):
         super().__init__(*a, **kw)
-        self.open, self.tickets, self.last, self.from_device, self.unread_peak = {}, 0, None, 0, 0
+        self.open, self.tickets, self.last, self.from_device, self.unread_peak, self.truncated = {}, 0, None, 0, 0, 0
 
     def launch_and_choose(self, entries, params, uniforms):
         assert len(self.open) < 2
@@ -243,6 +243,14 @@ class AheadEngine(FakeEngine):
 
     def chosen(self, ticket):
         return self.open.pop(ticket)
+
+    def length(self, slot):
+        return self.lengths[slot]
+
+    def truncate(self, slot, n):
+        assert 0 <= n <= self.lengths[slot]
+        self.truncated += self.lengths[slot] - n
+        self.lengths[slot] = n
 
     def can_continue_on_device(self, slots):
         return self.last is not None and list(slots) == [s for s, _ in self.last] and len(self.open) < 2
@@ -265,8 +273,10 @@ def test_a_loop_one_step_ahead_decides_as_the_plain_one(stops, max_tokens):
         assert ahead.from_device > 0 and ahead.unread_peak == 2            # it did run ahead
     if not stops:
         assert len(ahead.steps) == len(plain.steps)                          # an end by max_tokens is foreseen: no step too many
+        assert ahead.truncated == 0
     else:
         assert len(plain.steps) <= len(ahead.steps) <= len(plain.steps) + len(stops)   # one dropped token per unforeseen end
+        assert ahead.truncated > 0                                                      # ... whose position is given back
 
 
 def test_a_loop_one_step_ahead_draws_the_same_uniforms():
@@ -285,4 +295,24 @@ def test_a_loop_one_step_ahead_runs_out_of_room_as_the_plain_one(kw):
     a = generate(plain, prompts, opt, hb.SamplingParams(temperature=0.0))
     b = generate(ahead, prompts, opt, hb.SamplingParams(temperature=0.0))
     assert a.tokens == b.tokens and a.finish_reasons == b.finish_reasons and "capacity" in a.finish_reasons
+    assert not ahead.open and ahead.free == plain.free
+
+
+def test_a_batch_size_beyond_the_engines_slots_is_cut_to_them():
+    e = FakeEngine(max_slots=2)
+    r = generate(e, [[1], [10], [20], [30], [40]], hb.GenerationOptions(max_tokens=2, max_batch=4), hb.SamplingParams(temperature=0.0))
+    assert r.tokens == [[2, 3], [11, 12], [21, 22], [31, 32], [41, 42]] and r.stats.batches == 3 and e.free == [0, 1]
+
+
+@pytest.mark.parametrize("pool", range(4, 18))
+def test_a_sequence_that_ends_a_step_late_leaves_the_others_the_room_it_would_have(pool):
+    """One sequence ends by a stop token while the step after is already queued with it in; the
+    position that step gave it is handed back, so the others run out of room exactly where they
+    would have with the plain loop."""
+    prompts = [[27], [1], [60, 61]]
+    opt = hb.GenerationOptions(max_tokens=9, stop_token_ids=[30])
+    plain, ahead = FakeEngine(pool=pool), AheadEngine(pool=pool)
+    a = generate(plain, prompts, opt, hb.SamplingParams(temperature=0.0))
+    b = generate(ahead, prompts, opt, hb.SamplingParams(temperature=0.0))
+    assert a.tokens == b.tokens and a.finish_reasons == b.finish_reasons
     assert not ahead.open and ahead.free == plain.free
